@@ -1,0 +1,108 @@
+// Shared helpers of the sm_100a kernels: element-type codes, loads and stores
+// that widen to float, block reductions, and the error channel of the C entry
+// points.  Every entry point returns 0 on success; on refusal it returns a
+// non-zero code and leaves a message for nncpu_last_error().
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum DType : int { DT_F32 = 0, DT_BF16 = 1 };
+
+constexpr int kPage = 64;  // tokens per cache page; the host-side cache uses the same number
+
+// Each library built from these sources keeps its own message; NN_LIB names the
+// library and the exported function that returns the message.
+#ifndef NN_LIB
+#error "define NN_LIB (the library's name) before including common.cuh"
+#endif
+#include <stdarg.h>
+#include <stdio.h>
+
+static thread_local char g_error[512] = "";
+
+static void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+#define NN_CAT2(a, b) a##b
+#define NN_CAT(a, b) NN_CAT2(a, b)
+extern "C" const char* NN_CAT(nncpu_last_error_, NN_LIB)() { return g_error; }
+
+#define NN_CHECK(cond, ...)            \
+    do {                               \
+        if (!(cond)) {                 \
+            set_error(__VA_ARGS__);    \
+            return 1;                  \
+        }                              \
+    } while (0)
+
+#define NN_LAUNCH_OK(name)                                                        \
+    do {                                                                          \
+        cudaError_t e_ = cudaGetLastError();                                      \
+        if (e_ != cudaSuccess) {                                                  \
+            set_error("%s: launch failed: %s", name, cudaGetErrorString(e_));     \
+            return 2;                                                             \
+        }                                                                         \
+    } while (0)
+
+__device__ __forceinline__ float ld_f(const void* p, size_t i, int dt) {
+    return dt == DT_F32 ? reinterpret_cast<const float*>(p)[i]
+                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ void st_f(void* p, size_t i, int dt, float v) {
+    if (dt == DT_F32) reinterpret_cast<float*>(p)[i] = v;
+    else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats.  The order of additions is fixed, so the result
+// does not depend on anything but the inputs.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}

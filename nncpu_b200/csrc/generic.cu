@@ -1,0 +1,528 @@
+// Kernels that take every size and both element types (float and bfloat16,
+// chosen per tensor at run time) and compute in 32-bit: the whole float32 path
+// of the model runs on them, and the bfloat16 path uses them wherever no
+// specialised kernel applies.  Plain CUDA cores, no reduced-precision matrix
+// mode anywhere in this file.
+//
+// The arithmetic follows ZacWalk/nncpu's scalar kernels:
+//   RMSNorm            crates/nncpu/src/kernels/scalar.rs:270-292
+//   rotary embedding   crates/nncpu/src/kernels/mod.rs:687-737
+//   attention          crates/nncpu/src/kernels/scalar.rs:444-548 (online softmax, scale after the dot)
+//   SiLU gate          crates/nncpu/src/kernels/scalar.rs:102-106,146-150
+//   argmax             crates/nncpu/src/model/forward.rs:1003-1011 (first largest)
+//   temperature draw   crates/nncpu/src/session/sample.rs:186-200
+
+#include <math.h>
+
+#define NN_LIB generic
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding rows: out[t, :] = table[ids[t], :] * scale, float32 out.
+// A negative id (a padded row) gives zeros.
+// ---------------------------------------------------------------------------
+__global__ void embed_kernel(const void* __restrict__ table, int table_dt, const int* __restrict__ ids,
+                             float* __restrict__ out, int hidden, float scale) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        out[(size_t)t * hidden + i] = id < 0 ? 0.0f : ld_f(table, (size_t)id * hidden + i, table_dt) * scale;
+}
+
+extern "C" int nncpu_embed(const void* table, int table_dt, const int* ids, float* out, int n_tok, int hidden,
+                           int vocab, float scale, void* stream) {
+    NN_CHECK(n_tok >= 0 && hidden > 0 && vocab > 0, "embed: n_tok %d, hidden %d, vocab %d", n_tok, hidden, vocab);
+    if (n_tok == 0) return 0;
+    embed_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(table, table_dt, ids, out, hidden, scale);
+    NN_LAUNCH_OK("embed");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm over the last axis: y = (x * scale) * gamma,
+// scale = 1 / sqrt(mean(x^2) + eps).  `rows` (optional) picks input rows, so
+// the final norm runs only on the rows whose logits are wanted.
+// ---------------------------------------------------------------------------
+__global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ gamma, int g_dt,
+                               void* __restrict__ y, int y_dt, const int* __restrict__ rows, int dim, float eps) {
+    __shared__ float scratch[33];
+    const int r_out = blockIdx.x;
+    const int r_in = rows ? rows[r_out] : r_out;
+    if (r_in < 0) {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(y, (size_t)r_out * dim + i, y_dt, 0.0f);
+        return;
+    }
+    const size_t base = (size_t)r_in * dim;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = ld_f(x, base + i, x_dt);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss * (1.0f / (float)dim) + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = ld_f(x, base + i, x_dt) * scale;
+        st_f(y, (size_t)r_out * dim + i, y_dt, gamma ? v * ld_f(gamma, i, g_dt) : v);
+    }
+}
+
+extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_dt, void* y, int y_dt,
+                             const int* rows, int n_rows, int dim, float eps, void* stream) {
+    NN_CHECK(n_rows >= 0 && dim > 0, "rmsnorm: %d rows of %d", n_rows, dim);
+    if (n_rows == 0) return 0;
+    int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
+    rmsnorm_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, x_dt, gamma, g_dt, y, y_dt, rows, dim, eps);
+    NN_LAUNCH_OK("rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// C[M, N] (+)= A[M, K] . W[N, K]^T + bias[N], 32-bit multiply-add on CUDA
+// cores.  Each output element is summed over k in ascending order by one
+// thread, so a row's result does not depend on which other rows are present.
+// ---------------------------------------------------------------------------
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+linear_simt_kernel(const void* __restrict__ A, int a_dt, const void* __restrict__ W, int w_dt,
+                   const void* __restrict__ bias, int b_dt, void* __restrict__ C, int c_dt, int M, int N, int K,
+                   int lda, int ldc, int accumulate) {
+    constexpr int NT = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int e = tid; e < BM * BK; e += NT) {
+            const int r = e / BK, c = e % BK;
+            const int m = m0 + r, k = k0 + c;
+            As[c][r] = (m < M && k < K) ? ld_f(A, (size_t)m * lda + k, a_dt) : 0.0f;
+        }
+        for (int e = tid; e < BN * BK; e += NT) {
+            const int r = e / BK, c = e % BK;
+            const int n = n0 + r, k = k0 + c;
+            Ws[c][r] = (n < N && k < K) ? ld_f(W, (size_t)n * K + k, w_dt) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += ld_f(bias, n, b_dt);
+            const size_t o = (size_t)m * ldc + n;
+            if (accumulate) v += ld_f(C, o, c_dt);
+            st_f(C, o, c_dt, v);
+        }
+    }
+}
+
+extern "C" int nncpu_linear_simt(const void* A, int a_dt, const void* W, int w_dt, const void* bias, int b_dt,
+                                 void* C, int c_dt, int M, int N, int K, int lda, int ldc, int accumulate,
+                                 void* stream) {
+    NN_CHECK(M >= 0 && N > 0 && K > 0 && lda >= K && ldc >= N, "linear: M %d, N %d, K %d, lda %d, ldc %d", M, N,
+             K, lda, ldc);
+    if (M == 0) return 0;
+    if (M <= 16) {
+        dim3 grid((N + 63) / 64, (M + 15) / 16);
+        linear_simt_kernel<16, 64, 32, 2, 2><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            A, a_dt, W, w_dt, bias, b_dt, C, c_dt, M, N, K, lda, ldc, accumulate);
+    } else {
+        dim3 grid((N + 63) / 64, (M + 63) / 64);
+        linear_simt_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            A, a_dt, W, w_dt, bias, b_dt, C, c_dt, M, N, K, lda, ldc, accumulate);
+    }
+    NN_LAUNCH_OK("linear");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Rotation table of a step: cs[t, i] = (cos, sin)(float(pos_t) * pos_scale * inv_freq[i]).
+// Computed once per step and read by every layer that shares the encoding.
+// ---------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ cs, int n_tok, int half, float pos_scale) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tok * half) return;
+    const int t = idx / half, i = idx % half;
+    const float theta = ((float)pos[t] * pos_scale) * inv_freq[i];
+    float s, c;
+    sincosf(theta, &s, &c);
+    cs[idx] = make_float2(c, s);
+}
+
+extern "C" int nncpu_rope_table(const int* pos, const float* inv_freq, float* cs, int n_tok, int half,
+                                float pos_scale, void* stream) {
+    NN_CHECK(n_tok >= 0 && half > 0, "rope_table: %d tokens, %d pairs", n_tok, half);
+    if (n_tok == 0) return 0;
+    const int total = n_tok * half;
+    rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(pos, inv_freq, (float2*)cs, n_tok,
+                                                                             half, pos_scale);
+    NN_LAUNCH_OK("rope_table");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Per-head q/k RMSNorm, rotation, and the append of k and v to the cache.
+// qkv [n_tok, (n_heads + 2 n_kv) * hd] holds q heads, then k heads, then v
+// heads.  One warp per (token, head).  q goes to q_out [n_tok, n_heads * hd];
+// k (normed, rotated) and v (raw) go to their page rows.  With n_kv == 0 the
+// mixer reads another layer's cache and only q is processed.
+// ---------------------------------------------------------------------------
+__global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_dt, const void* __restrict__ q_gamma,
+                                           const void* __restrict__ k_gamma, int g_dt, float eps,
+                                           const float2* __restrict__ cs, int rot_half,
+                                           const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                           const int* __restrict__ block_table, int bt_stride,
+                                           void* __restrict__ k_pages, void* __restrict__ v_pages, int kv_dt,
+                                           void* __restrict__ q_out, int q_dt, int n_tok, int n_heads, int n_kv,
+                                           int hd) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_tok = n_heads + 2 * n_kv;
+    const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long)n_tok * per_tok) return;
+    const int t = (int)(item / per_tok), h = (int)(item % per_tok);
+    const int seq = tok_seq[t];
+    float* x = smem + warp * hd;
+    const size_t in_base = (size_t)t * per_tok * hd + (size_t)h * hd;
+    const bool is_q = h < n_heads, is_k = !is_q && h < n_heads + n_kv;
+    const void* gamma = is_q ? q_gamma : (is_k ? k_gamma : nullptr);
+
+    float ss = 0.0f;
+    for (int i = lane; i < hd; i += 32) {
+        const float v = ld_f(qkv, in_base + i, in_dt);
+        x[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (gamma) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss * (1.0f / (float)hd) + eps);
+        for (int i = lane; i < hd; i += 32) x[i] = (x[i] * scale) * ld_f(gamma, i, g_dt);
+    }
+    __syncwarp();
+    if ((is_q || is_k) && cs != nullptr) {
+        for (int i = lane; i < rot_half; i += 32) {
+            const float2 c = cs[(size_t)t * rot_half + i];
+            const float a = x[i], b = x[i + rot_half];
+            x[i] = c.x * a - c.y * b;
+            x[i + rot_half] = c.y * a + c.x * b;
+        }
+        __syncwarp();
+    }
+    if (is_q) {
+        const size_t o = (size_t)t * n_heads * hd + (size_t)h * hd;
+        for (int i = lane; i < hd; i += 32) st_f(q_out, o + i, q_dt, x[i]);
+        return;
+    }
+    if (seq < 0) return;  // a padded row owns no place in the cache
+    const int pos = tok_pos[t];
+    const int page = block_table[(size_t)seq * bt_stride + pos / kPage];
+    if (page < 0) return;
+    const int kvh = is_k ? h - n_heads : h - n_heads - n_kv;
+    const size_t o = (((size_t)page * n_kv + kvh) * kPage + pos % kPage) * hd;
+    void* dst = is_k ? k_pages : v_pages;
+    for (int i = lane; i < hd; i += 32) st_f(dst, o + i, kv_dt, x[i]);
+}
+
+extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void* q_gamma, const void* k_gamma,
+                                         int g_dt, float eps, const float* cs, int rot_half, const int* tok_seq,
+                                         const int* tok_pos, const int* block_table, int bt_stride, void* k_pages,
+                                         void* v_pages, int kv_dt, void* q_out, int q_dt, int n_tok, int n_heads,
+                                         int n_kv, int hd, void* stream) {
+    NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv >= 0 && hd > 0, "qk_norm_rope_append: sizes");
+    NN_CHECK(hd % 2 == 0 && 2 * rot_half <= hd, "qk_norm_rope_append: head size %d with %d rotated pairs", hd,
+             rot_half);
+    NN_CHECK(hd <= 1024, "qk_norm_rope_append: head size %d is above 1024", hd);
+    if (n_tok == 0) return 0;
+    const int warps = 4;
+    const long items = (long)n_tok * (n_heads + 2 * n_kv);
+    const long blocks = (items + warps - 1) / warps;
+    qk_norm_rope_append_kernel<<<(unsigned)blocks, warps * 32, warps * hd * sizeof(float), (cudaStream_t)stream>>>(
+        qkv, in_dt, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, rot_half, tok_seq, tok_pos, block_table,
+        bt_stride, k_pages, v_pages, kv_dt, q_out, q_dt, n_tok, n_heads, n_kv, hd);
+    NN_LAUNCH_OK("qk_norm_rope_append");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Attention of every (token, head) over the cache of the token's sequence:
+// keys first..pos with first = max(0, pos + 1 - window) (window 0: all).
+// One block per (token, head) walks the span in chunks of 128 keys with an
+// online softmax; the chunk boundaries are fixed by the span alone, so the
+// result does not depend on the batch or on how tokens were cut into steps.
+// ---------------------------------------------------------------------------
+constexpr int kAttnThreads = 128;
+
+__global__ void __launch_bounds__(kAttnThreads)
+attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ k_pages,
+                 const void* __restrict__ v_pages, int kv_dt, const int* __restrict__ block_table, int bt_stride,
+                 const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, void* __restrict__ out,
+                 int out_dt, int n_heads, int n_kv, int hd, float scale, int window) {
+    extern __shared__ float smem[];
+    float* qs = smem;                       // hd
+    float* p = smem + hd;                   // kAttnThreads
+    long long* row = (long long*)(p + kAttnThreads);  // kAttnThreads element offsets of the chunk's rows
+    __shared__ float scratch[33];
+
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int seq = tok_seq[t];
+    const size_t out_base = (size_t)t * n_heads * hd + (size_t)h * hd;
+    if (seq < 0) {
+        for (int d = tid; d < hd; d += kAttnThreads) st_f(out, out_base + d, out_dt, 0.0f);
+        return;
+    }
+    const int pos = tok_pos[t];
+    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int kvh = h / (n_heads / n_kv);
+    for (int d = tid; d < hd; d += kAttnThreads) qs[d] = ld_f(q, out_base + d, q_dt);
+    __syncthreads();
+
+    float m = -INFINITY, l = 0.0f;
+    float acc[8];  // lanes d = tid + 128 * j, hd <= 1024
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+
+    for (int k0 = first; k0 <= pos; k0 += kAttnThreads) {
+        const int key = k0 + tid;
+        float s = -INFINITY;
+        long long off = -1;
+        if (key <= pos) {
+            const int page = block_table[(size_t)seq * bt_stride + key / kPage];
+            off = (((long long)page * n_kv + kvh) * kPage + key % kPage) * hd;
+            float dot = 0.0f;
+            for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], ld_f(k_pages, (size_t)off + d, kv_dt), dot);
+            s = dot * scale;
+        }
+        const float m_new = fmaxf(m, block_max(s, scratch));
+        const float w = key <= pos ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);  // 0 on the first chunk
+        l = l * corr + block_sum(w, scratch);
+        m = m_new;
+        p[tid] = w;
+        row[tid] = off;
+        __syncthreads();
+        const int n_keys = min(kAttnThreads, pos + 1 - k0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int d = tid + kAttnThreads * j;
+            if (d < hd) {
+                float a = acc[j] * corr;
+                for (int i = 0; i < n_keys; ++i) a = fmaf(p[i], ld_f(v_pages, (size_t)row[i] + d, kv_dt), a);
+                acc[j] = a;
+            }
+        }
+        __syncthreads();
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d = tid + kAttnThreads * j;
+        if (d < hd) st_f(out, out_base + d, out_dt, acc[j] * inv);
+    }
+}
+
+extern "C" int nncpu_attention(const void* q, int q_dt, const void* k_pages, const void* v_pages, int kv_dt,
+                               const int* block_table, int bt_stride, const int* tok_seq, const int* tok_pos,
+                               void* out, int out_dt, int n_tok, int n_heads, int n_kv, int hd, float scale,
+                               int window, void* stream) {
+    NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0,
+             "attention: %d heads over %d key/value heads", n_heads, n_kv);
+    NN_CHECK(hd > 0 && hd <= 1024 && hd % 2 == 0, "attention: head size %d must be even and at most 1024", hd);
+    NN_CHECK(window >= 0, "attention: window %d", window);
+    if (n_tok == 0) return 0;
+    const size_t smem = (hd + kAttnThreads) * sizeof(float) + kAttnThreads * sizeof(long long) + 8;
+    dim3 grid(n_tok, n_heads);
+    attention_kernel<<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(q, q_dt, k_pages, v_pages, kv_dt,
+                                                                         block_table, bt_stride, tok_seq, tok_pos,
+                                                                         out, out_dt, n_heads, n_kv, hd, scale,
+                                                                         window);
+    NN_LAUNCH_OK("attention");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Gated activation: out[t, i] = silu(gu[t, i]) * gu[t, inter + i].
+// ---------------------------------------------------------------------------
+__global__ void swiglu_kernel(const void* __restrict__ gu, int in_dt, void* __restrict__ out, int out_dt,
+                              long n_tok, int inter) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tok * inter) return;
+    const long t = idx / inter;
+    const int i = (int)(idx % inter);
+    const float g = ld_f(gu, (size_t)t * 2 * inter + i, in_dt);
+    const float u = ld_f(gu, (size_t)t * 2 * inter + inter + i, in_dt);
+    st_f(out, (size_t)idx, out_dt, (g * (1.0f / (1.0f + expf(0.0f - g)))) * u);
+}
+
+extern "C" int nncpu_swiglu(const void* gu, int in_dt, void* out, int out_dt, int n_tok, int inter, void* stream) {
+    NN_CHECK(n_tok >= 0 && inter > 0, "swiglu: %d tokens of %d", n_tok, inter);
+    if (n_tok == 0) return 0;
+    const long total = (long)n_tok * inter;
+    swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gu, in_dt, out, out_dt, n_tok,
+                                                                                      inter);
+    NN_LAUNCH_OK("swiglu");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Gather rows: out[r, :] = x[rows[r], :] (float32), zeros for a negative row.
+// ---------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   float* __restrict__ out, int dim) {
+    const int r = blockIdx.x, src = rows[r];
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        out[(size_t)r * dim + i] = src < 0 ? 0.0f : x[(size_t)src * dim + i];
+}
+
+extern "C" int nncpu_gather_rows(const float* x, const int* rows, float* out, int n_rows, int dim, void* stream) {
+    NN_CHECK(n_rows >= 0 && dim > 0, "gather_rows: %d rows of %d", n_rows, dim);
+    if (n_rows == 0) return 0;
+    gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, rows, out, dim);
+    NN_LAUNCH_OK("gather_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Greedy choice: the first largest logit of each row.  NaN never wins.
+// ---------------------------------------------------------------------------
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int n_warps = blockDim.x >> 5;
+        bv = lane < n_warps ? best_v[lane] : -INFINITY;
+        bi = lane < n_warps ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+extern "C" int nncpu_argmax(const float* logits, int* out, int n_rows, int vocab, void* stream) {
+    NN_CHECK(n_rows >= 0 && vocab > 0, "argmax: %d rows of %d", n_rows, vocab);
+    if (n_rows == 0) return 0;
+    argmax_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, out, vocab);
+    NN_LAUNCH_OK("argmax");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Temperature draw over the whole vocabulary, in token-id order:
+// p_i = exp((l_i - max) / T) in double, r = u * sum(p), the first i whose
+// running sum reaches r.  NaN counts as -inf.  `u[row]` is uniform in [0, 1).
+// ---------------------------------------------------------------------------
+__global__ void sample_kernel(const float* __restrict__ logits, const double* __restrict__ u,
+                              int* __restrict__ out, int vocab, float inv_temp) {
+    __shared__ float scratch[33];
+    __shared__ double part[1024];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += nt) {
+        const float v = row[i];
+        if (v == v) mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, scratch);
+    if (!(mx > -INFINITY) || mx == INFINITY) {  // nothing finite to draw from: the first largest
+        if (tid == 0) {
+            int best = 0;
+            for (int i = 1; i < vocab; ++i) if (row[i] > row[best] || (row[best] != row[best] && row[i] == row[i])) best = i;
+            out[blockIdx.x] = best;
+        }
+        return;
+    }
+    // thread `tid` owns the contiguous ids [lo, hi)
+    const int per = (vocab + nt - 1) / nt;
+    const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
+    double s = 0.0;
+    for (int i = lo; i < hi; ++i) {
+        const float v = row[i];
+        if (v == v) s += exp((double)(v - mx) * (double)inv_temp);
+    }
+    part[tid] = s;
+    __syncthreads();
+    if (tid == 0) {
+        double total = 0.0;
+        for (int i = 0; i < nt; ++i) total += part[i];
+        double r = u[blockIdx.x] * total;
+        int owner = nt - 1;
+        for (int i = 0; i < nt; ++i) {
+            if (r - part[i] <= 0.0 && part[i] > 0.0) { owner = i; break; }
+            r -= part[i];
+        }
+        // walk the owner's ids; the last id with weight is the fallback
+        const int olo = min(vocab, owner * per), ohi = min(vocab, olo + per);
+        int pick = -1, last = -1;
+        for (int i = olo; i < ohi; ++i) {
+            const float v = row[i];
+            if (!(v == v)) continue;
+            const double w = exp((double)(v - mx) * (double)inv_temp);
+            if (w > 0.0) last = i;
+            r -= w;
+            if (r <= 0.0 && w > 0.0) { pick = i; break; }
+        }
+        if (pick < 0) pick = last;
+        if (pick < 0) {  // rounding pushed r past the end: the last id with weight anywhere
+            for (int i = vocab - 1; i >= 0; --i) {
+                const float v = row[i];
+                if (v == v && exp((double)(v - mx) * (double)inv_temp) > 0.0) { pick = i; break; }
+            }
+        }
+        out[blockIdx.x] = pick < 0 ? 0 : pick;
+    }
+}
+
+extern "C" int nncpu_sample_temperature(const float* logits, const double* u, int* out, int n_rows, int vocab,
+                                        float temperature, void* stream) {
+    NN_CHECK(n_rows >= 0 && vocab > 0, "sample: %d rows of %d", n_rows, vocab);
+    NN_CHECK(temperature > 0.0f && isfinite(temperature), "sample: temperature %g must be positive", temperature);
+    if (n_rows == 0) return 0;
+    sample_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, u, out, vocab, 1.0f / temperature);
+    NN_LAUNCH_OK("sample");
+    return 0;
+}

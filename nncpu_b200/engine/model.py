@@ -1,0 +1,134 @@
+"""A model: the parts its spec names, their weights, and the forward pass of
+one step over a schedule of layers.
+
+The forward pass follows the reference's order
+(crates/nncpu/src/model/forward.rs:848-965): embedding rows, the schedule's
+blocks over a float32 residual stream, and, only for the rows whose logits
+are wanted, the final norm and the vocabulary projection
+(crates/nncpu/src/model/forward.rs:974-985,1017-1030).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..cache import KVRequest, StateRequest
+from ..config import ModelSpec, load_config
+from ..errors import BadFormat, InvalidArgument
+from ..kernels import ops
+from ..parts import EntryCache, Runtime, build
+from ..weights import ParamSpec, load_tensors
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise InvalidArgument(f"dtype {dtype!r} is not supported (bfloat16 or float32)") from None
+
+
+def _shares(spec: ModelSpec) -> List[bool]:
+    """Per layer: whether its runs read another entry's keys and values."""
+    share: List[Optional[bool]] = [None] * len(spec.layers)
+    for i, e in enumerate(spec.schedule):
+        if not 0 <= e.layer < len(spec.layers):
+            raise BadFormat(f"schedule entry {i} names layer {e.layer}, but there are {len(spec.layers)} layers")
+        s = e.cache_of is not None
+        if share[e.layer] is not None and share[e.layer] != s:
+            raise BadFormat(f"layer {e.layer} runs both with a cache of its own and on another entry's cache")
+        share[e.layer] = s
+    return [bool(s) for s in share]
+
+
+def build_blocks(spec: ModelSpec) -> list:
+    shares = _shares(spec)
+    return [build("block", b, **({"reads_other_cache": True} if shares[i] else {}))
+            for i, b in enumerate(spec.layers)]
+
+
+def parameter_list(spec: ModelSpec) -> List[ParamSpec]:
+    """Every tensor the model of ``spec`` reads from its file."""
+    e, o = spec.embedding, spec.output
+    params = [ParamSpec(f"{e.name}.weight", (e.vocab_size, e.hidden_size))]
+    for block in build_blocks(spec):
+        params += block.params()
+    params += build("norm", o.norm).params()
+    if not o.tied:
+        params.append(ParamSpec(f"{o.name}.weight", (o.vocab_size, o.hidden_size)))
+    return params
+
+
+class Model:
+    """Built by ``Model.load``; run through an ``Engine``."""
+
+    def __init__(self, config, tensors: Dict[str, torch.Tensor], rt: Runtime):
+        self.config = config
+        self.spec = spec = config.model_spec()
+        self.rt = rt
+        self.blocks = build_blocks(spec)
+        self.final_norm = build("norm", spec.output.norm)
+        tensors = dict(tensors)
+        self.embed_table = tensors[f"{spec.embedding.name}.weight"]
+        self.lm_head = self.embed_table if spec.output.tied else tensors[f"{spec.output.name}.weight"]
+        for block in self.blocks:
+            block.bind(tensors, rt)
+        self.final_norm.bind(tensors, rt)
+        self.schedule = list(spec.schedule)
+
+    @classmethod
+    def load(cls, folder, dtype="bfloat16", device="cuda:0", progress=None) -> "Model":
+        """Reads ``folder/config.json``, picks the architecture's configuration
+        class from the registry, checks ``folder/model.safetensors`` against
+        what the parts ask for, and moves the weights to ``device``."""
+        config = load_config(folder)
+        dt = resolve_dtype(dtype)
+        rt = Runtime(device, dt)
+        tensors = load_tensors(folder, parameter_list(config.model_spec()), dt, rt.device, progress)
+        return cls(config, tensors, rt)
+
+    # -- storage the schedule asks for ------------------------------------------
+
+    def cache_requests(self) -> Tuple[List[Tuple[Optional[KVRequest], Optional[StateRequest]]], List[Optional[int]]]:
+        requests, cache_of = [], []
+        for e in self.schedule:
+            mixer = self.blocks[e.layer].mixer
+            requests.append((None if e.cache_of is not None else mixer.kv_request(), mixer.state_request()))
+            cache_of.append(e.cache_of)
+        return requests, cache_of
+
+    # -- numbers for reports ------------------------------------------------------
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights a decode step reads: every scheduled block once
+        and the output matrix; the embedding table is gathered, not streamed."""
+        head = self.lm_head.numel() * self.lm_head.element_size()
+        return sum(self.blocks[e.layer].weight_bytes() for e in self.schedule) + head
+
+    def info(self) -> dict:
+        n_params = sum(int(torch.tensor(p.shape).prod()) for p in parameter_list(self.spec) if p.required)
+        return {"architecture": self.spec.architecture, "dtype": str(self.rt.dtype).replace("torch.", ""),
+                "layers": len(self.spec.layers), "schedule": len(self.schedule),
+                "hidden_size": self.spec.hidden_size, "vocab_size": self.spec.vocab_size,
+                "parameters": n_params, "max_positions": self.spec.max_positions}
+
+    # -- one step -------------------------------------------------------------------
+
+    def forward(self, ctx, cache) -> Optional[torch.Tensor]:
+        """Runs the step's tokens through the schedule and returns float32
+        logits [n_wanted, vocab] (None when no row is wanted)."""
+        rt, spec = self.rt, self.spec
+        residual = rt.empty(ctx.n_tokens, spec.hidden_size, dtype=torch.float32)
+        ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale)
+        for i, e in enumerate(self.schedule):
+            self.blocks[e.layer].forward(ctx, residual, ctx.entry_cache(cache, i))
+        if ctx.n_wanted == 0:
+            return None
+        x = self.final_norm.forward(ctx, residual, rows=ctx.logit_rows)
+        logits = rt.empty(ctx.n_wanted, spec.vocab_size, dtype=torch.float32)
+        rt.linear(x, self.lm_head, None, logits)
+        return logits

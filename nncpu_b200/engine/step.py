@@ -1,0 +1,133 @@
+"""The step function: one batch of sequences, each bringing its next tokens.
+
+A step runs only the tokens it is given, as one flat batch, against the cache
+that earlier steps left, appends their keys and values, and returns the logits
+at the wanted places.  Sequences of a batch start together with prompts of
+unequal lengths (one step), then go on by one token each; a step may also mix
+lengths freely, because every kernel works from per-token (sequence, position)
+pairs.  Arguments are checked before anything changes, as the reference does
+for its one-sequence forward pass (crates/nncpu/src/model/forward.rs:851-886).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache import Cache
+from ..errors import ContextFull, InvalidArgument
+from ..parts import EntryCache
+
+
+@dataclass
+class StepContext:
+    """What kernels and parts see of a step.  Device tensors are int32."""
+    n_tokens: int
+    n_seqs: int
+    n_wanted: int
+    tok_ids: torch.Tensor       # [n_tokens] token ids
+    tok_seq: torch.Tensor       # [n_tokens] index of the token's sequence in this step (-1: padding)
+    tok_pos: torch.Tensor       # [n_tokens] position in its sequence
+    seq_slots: torch.Tensor     # [n_seqs] cache slot of each sequence
+    cu_seqlens: torch.Tensor    # [n_seqs + 1] first flat token of each sequence
+    logit_rows: torch.Tensor    # [n_wanted] flat tokens whose logits are wanted
+    block_tables: List[torch.Tensor]  # per cache group: [n_seqs, width] page ids
+    q_lens: List[int]           # host: tokens per sequence in this step
+    kv_lens: List[int]          # host: length of each sequence after this step
+    is_decode: bool             # every sequence brings exactly one token
+    memo: Dict = field(default_factory=dict)  # per-step results shared between layers
+
+    def entry_cache(self, cache: Cache, entry: int) -> EntryCache:
+        g = cache.group_of(entry)
+        if g is None:
+            return EntryCache(None, None, None, False, cache.state(entry))
+        k, v = cache.kv(entry)
+        return EntryCache(k, v, self.block_tables[g], cache.owns_kv(entry), cache.state(entry))
+
+
+class Engine:
+    """A model with its cache.  ``step`` is the only way tokens reach the model."""
+
+    def __init__(self, model, max_tokens: int, n_slots: Optional[int] = None, max_seq_len: Optional[int] = None,
+                 kv_dtype: Optional[torch.dtype] = None):
+        self.model = model
+        requests, cache_of = model.cache_requests()
+        rt = model.rt
+        self.cache = Cache(requests, cache_of, max_tokens, kv_dtype or rt.dtype, rt.device, n_slots=n_slots,
+                           max_seq_len=min(max_seq_len or model.spec.max_positions, model.spec.max_positions))
+        self.vocab_size = model.spec.vocab_size
+
+    # -- slots -----------------------------------------------------------------
+
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # -- the step ----------------------------------------------------------------
+
+    def check(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+              want: Sequence[Sequence[int]]) -> None:
+        if not slots or len(slots) != len(tokens) or len(want) != len(tokens):
+            raise InvalidArgument(f"a step of {len(slots)} slots, {len(tokens)} token lists and {len(want)} want lists")
+        for b, (toks, w) in enumerate(zip(tokens, want)):
+            if len(toks) == 0:
+                raise InvalidArgument(f"sequence {b} brings no token to the step")
+            for t in toks:
+                if not 0 <= t < self.vocab_size:
+                    raise InvalidArgument(f"token {t} is outside the vocabulary [0, {self.vocab_size})")
+            for i in w:
+                if not 0 <= i < len(toks):
+                    raise InvalidArgument(f"sequence {b}: wanted place {i} is outside its {len(toks)} tokens")
+
+    def build_context(self, slots, tokens, want) -> StepContext:
+        cache = self.cache
+        starts = [cache.length(s) for s in slots]
+        q_lens = [len(t) for t in tokens]
+        n = sum(q_lens)
+        tok_ids, tok_seq, tok_pos, cu, rows = [], [], [], [0], []
+        for b, toks in enumerate(tokens):
+            base = cu[-1]
+            tok_ids += list(toks)
+            tok_seq += [b] * len(toks)
+            tok_pos += list(range(starts[b], starts[b] + len(toks)))
+            rows += [base + i for i in want[b]]
+            cu.append(base + len(toks))
+        tables = [cache.block_table(g, slots) for g in range(len(cache.groups))]
+        flat = tok_ids + tok_seq + tok_pos + list(slots) + cu + rows
+        offsets = [0, n, 2 * n, 3 * n, 3 * n + len(slots), 3 * n + 2 * len(slots) + 1]
+        table_at = []
+        for t in tables:
+            table_at.append(len(flat))
+            for row in t:
+                flat += row
+        host = torch.tensor(flat, dtype=torch.int32).pin_memory() if cache.device.type == "cuda" \
+            else torch.tensor(flat, dtype=torch.int32)
+        dev = host.to(cache.device, non_blocking=True)
+        B = len(slots)
+        views = [dev[offsets[0]:offsets[1]], dev[offsets[1]:offsets[2]], dev[offsets[2]:offsets[3]],
+                 dev[offsets[3]:offsets[4]], dev[offsets[4]:offsets[5]], dev[offsets[5]:offsets[5] + len(rows)]]
+        bts = [dev[a:a + B * len(t[0])].view(B, len(t[0])) for a, t in zip(table_at, tables)]
+        return StepContext(n_tokens=n, n_seqs=B, n_wanted=len(rows), tok_ids=views[0], tok_seq=views[1],
+                           tok_pos=views[2], seq_slots=views[3], cu_seqlens=views[4], logit_rows=views[5],
+                           block_tables=bts, q_lens=q_lens, kv_lens=[s + q for s, q in zip(starts, q_lens)],
+                           is_decode=all(q == 1 for q in q_lens))
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """Feeds ``tokens[b]`` to the sequence in ``slots[b]``.  ``want[b]``
+        lists the places among ``tokens[b]`` whose logits are returned
+        (default: the last).  Returns float32 [n_wanted, vocab] on the device,
+        rows in the order of the sequences and of ``want``; None if nothing is
+        wanted."""
+        if want is None:
+            want = [[len(t) - 1] for t in tokens]
+        slots = [int(s) for s in slots]
+        self.check(slots, tokens, want)
+        self.cache.prepare(slots, [len(t) for t in tokens])
+        ctx = self.build_context(slots, tokens, want)
+        logits = self.model.forward(ctx, self.cache)
+        self.cache.commit(slots, ctx.q_lens)
+        return logits

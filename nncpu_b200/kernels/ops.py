@@ -1,0 +1,164 @@
+"""Python faces of the CUDA kernels: one function per kernel, taking torch
+tensors on the GPU and launching on torch's current stream.
+
+Nothing here computes: every function checks what only Python can see
+(devices, element types, contiguity), then calls the C entry point, which
+checks sizes and either launches or refuses with a message.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..errors import ExtensionError, InvalidArgument
+from . import library
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_vp = ctypes.c_void_p
+
+
+def _code(t: Optional[torch.Tensor]) -> int:
+    if t is None:
+        return 0
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise InvalidArgument(f"kernels take float32 or bfloat16 tensors, not {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return _vp(0)
+    if not t.is_cuda:
+        raise ExtensionError("the kernels run on the GPU: a tensor on the CPU was passed, and there is no CPU path")
+    if not t.is_contiguous():
+        raise InvalidArgument("kernels take contiguous tensors")
+    return _vp(t.data_ptr())
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _call(libname: str, fn: str, *args) -> None:
+    lib = library.load(libname)
+    f = getattr(lib, fn)
+    if f(*args) != 0:
+        raise ExtensionError(lib.last_error().decode())
+
+
+def _i(v) -> ctypes.c_int:
+    return ctypes.c_int(int(v))
+
+
+def _f(v) -> ctypes.c_float:
+    return ctypes.c_float(float(v))
+
+
+def embed(table, ids, out, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale; out is float32 [n, hidden]; ids int32."""
+    n, hidden = out.shape
+    assert out.dtype == torch.float32 and ids.dtype == torch.int32 and ids.numel() >= n
+    _call("generic", "nncpu_embed", _ptr(table), _i(_code(table)), _ptr(ids), _ptr(out), _i(n), _i(hidden),
+          _i(table.shape[0]), _f(scale), _stream())
+
+
+def rmsnorm(x, gamma, eps: float, out, rows=None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * gamma over the last axis."""
+    dim = x.shape[-1]
+    n_rows = out.numel() // dim
+    assert gamma is None or gamma.numel() == dim
+    assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= n_rows)
+    _call("generic", "nncpu_rmsnorm", _ptr(x), _i(_code(x)), _ptr(gamma), _i(_code(gamma)), _ptr(out),
+          _i(_code(out)), _ptr(rows), _i(n_rows), _i(dim), _f(eps), _stream())
+
+
+def linear_simt(x, w, bias, out, accumulate: bool = False) -> None:
+    """out (+)= x . w^T + bias on CUDA cores in 32-bit; any sizes and element types."""
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (m, n)
+    _call("generic", "nncpu_linear_simt", _ptr(x), _i(_code(x)), _ptr(w), _i(_code(w)), _ptr(bias),
+          _i(_code(bias)), _ptr(out), _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(n), _i(accumulate), _stream())
+
+
+def linear_tc_supported(m: int, n: int, k: int) -> bool:
+    return m > 0 and k % 8 == 0
+
+
+def linear_tc(x, w, bias, out, status, accumulate: bool = False) -> None:
+    """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16."""
+    m, k = x.shape
+    n = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert w.shape[1] == k and out.shape == (m, n) and status.dtype == torch.int32
+    _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
+          _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(n), _i(accumulate), _ptr(status), _stream())
+
+
+def rope_table(positions, inv_freq, out, position_scale: float = 1.0) -> None:
+    """out[t, i] = (cos, sin)(positions[t] * position_scale * inv_freq[i]); out float32 [n, half, 2]."""
+    n, half, two = out.shape
+    assert two == 2 and out.dtype == torch.float32 and inv_freq.dtype == torch.float32
+    assert inv_freq.numel() == half and positions.dtype == torch.int32 and positions.numel() >= n
+    _call("generic", "nncpu_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(out), _i(n), _i(half),
+          _f(position_scale), _stream())
+
+
+def qk_norm_rope_append(qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, block_table, k_pages, v_pages,
+                        q_out, n_heads: int, n_kv: int, head_dim: int) -> None:
+    """Per-head norm and rotation of q and k, and the append of k and v to
+    their pages.  ``n_kv`` 0: qkv holds q only and nothing is appended."""
+    n = q_out.shape[0]
+    rot_half = 0 if cos_sin is None else cos_sin.shape[1]
+    assert qkv.shape == (n, (n_heads + 2 * n_kv) * head_dim) and q_out.shape == (n, n_heads * head_dim)
+    assert q_gamma is None or k_gamma is None or q_gamma.dtype == k_gamma.dtype
+    g = q_gamma if q_gamma is not None else k_gamma
+    bt_stride = block_table.shape[1] if block_table is not None else 0
+    _call("generic", "nncpu_qk_norm_rope_append", _ptr(qkv), _i(_code(qkv)), _ptr(q_gamma), _ptr(k_gamma),
+          _i(_code(g)), _f(eps), _ptr(cos_sin), _i(rot_half), _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table),
+          _i(bt_stride), _ptr(k_pages), _ptr(v_pages), _i(_code(k_pages)), _ptr(q_out), _i(_code(q_out)), _i(n),
+          _i(n_heads), _i(n_kv), _i(head_dim), _stream())
+
+
+def attention(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, n_heads: int, n_kv: int, head_dim: int,
+              scale: float, window: int = 0) -> None:
+    """Causal attention of each token over its sequence's pages."""
+    n = q.shape[0]
+    assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape
+    assert k_pages.dtype == v_pages.dtype and block_table.dtype == torch.int32
+    _call("generic", "nncpu_attention", _ptr(q), _i(_code(q)), _ptr(k_pages), _ptr(v_pages), _i(_code(k_pages)),
+          _ptr(block_table), _i(block_table.shape[1]), _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _i(_code(out)),
+          _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _stream())
+
+
+def swiglu(gate_up, out) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    n, inter = out.shape
+    assert gate_up.shape == (n, 2 * inter)
+    _call("generic", "nncpu_swiglu", _ptr(gate_up), _i(_code(gate_up)), _ptr(out), _i(_code(out)), _i(n),
+          _i(inter), _stream())
+
+
+def gather_rows(x, rows, out) -> None:
+    n, dim = out.shape
+    assert x.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32
+    _call("generic", "nncpu_gather_rows", _ptr(x), _ptr(rows), _ptr(out), _i(n), _i(dim), _stream())
+
+
+def argmax(logits, out) -> None:
+    """out[r] = the first largest of logits[r]; logits float32 [n, vocab], out int32 [n]."""
+    n, vocab = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() >= n
+    _call("generic", "nncpu_argmax", _ptr(logits), _ptr(out), _i(n), _i(vocab), _stream())
+
+
+def sample_temperature(logits, uniforms, out, temperature: float) -> None:
+    """One draw per row at ``temperature`` over the whole vocabulary in id
+    order; uniforms float64 [n] in [0, 1)."""
+    n, vocab = logits.shape
+    assert logits.dtype == torch.float32 and uniforms.dtype == torch.float64 and out.dtype == torch.int32
+    _call("generic", "nncpu_sample_temperature", _ptr(logits), _ptr(uniforms), _ptr(out), _i(n), _i(vocab),
+          _f(temperature), _stream())

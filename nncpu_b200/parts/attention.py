@@ -1,0 +1,94 @@
+"""Grouped-query attention over the paged cache: projections (with optional
+biases, added before the per-head norms), optional per-head q/k norm, optional
+position encoding, append of k and v to the entry's pages, causal attention
+over all earlier keys or a window of them, output projection added to the
+residual stream (crates/nncpu/src/model/forward.rs:197-439).
+
+q, k and v projections are stored as one matrix so the input is read once.
+An entry that reads another entry's cache has no k/v projection at all
+(crates/nncpu/src/model/forward.rs:210,240-255).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import KVRequest
+from ..errors import UnsupportedModel
+from ..kernels import ops
+from ..weights.params import ParamSpec
+from . import base
+from .base import Mixer, register_mixer
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    def __init__(self, spec, reads_other_cache: bool = False):
+        s = self.spec = spec
+        self.shared_kv = reads_other_cache
+        if s.n_heads % s.n_kv_heads:
+            raise UnsupportedModel(f"{s.name}: {s.n_heads} heads over {s.n_kv_heads} key/value heads")
+        if s.qk_norm is not None and s.qk_norm.kind != "rmsnorm":
+            raise UnsupportedModel(f"{s.name}: per-head norm of kind {s.qk_norm.kind!r} is not supported")
+        self.q_size = s.n_heads * s.head_dim
+        self.kv_size = 0 if reads_other_cache else s.n_kv_heads * s.head_dim
+        self.position = None if s.position is None else base.build("position", s.position)
+
+    def kv_request(self):
+        s = self.spec
+        return None if self.shared_kv else KVRequest(s.n_kv_heads, s.head_dim, s.window)
+
+    def _proj_names(self):
+        return ["q_proj"] if self.shared_kv else ["q_proj", "k_proj", "v_proj"]
+
+    def params(self):
+        s, p = self.spec, []
+        sizes = {"q_proj": self.q_size, "k_proj": self.kv_size, "v_proj": self.kv_size}
+        for n in self._proj_names():
+            p.append(ParamSpec(f"{s.name}.{n}.weight", (sizes[n], s.hidden_size)))
+            if s.qkv_bias:
+                p.append(ParamSpec(f"{s.name}.{n}.bias", (sizes[n],)))
+        p.append(ParamSpec(f"{s.name}.o_proj.weight", (s.hidden_size, self.q_size)))
+        if s.out_bias_optional:
+            p.append(ParamSpec(f"{s.name}.o_proj.bias", (s.hidden_size,), required=False))
+        if s.qk_norm is not None:
+            p.append(ParamSpec(f"{s.qk_norm.name}.q_norm.weight", (s.head_dim,), init=("one_plus_normal", 0.1)))
+            if not self.shared_kv:
+                p.append(ParamSpec(f"{s.qk_norm.name}.k_norm.weight", (s.head_dim,), init=("one_plus_normal", 0.1)))
+        return p
+
+    def bind(self, tensors, rt):
+        s, self.rt = self.spec, rt
+        names = self._proj_names()
+        ws = [tensors.pop(f"{s.name}.{n}.weight") for n in names]
+        self.w_qkv = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
+        del ws
+        self.b_qkv = None
+        if s.qkv_bias:
+            bs = [tensors.pop(f"{s.name}.{n}.bias") for n in names]
+            self.b_qkv = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0).contiguous()
+        self.w_o = tensors[f"{s.name}.o_proj.weight"]
+        self.b_o = tensors.get(f"{s.name}.o_proj.bias")
+        self.q_gamma = self.k_gamma = None
+        if s.qk_norm is not None:
+            self.q_gamma = tensors[f"{s.qk_norm.name}.q_norm.weight"]
+            self.k_gamma = tensors.get(f"{s.qk_norm.name}.k_norm.weight")
+        if self.position is not None:
+            self.position.bind(tensors, rt)
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
+
+    def forward(self, ctx, x, residual, cache):
+        s, rt = self.spec, self.rt
+        n = x.shape[0]
+        qkv = rt.empty(n, self.q_size + 2 * self.kv_size)
+        rt.linear(x, self.w_qkv, self.b_qkv, qkv)
+        cos_sin = None if self.position is None else self.position.tables(ctx)
+        q = rt.empty(n, self.q_size)
+        ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, s.qk_norm.eps if s.qk_norm else 0.0, cos_sin,
+                                ctx.tok_seq, ctx.tok_pos, cache.block_table, cache.k_pages, cache.v_pages, q,
+                                s.n_heads, 0 if self.shared_kv else s.n_kv_heads, s.head_dim)
+        attn = rt.empty(n, self.q_size)
+        ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
+                      s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
+        rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True)

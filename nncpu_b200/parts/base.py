@@ -1,0 +1,133 @@
+"""The interfaces of the parts a layer is put together from, and the
+registries that map a spec's ``kind`` to its implementation.
+
+A part is built from its spec alone (sizes and constants are the spec's
+fields), lists the tensors it needs, receives them, and then runs on whatever
+step it is given.  No part knows which model it is in.
+
+Adding a part: subclass the interface, decorate the class with the matching
+``register_*("kind")``, and emit a spec with that ``kind`` from a
+configuration class.  Nothing else changes.
+
+Interfaces (``ctx`` is the engine's ``StepContext``; ``x`` is ``[n_tokens,
+hidden]`` in the run's element type; ``residual`` is the float32 residual
+stream ``[n_tokens, hidden]``):
+
+* ``Norm.forward(ctx, residual, rows=None) -> x``
+* ``Mixer.forward(ctx, x, residual, cache) -> None`` adds its output to
+  ``residual``; ``cache`` is the ``EntryCache`` of the schedule entry.  A mixer
+  asks for storage with ``kv_request()`` / ``state_request()``.
+* ``FeedForward.forward(ctx, x, residual) -> None`` adds its output to ``residual``.
+* ``PositionEncoding.tables(ctx)`` gives what its mixers need for the step's
+  positions, computed once per step.
+* ``Block.forward(ctx, residual, cache) -> None`` runs its parts in its arrangement.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..cache import KVRequest, StateRequest
+from ..errors import UnsupportedModel
+from ..weights.params import ParamSpec
+
+
+class Part:
+    """Common life cycle: ``params()`` before loading, ``bind()`` after."""
+
+    def params(self) -> List[ParamSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        """Takes the tensors it listed (absent optional ones are missing from
+        the dict).  ``rt`` is the ``Runtime``: device, element type, kernels."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one step reads, for the bandwidth model."""
+        return 0
+
+
+class Norm(Part):
+    def forward(self, ctx, residual: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def tables(self, ctx):
+        raise NotImplementedError
+
+
+@dataclass
+class EntryCache:
+    """What one schedule entry sees of the cache during a step."""
+    k_pages: Optional[torch.Tensor]      # [n_pages, n_kv_heads, PAGE, head_dim] or None
+    v_pages: Optional[torch.Tensor]
+    block_table: Optional[torch.Tensor]  # int32 [n_seqs, width]: page ids of the step's sequences
+    owns_kv: bool                        # False: the pages belong to another entry; read, do not append
+    state: Optional[torch.Tensor]        # [n_slots, *shape] or None; index with ctx.seq_slots
+
+
+class Mixer(Part):
+    def kv_request(self) -> Optional[KVRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, cache: EntryCache) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def forward(self, ctx, residual: torch.Tensor, cache: EntryCache) -> None:
+        raise NotImplementedError
+
+
+_REGISTRIES: Dict[str, Dict[str, Callable]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {},
+                                               "block": {}}
+
+
+def _register(family: str, kind: str):
+    def deco(cls):
+        _REGISTRIES[family][kind] = cls
+        return cls
+    return deco
+
+
+def register_norm(kind: str):
+    return _register("norm", kind)
+
+
+def register_position(kind: str):
+    return _register("position", kind)
+
+
+def register_mixer(kind: str):
+    return _register("mixer", kind)
+
+
+def register_feed_forward(kind: str):
+    return _register("feed_forward", kind)
+
+
+def register_block(kind: str):
+    return _register("block", kind)
+
+
+def build(family: str, spec, **kwargs):
+    """The part registered for ``spec.kind`` in ``family``, built from ``spec``."""
+    try:
+        cls = _REGISTRIES[family][spec.kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRIES[family])) or "none"
+        raise UnsupportedModel(f"no {family} of kind {spec.kind!r} is registered (registered: {known})") from None
+    return cls(spec, **kwargs)

@@ -1,0 +1,43 @@
+"""What parts need from their surroundings: the device, the run's element
+type, a device status word for kernels with bounded waits, and the choice
+between the tensor-core and the CUDA-core matrix product.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..errors import ExtensionError
+from ..kernels import ops
+
+
+class Runtime:
+    def __init__(self, device, dtype: torch.dtype):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise ExtensionError(f"models run on a CUDA device, not on {self.device}: there is no CPU path")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ExtensionError(f"run element type {dtype} is not supported (bfloat16 or float32)")
+        self.dtype = dtype
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0  # kernels launched through this runtime's parts, for the benchmark's count
+
+    def empty(self, *shape, dtype=None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def linear(self, x, w, bias, out, accumulate: bool = False) -> None:
+        """out (+)= x . w^T + bias.  bfloat16 inputs whose sizes keep TMA's
+        alignment rule go to the tensor cores; everything else, and every
+        float32 product, runs in true 32-bit on CUDA cores."""
+        m, k = x.shape
+        if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and ops.linear_tc_supported(m, w.shape[0], k)):
+            ops.linear_tc(x, w, bias, out, self.status, accumulate)
+        else:
+            ops.linear_simt(x, w, bias, out, accumulate)
+
+    def check_status(self) -> None:
+        """Call after a synchronisation: raises if a kernel's bounded wait ran out."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise ExtensionError(f"a kernel gave up waiting (status {code}); the step's results are not valid")

@@ -1,0 +1,8 @@
+"""Weights: the safetensors container, loading by name, random models."""
+from .params import ParamSpec
+from .safetensors_io import SafetensorsFile, write_safetensors
+from .loader import check_tensors, convert, load_tensors
+from .random_init import draw, random_tensors, write_model_folder
+
+__all__ = ["ParamSpec", "SafetensorsFile", "write_safetensors", "check_tensors", "convert",
+           "load_tensors", "draw", "random_tensors", "write_model_folder"]
