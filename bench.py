@@ -1,0 +1,262 @@
+#!/usr/bin/env python3
+"""Benchmark of the library's flagship step: decoding with the Qwen3-8B layer
+sizes, random weights, bfloat16, on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 sequences whose prompts are 2,048
+tokens long (context length 4,096).  ``value`` is decoded tokens per second,
+timed on the device with CUDA events over exactly K steps after W warm-up
+steps; ``e2e`` is the same workload through ``Session.generate`` with host
+token ids in and out.  The line also carries a prefill measurement (one
+2,048-token prompt), the decode step's memory roofline, decode at batch 1 and
+64, and the SM clocks sampled during the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
+                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, attention_bias=False,
+                max_position_embeddings=40960)
+CONTEXT = 4096
+PROMPT = 2048
+BATCH = 8
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]),
+                    "bf16_tflops": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def flops_prefill(cfg, T: int) -> float:
+    """Multiply-adds times two of one T-token prompt: the layer matrices, causal
+    attention (scores and weighted sum over half the square), one output row."""
+    q = cfg.num_attention_heads * cfg.head_dim
+    kv = cfg.num_key_value_heads * cfg.head_dim
+    h, i = cfg.hidden_size, cfg.intermediate_size
+    per_tok = 2.0 * (h * (q + 2 * kv) + q * h + 3 * h * i)
+    attn = 4.0 * q * (T * (T + 1) / 2.0)
+    return cfg.num_hidden_layers * (per_tok * T + attn) + 2.0 * h * cfg.vocab_size
+
+
+def kv_bytes_per_token(cfg, esize: int = 2) -> int:
+    return 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim * esize
+
+
+def timed_decode(engine, slots, first_tokens, steps: int, warmup: int):
+    """W warm-up decode steps, then exactly K timed ones (greedy, token ids stay
+    on the device).  Returns (milliseconds for K steps, mean kv length)."""
+    import torch
+    toks = engine.decode_run(slots, first_tokens, warmup) if warmup > 0 else None
+    nxt = first_tokens if toks is None else toks[-1]
+    torch.cuda.synchronize()
+    lens0 = [engine.cache.length(s) for s in slots]
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    out = engine.decode_run(slots, nxt, steps)
+    b.record()
+    torch.cuda.synchronize()
+    engine.model.rt.check_status()
+    mean_len = sum(lens0) / len(lens0) + (steps + 1) / 2.0
+    return a.elapsed_time(b), mean_len, out
+
+
+def run_decode_point(model, cfg, batch: int, steps: int, warmup: int, seed: int = 0):
+    import torch
+    from nncpu_b200 import Engine
+    per_seq = (CONTEXT + 63) // 64 * 64
+    engine = Engine(model, max_tokens=per_seq * batch, max_seq_len=CONTEXT)
+    g = torch.Generator().manual_seed(seed)
+    prompts = torch.randint(0, cfg.vocab_size, (batch, PROMPT), generator=g).tolist()
+    slots = [engine.alloc_slot() for _ in range(batch)]
+    # prefill in chunks of sequences to bound activation memory
+    firsts = []
+    from nncpu_b200.kernels import ops
+    for i in range(0, batch, 4):
+        logits = engine.step(slots[i:i + 4], prompts[i:i + 4])
+        ids = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        ops.argmax(logits, ids)
+        firsts += ids.tolist()
+    steps = min(steps, CONTEXT - PROMPT - warmup - 1)
+    ms, mean_len, _ = timed_decode(engine, slots, firsts, steps, warmup)
+    tok_s = batch * steps / (ms / 1e3)
+    bytes_step = model.weight_bytes_per_step() + batch * mean_len * kv_bytes_per_token(cfg)
+    for s in slots:
+        engine.free_slot(s)
+    del engine
+    torch.cuda.empty_cache()
+    return tok_s, ms / steps, bytes_step
+
+
+def run_prefill(model, cfg, reps: int = 3):
+    import torch
+    from nncpu_b200 import Engine
+    engine = Engine(model, max_tokens=PROMPT + 64, max_seq_len=CONTEXT)
+    g = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, cfg.vocab_size, (PROMPT,), generator=g).tolist()
+    best = None
+    for r in range(reps + 1):
+        slot = engine.alloc_slot()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.step([slot], [prompt])
+        b.record()
+        torch.cuda.synchronize()
+        engine.free_slot(slot)
+        if r > 0:
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+    model.rt.check_status()
+    del engine
+    torch.cuda.empty_cache()
+    return best
+
+
+def run_e2e(model, cfg, steps: int):
+    """The same decode workload through the public entry point: host token ids
+    in, host token ids out, every step."""
+    import torch
+    from nncpu_b200 import GenerateParams, SamplerParams, Session, SessionParams
+    session = Session(model, SessionParams(n_ctx=CONTEXT, seed=1, max_batch=BATCH))
+    g = torch.Generator().manual_seed(3)
+    prompts = torch.randint(0, cfg.vocab_size, (BATCH, PROMPT), generator=g).tolist()
+    steps = min(steps, CONTEXT - PROMPT - 1)
+    res = session.generate(prompts, GenerateParams(max_tokens=steps, sampler=SamplerParams.greedy()),
+                           stop_token_ids=())
+    n = sum(r.n_generated for r in res)
+    decode_s = res[0].decode
+    return {"value": n / decode_s if decode_s > 0 else None, "unit": "tokens/s",
+            "h2d_bytes_per_step": session.engine.h2d_bytes_last_step, "d2h_bytes_per_step": 4 * BATCH,
+            "prefill_s": res[0].prefill, "generated": n}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "ZacWalk/nncpu is a Rust crate with no Python package and no Rust toolchain is installed: "
+                          "pip cannot install it offline and it has no GPU path"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this library is single-GPU by design, --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from nncpu_b200.config import config_from_dict
+    from nncpu_b200 import Model
+    from nncpu_b200.kernels import ops
+
+    d = dict(QWEN3_8B)
+    full_layers = d["num_hidden_layers"]
+    if args.layers:
+        d["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(d)
+    pk = peaks()
+    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+
+    prefill_ms = run_prefill(model, cfg)
+    pf_flops = flops_prefill(cfg, PROMPT)
+    launches0 = ops.launch_count()
+    with ClockSampler() as clocks:
+        tok_s, ms_step, bytes_step = run_decode_point(model, cfg, BATCH, args.steps, args.warmup)
+    launches = ops.launch_count() - launches0
+    points = {}
+    if not args.skip_points:
+        points["decode_b1"] = run_decode_point(model, cfg, 1, min(args.steps, 256), args.warmup)[0]
+        points["decode_b64"] = run_decode_point(model, cfg, 64, min(args.steps, 128), args.warmup)[0]
+    e2e = run_e2e(model, cfg, min(args.steps, 256))
+    achieved = bytes_step / (ms_step / 1e3) / 1e9
+    line = {
+        "metric": "decode tokens/s, Qwen3-8B sizes, bf16, batch 8, 2048-token prompts, context 4096",
+        "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": min(args.steps, CONTEXT - PROMPT - args.warmup - 1),
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B sizes", "layers": cfg.num_hidden_layers, "layers_of_config": full_layers,
+                   "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
+                   "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": pk["source"]},
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "prefill": {"value": PROMPT / (prefill_ms / 1e3), "tokens": PROMPT, "ms": prefill_ms,
+                    "frac": pf_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -9,8 +9,11 @@ loop, sampling, and hand-written sm_100a kernels underneath.
 from .errors import (BadFormat, Cancelled, ContextFull, ExtensionError, InvalidArgument, NncpuError, OutOfMemory,
                      UnsupportedModel)
 from .engine import Engine, Model
+from .sampling import GenerateParams, GenerateResult, SamplerParams, StopReason
+from .session import CancelHandle, Piece, Session, SessionParams
 
 __version__ = "0.1.0"
 
 __all__ = ["BadFormat", "Cancelled", "ContextFull", "ExtensionError", "InvalidArgument", "NncpuError",
-           "OutOfMemory", "UnsupportedModel", "Engine", "Model", "__version__"]
+           "OutOfMemory", "UnsupportedModel", "Engine", "Model", "GenerateParams", "GenerateResult", "SamplerParams",
+           "StopReason", "CancelHandle", "Piece", "Session", "SessionParams", "__version__"]

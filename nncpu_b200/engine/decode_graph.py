@@ -1,0 +1,170 @@
+"""Decode steps as CUDA graphs.
+
+A decode step is launch-bound when run kernel by kernel: a few hundred small
+launches per token.  For every batch size (rounded up to a power of two) the
+engine captures the step once over static buffers and replays it afterwards;
+per step the host only refreshes a small block of int32 metadata (positions,
+page tables) and copies it to the device.
+
+Rows beyond the live sequences are padding: their sequence index is -1, so no
+kernel writes the cache for them and their outputs are zeros.
+"""
+from __future__ import annotations
+
+import gc
+import weakref
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import pages_for
+from ..kernels import ops
+from .step import StepContext
+
+_RING = 4  # pinned host copies of the metadata in flight
+
+
+def bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class DecodeGraph:
+    """Static buffers and the captured step for one padded batch size."""
+
+    def __init__(self, engine, size: int):
+        self._engine, self.size = weakref.ref(engine), size  # no cycle: graphs die with their engine
+        cache = engine.cache
+        dev = cache.device
+        self.width = pages_for(cache.max_seq_len)
+        n_groups = len(cache.groups)
+        B = size
+        # layout of the metadata block (int32): tok_seq, tok_pos, seq_slots, cu_seqlens, logit_rows, page tables
+        self.o_seq, self.o_pos, self.o_slot, self.o_cu = 0, B, 2 * B, 3 * B
+        self.o_rows = 4 * B + 1
+        self.o_tables = [5 * B + 1 + g * B * self.width for g in range(n_groups)]
+        self.n_meta = 5 * B + 1 + n_groups * B * self.width
+        self.meta = torch.zeros(self.n_meta, dtype=torch.int32, device=dev)
+        self.tok_ids = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.next_ids = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.host = [torch.zeros(self.n_meta, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.host_np = [h.numpy() for h in self.host]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * _RING
+        self.turn = 0
+        self.tok_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        m = self.meta
+        self.ctx = StepContext(
+            n_tokens=B, n_seqs=B, n_wanted=B, tok_ids=self.tok_ids, tok_seq=m[self.o_seq:self.o_seq + B],
+            tok_pos=m[self.o_pos:self.o_pos + B], seq_slots=m[self.o_slot:self.o_slot + B],
+            cu_seqlens=m[self.o_cu:self.o_cu + B + 1], logit_rows=m[self.o_rows:self.o_rows + B],
+            block_tables=[m[o:o + B * self.width].view(B, self.width) for o in self.o_tables],
+            q_lens=[1] * B, kv_lens=[0] * B, is_decode=True)
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.n_kernels = 0
+        self.slots: Optional[tuple] = None
+        self.pages_seen: List[List[int]] = []
+        self.h2d_bytes = 0
+
+    @property
+    def engine(self):
+        return self._engine()
+
+    def _fill(self, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> None:
+        """Writes this step's metadata into the next pinned copy and sends it."""
+        cache, B, n = self.engine.cache, self.size, len(slots)
+        i = self.turn = (self.turn + 1) % _RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        a = self.host_np[i]
+        prev = self.host_np[(i - 1) % _RING]
+        same = self.slots == tuple(slots)
+        if same:
+            a[:] = prev
+        else:
+            a[:] = -1
+            a[self.o_seq:self.o_seq + n] = np.arange(n)
+            a[self.o_pos:self.o_pos + B] = 0
+            a[self.o_slot:self.o_slot + n] = slots
+            a[self.o_slot + n:self.o_slot + B] = 0
+            a[self.o_cu:self.o_cu + B + 1] = np.arange(B + 1)
+            a[self.o_rows:self.o_rows + n] = np.arange(n)
+            self.slots = tuple(slots)
+            self.pages_seen = [[0] * n for _ in cache.groups]
+        a[self.o_pos:self.o_pos + n] = [cache.lengths[s] for s in slots]
+        for g, group in enumerate(cache.groups):
+            seen = self.pages_seen[g]
+            windowed = group.request.window > 0
+            for b, s in enumerate(slots):
+                table = group.tables[s]
+                if windowed or len(table) != seen[b]:
+                    o = self.o_tables[g] + b * self.width
+                    a[o:o + len(table)] = table
+                    seen[b] = len(table)
+        self.meta.copy_(self.host[i], non_blocking=True)
+        self.h2d_bytes = self.n_meta * 4
+        if tokens is not None:
+            th = self.tok_host[i]
+            th[:n] = torch.as_tensor(tokens, dtype=torch.int32)
+            th[n:] = 0
+            self.tok_ids.copy_(th, non_blocking=True)
+            self.h2d_bytes += B * 4
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+    def _forward(self) -> None:
+        self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
+        ops.argmax(self.logits, self.next_ids)
+
+    def run(self, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> torch.Tensor:
+        """One decode step for ``slots``.  ``tokens`` None: the step's tokens
+        are the previous step's greedy choices, which never left the device.
+        Returns float32 logits [len(slots), vocab], valid until the next step."""
+        self.ctx.memo.clear()
+        self._fill(slots, tokens)
+        if tokens is None:
+            self.tok_ids.copy_(self.next_ids, non_blocking=True)
+        if self.graph is None:
+            # the first step of this size runs kernel by kernel, then the same work is captured
+            self._forward()
+            before = ops.launch_count()
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            self.ctx.memo.clear()
+            # Nothing may free device memory or destroy another graph while the stream captures:
+            # collect garbage now and keep the collector off until the capture has ended.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    self._forward()
+            finally:
+                if gc_was_on:
+                    gc.enable()
+            self.n_kernels = ops.launch_count() - before
+            ops.add_launches(-self.n_kernels)  # capturing launches nothing
+            self.graph = g
+            g.replay()  # the captured buffers now hold this step's result
+            ops.add_launches(self.n_kernels)
+        else:
+            self.graph.replay()
+            ops.add_launches(self.n_kernels)
+        return self.logits[:len(slots)]
+
+
+class DecodeGraphs:
+    def __init__(self, engine):
+        self._engine = weakref.ref(engine)
+        self.by_size: Dict[int, DecodeGraph] = {}
+
+    def get(self, n: int) -> DecodeGraph:
+        size = bucket(n)
+        g = self.by_size.get(size)
+        if g is None:
+            g = self.by_size[size] = DecodeGraph(self._engine(), size)
+        return g

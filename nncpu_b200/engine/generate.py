@@ -1,0 +1,127 @@
+"""The generation loop: batches of prompts of unequal lengths, one prefill
+step, then one token per live sequence and step until every sequence stopped.
+
+The decisions per sampled token are the reference's, in its order
+(crates/nncpu/src/session/engine.rs:476-506): a stop token ends the sequence
+and is neither counted nor streamed; otherwise the token is counted and
+streamed; the callback may stop the sequence; a full context stops it; then
+``max_tokens``.  A cancel is seen before each sampling round
+(crates/nncpu/src/session/engine.rs:657-660).  The last generated token is
+never run through the model (crates/nncpu/src/session/engine.rs:665-667).
+
+A sequence that stops leaves the batch: later steps carry only the live ones,
+and its slot and pages go back to the cache at once.  Requests beyond
+``max_batch`` wait for the next batch; batches run one after another and never
+take on new members.
+
+The loop talks to an engine through ``alloc_slot``, ``free_slot``, ``step``
+and ``max_seq_len`` only, and to a chooser through ``choose(logits, indices)``,
+so its decisions can be tested with scripted stand-ins for both.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, List, Optional, Sequence
+
+from ..cache import PAGE, pages_for
+from ..errors import ContextFull, InvalidArgument
+from ..sampling.params import GenerateParams, GenerateResult, StopReason
+
+
+def plan_batches(prompt_lens: Sequence[int], max_new: Sequence[int], max_batch: int, n_pages: int) -> List[List[int]]:
+    """Cuts request indices 0..n-1, in order, into batches of at most
+    ``max_batch`` whose prompts plus room to generate fit ``n_pages`` pages."""
+    batches, cur, used = [], [], 0
+    for i, (p, g) in enumerate(zip(prompt_lens, max_new)):
+        need = pages_for(p + g)
+        if need > n_pages:
+            raise ContextFull(f"request {i}: {p} prompt tokens and room for {g} more need {need} cache pages "
+                              f"of {PAGE} tokens, the cache has {n_pages}")
+        if cur and (len(cur) >= max_batch or used + need > n_pages):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def generate(engine, chooser, prompts: Sequence[Sequence[int]], params: GenerateParams,
+             stop_token_ids: Sequence[int] = (), on_token: Optional[Callable[[int, int], bool]] = None,
+             cancelled: Callable[[], bool] = lambda: False, max_batch: int = 64,
+             n_ctx: Optional[int] = None, n_pages: Optional[int] = None) -> List[GenerateResult]:
+    """Generates a continuation for every prompt.  ``chooser.choose(logits,
+    indices)`` picks one token per logits row; ``on_token(index, token)`` is
+    called for every generated token and may return False to stop that
+    sequence.  Results come in the order of the prompts."""
+    n_ctx = n_ctx or engine.max_seq_len
+    stops = frozenset(int(t) for t in stop_token_ids)
+    if not prompts:
+        return []
+    for i, p in enumerate(prompts):
+        if len(p) == 0:
+            raise InvalidArgument(f"prompt {i} is empty: there is nothing to continue")
+        # the prompt plus at least one generated token must fit (crates/nncpu/src/session/engine.rs:605-615)
+        if len(p) + 1 > n_ctx:
+            raise ContextFull(f"prompt {i} of {len(p)} tokens does not fit the {n_ctx}-token context")
+    room = [min(n_ctx - len(p), params.max_tokens) if params.max_tokens > 0 else n_ctx - len(p) for p in prompts]
+    batches = plan_batches([len(p) for p in prompts], room, max_batch,
+                           n_pages if n_pages is not None else engine.n_pages)
+    results: List[Optional[GenerateResult]] = [None] * len(prompts)
+    for batch in batches:
+        _run_batch(engine, chooser, [(i, list(prompts[i])) for i in batch], params, stops, on_token, cancelled,
+                   n_ctx, results)
+    return results  # type: ignore[return-value]
+
+
+def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_ctx, results) -> None:
+    live = []  # [index, slot, tokens so far (prompt + generated), result]
+    try:
+        for idx, prompt in members:
+            live.append([idx, engine.alloc_slot(), prompt, GenerateResult(n_prompt=len(prompt))])
+        t0 = time.perf_counter()
+        logits = engine.step([s for _, s, _, _ in live], [p for _, _, p, _ in live])
+        done_results = [r for _, _, _, r in live]
+        prefill = None
+        t1 = t0
+        while live:
+            if cancelled():
+                for _, _, _, r in live:
+                    r.stop = StopReason.CANCELLED
+                break
+            chosen = chooser.choose(logits, [idx for idx, _, _, _ in live])
+            if prefill is None:  # the first choice waits for the prompt step to finish
+                t1 = time.perf_counter()
+                prefill = t1 - t0
+            still = []
+            for (idx, slot, toks, r), tok in zip(live, chosen):
+                tok = int(tok)
+                toks.append(tok)
+                if tok in stops:
+                    r.stop = StopReason.END_OF_TURN
+                else:
+                    r.n_generated += 1
+                    r.tokens.append(tok)
+                    if on_token is not None and on_token(idx, tok) is False:
+                        r.stop = StopReason.CALLBACK
+                    elif len(toks) >= n_ctx:
+                        r.stop = StopReason.CONTEXT_FULL
+                    elif params.max_tokens > 0 and r.n_generated >= params.max_tokens:
+                        r.stop = StopReason.MAX_TOKENS
+                    else:
+                        still.append([idx, slot, toks, r])
+                        continue
+                engine.free_slot(slot)
+            live = still
+            if live:
+                logits = engine.step([s for _, s, _, _ in live], [[t[-1]] for _, _, t, _ in live])
+        t2 = time.perf_counter()
+        for r in done_results:
+            r.prefill = prefill if prefill is not None else t2 - t0
+            r.decode = t2 - t1
+        for (idx, _), r in zip(members, done_results):
+            results[idx] = r
+    finally:
+        for _, slot, _, _ in live:
+            engine.free_slot(slot)

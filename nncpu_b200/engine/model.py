@@ -19,7 +19,7 @@ from ..config import ModelSpec, load_config
 from ..errors import BadFormat, InvalidArgument
 from ..kernels import ops
 from ..parts import EntryCache, Runtime, build
-from ..weights import ParamSpec, load_tensors
+from ..weights import ParamSpec, load_tensors, random_tensors_on_device
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -72,7 +72,7 @@ class Model:
         self.rt = rt
         self.blocks = build_blocks(spec)
         self.final_norm = build("norm", spec.output.norm)
-        tensors = dict(tensors)
+        # `tensors` is consumed: parts take what they fuse out of it, so that no second copy stays alive
         self.embed_table = tensors[f"{spec.embedding.name}.weight"]
         self.lm_head = self.embed_table if spec.output.tied else tensors[f"{spec.output.name}.weight"]
         for block in self.blocks:
@@ -90,6 +90,14 @@ class Model:
         rt = Runtime(device, dt)
         tensors = load_tensors(folder, parameter_list(config.model_spec()), dt, rt.device, progress)
         return cls(config, tensors, rt)
+
+    @classmethod
+    def random(cls, config, seed: int, dtype="bfloat16", device="cuda:0") -> "Model":
+        """A model of ``config`` with random weights made on the device (no
+        files).  ``write_model_folder`` is the mode that writes a folder."""
+        dt = resolve_dtype(dtype)
+        rt = Runtime(device, dt)
+        return cls(config, random_tensors_on_device(parameter_list(config.model_spec()), seed, dt, rt.device), rt)
 
     # -- storage the schedule asks for ------------------------------------------
 

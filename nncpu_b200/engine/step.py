@@ -50,13 +50,24 @@ class Engine:
     """A model with its cache.  ``step`` is the only way tokens reach the model."""
 
     def __init__(self, model, max_tokens: int, n_slots: Optional[int] = None, max_seq_len: Optional[int] = None,
-                 kv_dtype: Optional[torch.dtype] = None):
+                 kv_dtype: Optional[torch.dtype] = None, use_graphs: bool = True):
+        from .decode_graph import DecodeGraphs
         self.model = model
+        self.graphs = DecodeGraphs(self) if use_graphs else None
+        self.h2d_bytes_last_step = 0
         requests, cache_of = model.cache_requests()
         rt = model.rt
         self.cache = Cache(requests, cache_of, max_tokens, kv_dtype or rt.dtype, rt.device, n_slots=n_slots,
                            max_seq_len=min(max_seq_len or model.spec.max_positions, model.spec.max_positions))
         self.vocab_size = model.spec.vocab_size
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.cache.max_seq_len
+
+    @property
+    def n_pages(self) -> int:
+        return self.cache.n_pages
 
     # -- slots -----------------------------------------------------------------
 
@@ -106,6 +117,7 @@ class Engine:
         host = torch.tensor(flat, dtype=torch.int32).pin_memory() if cache.device.type == "cuda" \
             else torch.tensor(flat, dtype=torch.int32)
         dev = host.to(cache.device, non_blocking=True)
+        self.h2d_bytes_last_step = host.numel() * 4
         B = len(slots)
         views = [dev[offsets[0]:offsets[1]], dev[offsets[1]:offsets[2]], dev[offsets[2]:offsets[3]],
                  dev[offsets[3]:offsets[4]], dev[offsets[4]:offsets[5]], dev[offsets[5]:offsets[5] + len(rows)]]
@@ -127,7 +139,40 @@ class Engine:
         slots = [int(s) for s in slots]
         self.check(slots, tokens, want)
         self.cache.prepare(slots, [len(t) for t in tokens])
+        if self.graphs is not None and all(len(t) == 1 for t in tokens) and all(list(w) == [0] for w in want):
+            g = self.graphs.get(len(slots))
+            logits = g.run(slots, [t[0] for t in tokens])
+            self.h2d_bytes_last_step = g.h2d_bytes
+            self.cache.commit(slots, [1] * len(slots))
+            return logits
         ctx = self.build_context(slots, tokens, want)
         logits = self.model.forward(ctx, self.cache)
         self.cache.commit(slots, ctx.q_lens)
         return logits
+
+    def decode_run(self, slots: Sequence[int], first_tokens, n_steps: int) -> torch.Tensor:
+        """``n_steps`` greedy decode steps for the sequences in ``slots``
+        without a stop check: the first step feeds ``first_tokens`` (a list, or
+        an int32 device tensor), every later step feeds the previous step's
+        choice, which stays on the device.  Returns the chosen tokens, int32
+        [n_steps, len(slots)] on the device."""
+        slots = [int(s) for s in slots]
+        n = len(slots)
+        out = torch.empty((n_steps, n), dtype=torch.int32, device=self.cache.device)
+        from .decode_graph import DecodeGraphs
+        graphs = self.graphs if self.graphs is not None else DecodeGraphs(self)
+        self.graphs = graphs
+        g = graphs.get(n)
+        for i in range(n_steps):
+            self.cache.prepare(slots, [1] * n)
+            if i == 0:
+                if isinstance(first_tokens, torch.Tensor):
+                    g.next_ids[:n].copy_(first_tokens.to(torch.int32))
+                    g.run(slots, None)
+                else:
+                    g.run(slots, [int(t) for t in first_tokens])
+            else:
+                g.run(slots, None)
+            self.cache.commit(slots, [1] * n)
+            out[i].copy_(g.next_ids[:n])
+        return out

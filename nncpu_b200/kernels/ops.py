@@ -42,11 +42,27 @@ def _stream():
     return _vp(torch.cuda.current_stream().cuda_stream)
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far in this process, graph replays included."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    """A CUDA graph that holds ``n`` of this library's kernels was replayed."""
+    global _launches
+    _launches += n
+
+
 def _call(libname: str, fn: str, *args) -> None:
+    global _launches
     lib = library.load(libname)
     f = getattr(lib, fn)
     if f(*args) != 0:
         raise ExtensionError(lib.last_error().decode())
+    _launches += 1
 
 
 def _i(v) -> ctypes.c_int:

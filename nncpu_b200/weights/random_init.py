@@ -47,6 +47,27 @@ def random_tensors(params: Iterable[ParamSpec], seed: int, store_dtype: torch.dt
     return out
 
 
+def random_tensors_on_device(params: Iterable[ParamSpec], seed: int, dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+    """The same distributions drawn on the GPU, for models too large to be
+    worth a round trip through a file (benchmarks at 8B sizes and above).  The
+    generator is the device's, keyed by (seed, tensor name); the values are
+    not those of ``draw``.  Two-axis tensors are made in ``dtype``, one-axis
+    tensors in float32 when ``dtype`` is float32 and in ``dtype`` otherwise."""
+    out = {}
+    gen = torch.Generator(device=device)
+    for p in params:
+        if not p.required:
+            continue
+        gen.manual_seed((int(seed) * 1000003 + zlib.crc32(p.name.encode())) & 0x7FFFFFFFFFFFFFFF)
+        kind, std = p.init
+        t = torch.empty(p.shape, dtype=dtype, device=device)
+        t.normal_(0.0, std, generator=gen)
+        if kind == "one_plus_normal":
+            t += 1.0
+        out[p.name] = t
+    return out
+
+
 def write_model_folder(folder, config, seed: int, store_dtype: torch.dtype = torch.bfloat16,
                        vector_dtype: torch.dtype = None, include_optional: bool = False) -> Path:
     """Writes ``config.json`` and ``model.safetensors`` for ``config`` (a
