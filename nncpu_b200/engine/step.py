@@ -36,6 +36,7 @@ class StepContext:
     q_lens: List[int]           # host: tokens per sequence in this step
     kv_lens: List[int]          # host: length of each sequence after this step
     is_decode: bool             # every sequence brings exactly one token
+    h2d_bytes: int = 0          # bytes of metadata copied to the device for this step
     memo: Dict = field(default_factory=dict)  # per-step results shared between layers
 
     def entry_cache(self, cache: Cache, entry: int) -> EntryCache:
@@ -44,6 +45,42 @@ class StepContext:
             return EntryCache(None, None, None, False, cache.state(entry))
         k, v = cache.kv(entry)
         return EntryCache(k, v, self.block_tables[g], cache.owns_kv(entry), cache.state(entry))
+
+
+def make_context(cache: Cache, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+                 want: Sequence[Sequence[int]]) -> StepContext:
+    """The step's metadata as one block of int32, copied to the device once.
+    Call after ``cache.prepare``: the page tables must already cover the new tokens."""
+    starts = [cache.length(s) for s in slots]
+    q_lens = [len(t) for t in tokens]
+    n = sum(q_lens)
+    tok_ids, tok_seq, tok_pos, cu, rows = [], [], [], [0], []
+    for b, toks in enumerate(tokens):
+        base = cu[-1]
+        tok_ids += list(toks)
+        tok_seq += [b] * len(toks)
+        tok_pos += list(range(starts[b], starts[b] + len(toks)))
+        rows += [base + i for i in want[b]]
+        cu.append(base + len(toks))
+    tables = [cache.block_table(g, slots) for g in range(len(cache.groups))]
+    flat = tok_ids + tok_seq + tok_pos + list(slots) + cu + rows
+    B = len(slots)
+    offsets = [0, n, 2 * n, 3 * n, 3 * n + B, 3 * n + 2 * B + 1]
+    table_at = []
+    for t in tables:
+        table_at.append(len(flat))
+        for row in t:
+            flat += row
+    host = torch.tensor(flat, dtype=torch.int32)
+    if cache.device.type == "cuda":
+        host = host.pin_memory()
+    dev = host.to(cache.device, non_blocking=True)
+    views = [dev[offsets[i]:offsets[i + 1]] for i in range(5)] + [dev[offsets[5]:offsets[5] + len(rows)]]
+    bts = [dev[a:a + B * len(t[0])].view(B, len(t[0])) for a, t in zip(table_at, tables)]
+    return StepContext(n_tokens=n, n_seqs=B, n_wanted=len(rows), tok_ids=views[0], tok_seq=views[1],
+                       tok_pos=views[2], seq_slots=views[3], cu_seqlens=views[4], logit_rows=views[5],
+                       block_tables=bts, q_lens=q_lens, kv_lens=[s + q for s, q in zip(starts, q_lens)],
+                       is_decode=all(q == 1 for q in q_lens), h2d_bytes=host.numel() * 4)
 
 
 class Engine:
@@ -94,38 +131,9 @@ class Engine:
                     raise InvalidArgument(f"sequence {b}: wanted place {i} is outside its {len(toks)} tokens")
 
     def build_context(self, slots, tokens, want) -> StepContext:
-        cache = self.cache
-        starts = [cache.length(s) for s in slots]
-        q_lens = [len(t) for t in tokens]
-        n = sum(q_lens)
-        tok_ids, tok_seq, tok_pos, cu, rows = [], [], [], [0], []
-        for b, toks in enumerate(tokens):
-            base = cu[-1]
-            tok_ids += list(toks)
-            tok_seq += [b] * len(toks)
-            tok_pos += list(range(starts[b], starts[b] + len(toks)))
-            rows += [base + i for i in want[b]]
-            cu.append(base + len(toks))
-        tables = [cache.block_table(g, slots) for g in range(len(cache.groups))]
-        flat = tok_ids + tok_seq + tok_pos + list(slots) + cu + rows
-        offsets = [0, n, 2 * n, 3 * n, 3 * n + len(slots), 3 * n + 2 * len(slots) + 1]
-        table_at = []
-        for t in tables:
-            table_at.append(len(flat))
-            for row in t:
-                flat += row
-        host = torch.tensor(flat, dtype=torch.int32).pin_memory() if cache.device.type == "cuda" \
-            else torch.tensor(flat, dtype=torch.int32)
-        dev = host.to(cache.device, non_blocking=True)
-        self.h2d_bytes_last_step = host.numel() * 4
-        B = len(slots)
-        views = [dev[offsets[0]:offsets[1]], dev[offsets[1]:offsets[2]], dev[offsets[2]:offsets[3]],
-                 dev[offsets[3]:offsets[4]], dev[offsets[4]:offsets[5]], dev[offsets[5]:offsets[5] + len(rows)]]
-        bts = [dev[a:a + B * len(t[0])].view(B, len(t[0])) for a, t in zip(table_at, tables)]
-        return StepContext(n_tokens=n, n_seqs=B, n_wanted=len(rows), tok_ids=views[0], tok_seq=views[1],
-                           tok_pos=views[2], seq_slots=views[3], cu_seqlens=views[4], logit_rows=views[5],
-                           block_tables=bts, q_lens=q_lens, kv_lens=[s + q for s, q in zip(starts, q_lens)],
-                           is_decode=all(q == 1 for q in q_lens))
+        ctx = make_context(self.cache, slots, tokens, want)
+        self.h2d_bytes_last_step = ctx.h2d_bytes
+        return ctx
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
