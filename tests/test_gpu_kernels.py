@@ -1,0 +1,317 @@
+"""Each CUDA kernel alone against a plain float32/float64 reference of the same
+operation, at sizes other than the models' (odd widths, tails, many pages)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+from gpu_util import DEV, check, rel_err, scatter_pages
+from nncpu_b200.cache import PAGE
+from nncpu_b200.errors import ExtensionError
+
+pytestmark = pytest.mark.gpu
+DT = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from nncpu_b200.kernels import ops
+    return ops
+
+
+def test_embed(ops):
+    table = torch.randn(37, 50, device=DEV)
+    ids = torch.tensor([3, 36, -1, 0, 3], dtype=torch.int32, device=DEV)
+    for t in (table, table.bfloat16()):
+        out = torch.empty(5, 50, device=DEV)
+        ops.embed(t, ids, out, 2.0)
+        want = t.float()[ids.clamp_min(0).long()] * 2.0
+        want[2] = 0
+        assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("dim", [1, 7, 80, 129, 4096])
+@pytest.mark.parametrize("dt", DT)
+def test_rmsnorm(ops, dim, dt):
+    g = torch.Generator().manual_seed(dim)
+    x = (torch.randn(9, dim, generator=g) * 3).to(DEV)
+    gamma = (1 + 0.1 * torch.randn(dim, generator=g)).to(dt).to(DEV)
+    want = P.rmsnorm(x.cpu().numpy(), gamma.float().cpu().numpy(), 1e-5)
+    out = torch.empty(9, dim, dtype=dt, device=DEV)
+    ops.rmsnorm(x, gamma, 1e-5, out)
+    check(out, want, 1e-5 if dt == torch.float32 else 8e-3, "rmsnorm")
+    rows = torch.tensor([8, -1, 0, 8], dtype=torch.int32, device=DEV)
+    out = torch.empty(4, dim, dtype=torch.float32, device=DEV)
+    ops.rmsnorm(x, gamma, 1e-5, out, rows)
+    w = np.stack([want[8], np.zeros(dim, np.float32), want[0], want[8]])
+    check(out, w, 1e-5, "rmsnorm of gathered rows")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (5, 307, 81), (17, 64, 409), (70, 130, 33), (300, 31, 200)])
+def test_linear_simt(ops, m, n, k):
+    g = torch.Generator().manual_seed(m * n + k)
+    x, w, b = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g) * 0.1, torch.randn(n, generator=g)
+    want = (x.double() @ w.double().T + b.double()).float()
+    out = torch.empty(m, n, device=DEV)
+    ops.linear_simt(x.to(DEV), w.to(DEV), b.to(DEV), out)
+    check(out, want, 2e-6, "linear")
+    acc = torch.ones(m, n, device=DEV)
+    ops.linear_simt(x.to(DEV), w.to(DEV), None, acc, accumulate=True)
+    check(acc, want - b + 1, 2e-6, "linear accumulate")
+    # mixed element types: bfloat16 activations, float32 weights, bfloat16 out
+    xb = x.bfloat16()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.linear_simt(xb.to(DEV), w.to(DEV), b.bfloat16().to(DEV), out)
+    check(out, xb.float() @ w.T + b.bfloat16().float(), 1e-2, "linear mixed")
+
+
+def test_linear_simt_row_does_not_depend_on_the_batch(ops):
+    x, w = torch.randn(70, 200, device=DEV), torch.randn(90, 200, device=DEV)
+    whole = torch.empty(70, 90, device=DEV)
+    ops.linear_simt(x, w, None, whole)
+    for rows in (slice(0, 1), slice(13, 14), slice(20, 37)):
+        part = torch.empty(rows.stop - rows.start, 90, device=DEV)
+        ops.linear_simt(x[rows].contiguous(), w, None, part)
+        assert torch.equal(part, whole[rows])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 307, 80), (16, 1000, 512), (17, 130, 72), (64, 2048, 1024),
+                                   (65, 100, 200), (128, 128, 128), (129, 384, 96), (256, 300, 264),
+                                   (257, 512, 128), (700, 307, 80), (1000, 1111, 1096)])
+def test_linear_tensor_core(ops, m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.1).bfloat16().to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = (x.double() @ w.double().T).float()
+    out = torch.full((m, n), 9.0, device=DEV)
+    ops.linear_tc(x, w, b, out, status)
+    check(out, want + b, 1e-5, "tensor-core linear, float32 out")
+    outb = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.linear_tc(x, w, b.bfloat16(), outb, status)
+    check(outb, want + b.bfloat16().float(), 8e-3, "tensor-core linear, bfloat16 out")
+    acc = torch.full((m, n), 0.5, device=DEV)
+    ops.linear_tc(x, w, None, acc, status, accumulate=True)
+    check(acc, want + 0.5, 1e-5, "tensor-core linear, accumulate")
+    assert int(status.item()) == 0
+
+
+def test_linear_tensor_core_refuses_unaligned(ops):
+    x = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    assert not ops.linear_tc_supported(4, 8, 20)
+    with pytest.raises(ExtensionError, match="multiples of 8"):
+        ops.linear_tc(x, w, None, torch.empty(4, 8, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
+
+
+def test_rope_table(ops):
+    pos = torch.tensor([0, 1, 5, 1000, 40959], dtype=torch.int32, device=DEV)
+    for theta, half in ((1e4, 8), (1e6, 64), (5e5, 24)):
+        inv = torch.pow(torch.tensor(theta, dtype=torch.float64),
+                        -2.0 * torch.arange(half, dtype=torch.float64) / (2 * half)).float()
+        out = torch.empty(5, half, 2, device=DEV)
+        ops.rope_table(pos, inv.to(DEV), out)
+        ang = (pos.cpu().float()[:, None] * inv[None, :]).double()
+        assert (out[..., 0].cpu() - torch.cos(ang).float()).abs().max() < 2e-6
+        assert (out[..., 1].cpu() - torch.sin(ang).float()).abs().max() < 2e-6
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (5, 1, 48, 48), (3, 3, 80, 32), (8, 2, 128, 128)])
+@pytest.mark.parametrize("dt", DT)
+def test_qk_norm_rope_append(ops, nh, nkv, hd, rot, dt):
+    g = torch.Generator().manual_seed(nh * hd)
+    lens, new = [70, 3], [5, 3]       # sequence 0 already holds 65 tokens, sequence 1 starts
+    n = sum(new)
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd, generator=g)
+    qg, kg = (1 + 0.1 * torch.randn(hd, generator=g) for _ in range(2))
+    tok_seq = torch.tensor([0] * 5 + [1] * 3, dtype=torch.int32)
+    tok_pos = torch.tensor(list(range(65, 70)) + [0, 1, 2], dtype=torch.int32)
+    table = torch.tensor([[4, 1], [2, -1]], dtype=torch.int32)
+    theta = 1e4
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)
+    cs = torch.empty(n, rot // 2, 2, device=DEV)
+    ops.rope_table(tok_pos.to(DEV), inv.float().to(DEV), cs)
+    kp = torch.full((6, nkv, PAGE, hd), 7.0, dtype=dt, device=DEV)
+    vp = torch.full((6, nkv, PAGE, hd), 7.0, dtype=dt, device=DEV)
+    q_out = torch.empty(n, nh * hd, dtype=dt, device=DEV)
+    ops.qk_norm_rope_append(qkv.to(dt).to(DEV), qg.to(DEV), kg.to(DEV), 1e-6, cs, tok_seq.to(DEV), tok_pos.to(DEV),
+                            table.to(DEV), kp, vp, q_out, nh, nkv, hd)
+    x = qkv.to(dt).float().numpy()
+    q = x[:, :nh * hd].reshape(n, nh, hd)
+    k = x[:, nh * hd:(nh + nkv) * hd].reshape(n, nkv, hd)
+    v = x[:, (nh + nkv) * hd:].reshape(n, nkv, hd)
+    q = P.rope_neox(P.rmsnorm(q, qg.numpy(), 1e-6), tok_pos.numpy(), theta, rot)
+    k = P.rope_neox(P.rmsnorm(k, kg.numpy(), 1e-6), tok_pos.numpy(), theta, rot)
+    tol = 1e-5 if dt == torch.float32 else 8e-3
+    check(q_out.view(n, nh, hd), q, tol, "q")
+    for t in range(n):
+        page = int(table[tok_seq[t], tok_pos[t] // PAGE])
+        check(kp[page, :, tok_pos[t] % PAGE], k[t], tol, f"k of token {t}")
+        check(vp[page, :, tok_pos[t] % PAGE], v[t], tol, f"v of token {t}")
+    # nothing else was written
+    written = torch.zeros(6, PAGE, dtype=torch.bool)
+    for t in range(n):
+        written[int(table[tok_seq[t], tok_pos[t] // PAGE]), tok_pos[t] % PAGE] = True
+    untouched = ~written[:, None, :, None].expand(6, nkv, PAGE, hd)
+    assert bool((kp.float().cpu()[untouched] == 7.0).all()) and bool((vp.float().cpu()[untouched] == 7.0).all())
+
+
+def test_qk_norm_rope_append_padding_and_no_norm(ops):
+    n, nh, nkv, hd = 3, 2, 1, 16
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd, device=DEV)
+    tok_seq = torch.tensor([0, -1, 0], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([0, 0, 1], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[1]], dtype=torch.int32, device=DEV)
+    kp = torch.zeros(2, nkv, PAGE, hd, device=DEV)
+    vp = torch.zeros(2, nkv, PAGE, hd, device=DEV)
+    q_out = torch.empty(n, nh * hd, device=DEV)
+    ops.qk_norm_rope_append(qkv, None, None, 0.0, None, tok_seq, tok_pos, table, kp, vp, q_out, nh, nkv, hd)
+    assert torch.equal(q_out, qkv[:, :nh * hd])                      # no norm, no rotation: a copy
+    assert torch.equal(kp[1, 0, 0], qkv[0, nh * hd:(nh + 1) * hd]) and torch.equal(kp[1, 0, 1], qkv[2, 32:48])
+    assert float(kp[0].abs().sum()) == 0 and float(kp[1, 0, 2:].abs().sum()) == 0   # the padded row wrote nothing
+
+
+def plain_paged_attention(q, ks, vs, tok_seq, tok_pos, window):
+    out = np.zeros_like(q)
+    for t in range(q.shape[0]):
+        b, p = tok_seq[t], tok_pos[t]
+        first, last = P.attn_span(window, p)
+        k, v = ks[b][first:last + 1].numpy(), vs[b][first:last + 1].numpy()
+        nh, hd = q.shape[1], q.shape[2]
+        for h in range(nh):
+            kv = h // (nh // k.shape[1])
+            s = (k[:, kv].astype(np.float64) @ q[t, h].astype(np.float64)) / math.sqrt(hd)
+            w = np.exp(s - s.max())
+            out[t, h] = (w @ v[:, kv].astype(np.float64)) / w.sum()
+    return out
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (5, 1, 48, 0), (8, 2, 128, 0), (6, 3, 32, 50),
+                                              (2, 2, 80, 7), (4, 1, 256, 130)])
+@pytest.mark.parametrize("dt", DT)
+def test_attention_over_pages(ops, nh, nkv, hd, window, dt):
+    seqs = [300, 1, 64, 65, 129]
+    kp, vp, table, ks, vs = scatter_pages(16, nkv, hd, seqs, dt, seed=hd)
+    # queries: the last 3 positions of sequence 0 (a prompt's end), every position of 3 and some of the others
+    tok = [(0, 297), (0, 298), (0, 299), (1, 0), (2, 63), (4, 128), (4, 64), (4, 5)] + [(3, p) for p in range(65)]
+    tok_seq = torch.tensor([t[0] for t in tok], dtype=torch.int32)
+    tok_pos = torch.tensor([t[1] for t in tok], dtype=torch.int32)
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(len(tok), nh, hd, generator=g).to(dt)
+    out = torch.empty(len(tok), nh * hd, dtype=dt, device=DEV)
+    ops.attention(q.view(len(tok), -1).to(DEV), kp, vp, table, tok_seq.to(DEV), tok_pos.to(DEV), out, nh, nkv, hd,
+                  1.0 / math.sqrt(hd), window)
+    want = plain_paged_attention(q.float().numpy(), ks, vs, tok_seq.tolist(), tok_pos.tolist(), window)
+    check(out.view(len(tok), nh, hd), want, 2e-5 if dt == torch.float32 else 1.5e-2, "attention")
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dt):
+    nh, nkv, hd, n = 2, 1, 32, 700
+    kp, vp, table, ks, vs = scatter_pages(12, nkv, hd, [n], dt, seed=3)
+    q = torch.randn(1, nh, hd).to(dt)
+    # make key 3 (far back, first page) the one that matters: aligned with q and large
+    far = 3
+    page, row = int(table[0, far // PAGE]), far % PAGE
+    kp[page, 0, row] = (q[0, 0].float() * 4).to(dt).to(DEV)
+    args = (table, torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV))
+    out = torch.empty(1, nh * hd, dtype=dt, device=DEV)
+    ops.attention(q.view(1, -1).to(DEV), kp, vp, *args, out, nh, nkv, hd, 1.0 / math.sqrt(hd), 0)
+    assert rel_err(out.view(nh, hd)[0], vs[0][far, 0].to(dt).float()) < 2e-2      # head 0 returns that key's value
+    # window n - far: key `far` is the first key inside; window one less: it is outside
+    inside = torch.empty_like(out)
+    ops.attention(q.view(1, -1).to(DEV), kp, vp, *args, inside, nh, nkv, hd, 1.0 / math.sqrt(hd), n - far)
+    assert rel_err(inside.view(nh, hd)[0], vs[0][far, 0].to(dt).float()) < 2e-2
+    outside = torch.empty_like(out)
+    ops.attention(q.view(1, -1).to(DEV), kp, vp, *args, outside, nh, nkv, hd, 1.0 / math.sqrt(hd), n - far - 1)
+    assert rel_err(outside.view(nh, hd)[0], vs[0][far, 0].to(dt).float()) > 0.5
+    ks[0][far, 0] = (q[0, 0].float() * 4).to(dt).float()
+    for w, got in ((0, out), (n - far, inside), (n - far - 1, outside)):
+        want = plain_paged_attention(q.float().numpy(), ks, vs, [0], [n - 1], w)
+        check(got.view(1, nh, hd), want, 2e-5 if dt == torch.float32 else 1.5e-2, f"window {w}")
+
+
+def test_attention_padding_row_is_zero(ops):
+    kp, vp, table, _, _ = scatter_pages(2, 1, 16, [10], torch.float32)
+    out = torch.full((2, 32), 5.0, device=DEV)
+    ops.attention(torch.randn(2, 32, device=DEV), kp, vp, table, torch.tensor([-1, 0], dtype=torch.int32, device=DEV),
+                  torch.tensor([0, 9], dtype=torch.int32, device=DEV), out, 2, 1, 16, 0.25, 0)
+    assert float(out[0].abs().sum()) == 0 and float(out[1].abs().sum()) > 0
+
+
+@pytest.mark.parametrize("inter", [1, 136, 1000])
+@pytest.mark.parametrize("dt", DT)
+def test_swiglu(ops, inter, dt):
+    gu = (torch.randn(7, 2 * inter) * 4).to(dt)
+    out = torch.empty(7, inter, dtype=dt, device=DEV)
+    ops.swiglu(gu.to(DEV), out)
+    want = P.swiglu(gu.float().numpy()[:, :inter], gu.float().numpy()[:, inter:])
+    check(out, want, 2e-6 if dt == torch.float32 else 8e-3, "swiglu")
+
+
+def test_gather_rows(ops):
+    x = torch.randn(9, 33, device=DEV)
+    out = torch.empty(3, 33, device=DEV)
+    ops.gather_rows(x, torch.tensor([8, -1, 2], dtype=torch.int32, device=DEV), out)
+    assert torch.equal(out[0], x[8]) and torch.equal(out[2], x[2]) and float(out[1].abs().sum()) == 0
+
+
+def test_argmax_first_largest(ops):
+    for vocab in (1, 31, 307, 151936):
+        logits = torch.randn(5, vocab)
+        if vocab > 30:
+            logits[1, 17] = logits[1, 5] = 50.0          # a tie: the lower id
+            logits[2, :] = float("nan")
+            logits[2, 9] = -3.0                          # NaN never wins
+            logits[3, vocab - 1] = 60.0
+        out = torch.empty(5, dtype=torch.int32, device=DEV)
+        ops.argmax(logits.to(DEV), out)
+        want = [P.argmax_first(np.where(np.isnan(r), -np.inf, r)) for r in logits.numpy()]
+        assert out.tolist() == want
+
+
+def plain_temperature_draw(row, u, temperature):
+    """The draw in token-id order: p_i = exp((l_i - max) / T) in double, first i whose running sum reaches u * total."""
+    ok = ~np.isnan(row)
+    mx = row[ok].max()
+    p = np.where(ok, np.exp((row.astype(np.float64) - mx) / np.float32(temperature)), 0.0)
+    r = u * p.sum()
+    c = np.cumsum(p)
+    return int(np.searchsorted(c, r, side="left"))
+
+
+def test_sample_temperature(ops):
+    rs = np.random.RandomState(0)
+    for vocab, temp in ((5, 1.0), (307, 0.8), (5000, 1.5), (151936, 0.7)):
+        logits = (rs.randn(6, vocab) * 2).astype(np.float32)
+        logits[1, 3 % vocab] = np.nan
+        u = rs.rand(6)
+        u[0], u[5] = 0.0, 1.0 - 1e-16
+        out = torch.empty(6, dtype=torch.int32, device=DEV)
+        ops.sample_temperature(torch.tensor(logits).to(DEV), torch.tensor(u).to(DEV), out, temp)
+        got = out.tolist()
+        for r in range(6):
+            want = plain_temperature_draw(logits[r], u[r], temp)
+            # rounding of the running sum may move a draw that lands on a boundary by one id
+            assert abs(got[r] - want) <= 1 and not np.isnan(logits[r, got[r]]), (vocab, r, got[r], want)
+    # the distribution
+    logits = torch.log(torch.tensor([[0.6, 0.3, 0.1]])).repeat(4000, 1).to(DEV)
+    out = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits, torch.tensor(rs.rand(4000)).to(DEV), out, 1.0)
+    freq = np.bincount(out.cpu().numpy(), minlength=3) / 4000
+    assert np.abs(freq - [0.6, 0.3, 0.1]).max() < 0.03
+    with pytest.raises(ExtensionError, match="temperature"):
+        ops.sample_temperature(logits, torch.zeros(4000, dtype=torch.float64, device=DEV), out, 0.0)
+
+
+def test_kernels_refuse_what_they_cannot_take(ops):
+    with pytest.raises(ExtensionError, match="no CPU path"):
+        ops.swiglu(torch.zeros(1, 2), torch.zeros(1, 1))
+    kp, vp, table, _, _ = scatter_pages(1, 1, 16, [4], torch.float32)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ExtensionError, match="key/value heads"):
+        ops.attention(torch.zeros(1, 48, device=DEV), kp, vp, table, z, z, torch.zeros(1, 48, device=DEV), 3, 2, 16,
+                      1.0, 0)
