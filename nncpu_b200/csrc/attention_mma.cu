@@ -1,0 +1,498 @@
+// bfloat16 attention over the paged cache on tensor cores (mma.sync m16n8k16),
+// for head sizes 64 and 128.  Softmax runs in 32-bit with the scale applied
+// after the dot product (crates/nncpu/src/kernels/scalar.rs:444-548), online
+// over groups of 16 keys, and partial results are merged in key order like the
+// reference's block partials (crates/nncpu/src/kernels/scalar.rs:521-548,
+// crates/nncpu/src/model/forward.rs:174-190).
+//
+// Keys and values go from global memory (or L2) straight into the registers
+// of the warp that multiplies them: no shared-memory staging.  That works
+// because a matrix product does not care in which order its inner index runs
+// as long as both operands agree:
+//   * scores: a lane loads 16 bytes (8 lanes of the head) of its key row and
+//     of its query row at the same offsets, and feeds them to the tensor core
+//     as if they were the 4 lanes the fragment layout asks for;
+//   * weighted sum: a lane loads 16 bytes of 4 value rows and interleaves them
+//     with byte permutes into the "two consecutive keys per register" form.
+//
+// Two kernels share the inner loop:
+//   * decode: one block per (token, key/value head, split of its keys); the 16
+//     tensor-core rows hold the query heads that share the key/value head
+//     (grouped-query attention reads each key once for all of them); the
+//     block's four warps take alternate 16-key groups; splits are merged by a
+//     second kernel through a scratch buffer.
+//   * prefill: one warp per (16 consecutive tokens of a sequence, head).
+
+#include <math.h>
+
+#define NN_LIB attention_mma
+#include "common.cuh"
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+
+__device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) {
+    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+// What one warp carries through its keys: 16 rows x HD output lanes, the running maximum (in the
+// log2 domain, scale folded in) and the running sum of each of its two rows per lane.
+template <int HD>
+struct Acc {
+    float o[HD / 8][4];
+    float m[2], l[2];
+    __device__ void init() {
+#pragma unroll
+        for (int t = 0; t < HD / 8; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[t][e] = 0.0f;
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.0f;
+    }
+};
+
+// Query fragments of the rows (lane / 4) and (lane / 4 + 8); a null row gives zeros.
+template <int HD>
+__device__ __forceinline__ void load_q(uint32_t (&qa)[HD / 16][4], const __nv_bfloat16* row_lo,
+                                       const __nv_bfloat16* row_hi, int lane) {
+    const int c = lane & 3;
+#pragma unroll
+    for (int j = 0; j < HD / 32; ++j) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        const uint4 lo = row_lo ? ld16(row_lo + (c + 4 * j) * 8) : z;
+        const uint4 hi = row_hi ? ld16(row_hi + (c + 4 * j) * 8) : z;
+        qa[2 * j][0] = lo.x; qa[2 * j][2] = lo.y; qa[2 * j][1] = hi.x; qa[2 * j][3] = hi.y;
+        qa[2 * j + 1][0] = lo.z; qa[2 * j + 1][2] = lo.w; qa[2 * j + 1][1] = hi.z; qa[2 * j + 1][3] = hi.w;
+    }
+}
+
+struct Pages {
+    const __nv_bfloat16* k;
+    const __nv_bfloat16* v;
+    const int* table;  // page ids of this sequence
+    int n_kv, kvh;
+    template <int HD>
+    __device__ __forceinline__ size_t row(int key) const {
+        return (((size_t)table[key / kPage] * n_kv + kvh) * kPage + key % kPage) * HD;
+    }
+};
+
+// Registers holding one group of 16 keys: two 8-key tiles of K, four value rows per lane.
+template <int HD>
+struct Group {
+    uint4 k[2][HD / 32];
+    uint4 v[4][HD / 64];
+};
+
+// Loads the group that starts at key k0 (a multiple of 16).  Keys outside [key_lo, key_hi] are
+// not touched (their pages may be gone) and read as zeros.
+template <int HD>
+__device__ __forceinline__ void load_group(Group<HD>& g, const Pages& pg, int k0, int key_lo, int key_hi, int lane) {
+    const int c = lane & 3, r = lane >> 2;
+    const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int key = k0 + 8 * t + r;
+        const bool ok = key >= key_lo && key <= key_hi;
+        const __nv_bfloat16* p = pg.k + (ok ? pg.row<HD>(key) : 0);
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) g.k[t][j] = ok ? ld16(p + (c + 4 * j) * 8) : z;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int key = k0 + 2 * c + (i & 1) + 8 * (i >> 1);
+        const bool ok = key >= key_lo && key <= key_hi;
+        const __nv_bfloat16* p = pg.v + (ok ? pg.row<HD>(key) : 0);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h) g.v[i][h] = ok ? ld16(p + h * 64 + r * 8) : z;
+    }
+}
+
+// One group of 16 keys starting at k0 into the accumulators.  Row `e` (0: lane / 4, 1: lane / 4 + 8)
+// sees the keys lo[e] .. hi[e]; scale2 = scale * log2(e).
+template <int HD>
+__device__ __forceinline__ void consume_group(Acc<HD>& acc, const uint32_t (&qa)[HD / 16][4], const Group<HD>& g,
+                                              int k0, const int (&lo)[2], const int (&hi)[2], float scale2,
+                                              int lane) {
+    const int c = lane & 3;
+    float s[2][4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) {
+            mma_bf16(s[t], qa[2 * j][0], qa[2 * j][1], qa[2 * j][2], qa[2 * j][3], g.k[t][j].x, g.k[t][j].y);
+            mma_bf16(s[t], qa[2 * j + 1][0], qa[2 * j + 1][1], qa[2 * j + 1][2], qa[2 * j + 1][3], g.k[t][j].z,
+                     g.k[t][j].w);
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = k0 + 8 * t + 2 * c + (e & 1), row = e >> 1;
+            const bool ok = key >= lo[row] && key <= hi[row];
+            s[t][e] = ok ? s[t][e] * scale2 : -INFINITY;
+            mx[row] = fmaxf(mx[row], s[t][e]);
+        }
+    float corr[2];
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 1));
+        mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 2));
+        const float m_new = fmaxf(acc.m[row], mx[row]);
+        corr[row] = m_new == -INFINITY ? 1.0f : exp2f(acc.m[row] - m_new);
+        acc.m[row] = m_new;
+    }
+    uint32_t pa[4];
+    {
+        float p[2][4];
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = e >> 1;
+                p[t][e] = acc.m[row] == -INFINITY ? 0.0f : exp2f(s[t][e] - acc.m[row]);
+            }
+#pragma unroll
+        for (int row = 0; row < 2; ++row)
+            acc.l[row] = acc.l[row] * corr[row] + (p[0][2 * row] + p[0][2 * row + 1]) + (p[1][2 * row] + p[1][2 * row + 1]);
+        pa[0] = pack_bf16(p[0][0], p[0][1]);
+        pa[1] = pack_bf16(p[0][2], p[0][3]);
+        pa[2] = pack_bf16(p[1][0], p[1][1]);
+        pa[3] = pack_bf16(p[1][2], p[1][3]);
+    }
+#pragma unroll
+    for (int h = 0; h < HD / 64; ++h)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float (&o)[4] = acc.o[h * 8 + e];
+            o[0] *= corr[0]; o[1] *= corr[0]; o[2] *= corr[1]; o[3] *= corr[1];
+            const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+            const uint32_t b0 = __byte_perm(u4_get(g.v[0][h], e >> 1), u4_get(g.v[1][h], e >> 1), sel);
+            const uint32_t b1 = __byte_perm(u4_get(g.v[2][h], e >> 1), u4_get(g.v[3][h], e >> 1), sel);
+            mma_bf16(o, pa[0], pa[1], pa[2], pa[3], b0, b1);
+        }
+}
+
+// Runs the groups first_group, first_group + stride, ... that overlap [key_lo, key_hi].
+template <int HD>
+__device__ __forceinline__ void run_keys(Acc<HD>& acc, const uint32_t (&qa)[HD / 16][4], const Pages& pg, int key_lo,
+                                         int key_hi, const int (&lo)[2], const int (&hi)[2], int first_group,
+                                         int stride, float scale2, int lane) {
+    const int last_group = key_hi >> 4;
+    int gi = first_group;
+    if (gi > last_group) return;
+    Group<HD> cur, nxt;
+    load_group<HD>(cur, pg, gi << 4, key_lo, key_hi, lane);
+    while (true) {
+        const int gn = gi + stride;
+        const bool more = gn <= last_group;
+        if (more) load_group<HD>(nxt, pg, gn << 4, key_lo, key_hi, lane);
+        consume_group<HD>(acc, qa, cur, gi << 4, lo, hi, scale2, lane);
+        if (!more) break;
+        cur = nxt;
+        gi = gn;
+    }
+}
+
+// The actual head lane of accumulator register (tile t, element e) for this lane.
+template <int HD>
+__device__ __forceinline__ int out_dim(int t, int e, int lane) {
+    return (t >> 3) * 64 + (2 * (lane & 3) + (e & 1)) * 8 + (t & 7);
+}
+
+// ---------------------------------------------------------------------------
+// Decode: one token per sequence.  grid = (n_splits, n_kv, n_tok), 128 threads.
+// ---------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(128, 2)
+decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+              const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
+              const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
+              float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv, float scale2,
+              int window) {
+    extern __shared__ float sm[];  // [4 warps][G rows][HD + 2]
+    const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = n_heads / n_kv;  // at most 16 here
+    const int seq = tok_seq[t];
+    const size_t out_row = (size_t)t * n_heads * HD + (size_t)kvh * G * HD;
+    if (seq < 0) {  // padding: zeros
+        if (n_splits == 1 || split == 0)
+            for (int i = threadIdx.x; i < G * HD; i += 128) out[out_row + i] = __float2bfloat16_rn(0.0f);
+        if (n_splits > 1) {
+            const size_t pb = ((size_t)t * n_kv + kvh) * n_splits + split;
+            for (int i = threadIdx.x; i < G * HD; i += 128) part_o[pb * G * HD + i] = 0.0f;
+            for (int i = threadIdx.x; i < G * 2; i += 128) part_ml[pb * G * 2 + i] = (i & 1) ? 0.0f : -INFINITY;
+        }
+        return;
+    }
+    const int pos = tok_pos[t];
+    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    // this split's keys: whole 16-key groups, the same number (rounded up) for every split
+    const int g_first = first >> 4, g_last = pos >> 4;
+    const int per = (g_last - g_first + n_splits) / n_splits;
+    const int g0 = g_first + split * per;
+    const int g1 = min(g_last, g0 + per - 1);
+    const int key_lo = max(first, g0 << 4), key_hi = min(pos, (g1 << 4) + 15);
+
+    Acc<HD> acc;
+    acc.init();
+    if (g0 <= g1) {
+        const int r = lane >> 2;
+        uint32_t qa[HD / 16][4];
+        const __nv_bfloat16* qbase = q + out_row;
+        load_q<HD>(qa, r < G ? qbase + (size_t)r * HD : nullptr, r + 8 < G ? qbase + (size_t)(r + 8) * HD : nullptr,
+                   lane);
+        Pages pg{k_pages, v_pages, block_table + (size_t)seq * bt_stride, n_kv, kvh};
+        const int lo[2] = {key_lo, key_lo}, hi[2] = {key_hi, key_hi};
+        run_keys<HD>(acc, qa, pg, key_lo, key_hi, lo, hi, g0 + warp, 4, scale2, lane);
+    }
+    // every lane's partial sums of its two rows -> the row's sum
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 1);
+        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 2);
+    }
+    // the four warps' results meet in shared memory
+    constexpr int W = HD + 2;
+    float* mine = sm + (size_t)warp * G * W;
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        const int head = (lane >> 2) + 8 * row;
+        if (head < G) {
+#pragma unroll
+            for (int tt = 0; tt < HD / 8; ++tt) {
+                mine[head * W + out_dim<HD>(tt, 0, lane)] = acc.o[tt][2 * row];
+                mine[head * W + out_dim<HD>(tt, 1, lane)] = acc.o[tt][2 * row + 1];
+            }
+            if ((lane & 3) == 0) {
+                mine[head * W + HD] = acc.m[row];
+                mine[head * W + HD + 1] = acc.l[row];
+            }
+        }
+    }
+    __syncthreads();
+    const size_t pb = ((size_t)t * n_kv + kvh) * n_splits + split;
+    for (int i = threadIdx.x; i < G * HD; i += 128) {
+        const int head = i / HD, d = i % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, sm[(w * G + head) * W + HD]);
+        float o = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm[(w * G + head) * W + HD];
+            const float cw = mw == -INFINITY ? 0.0f : exp2f(mw - m);
+            o = fmaf(sm[(w * G + head) * W + d], cw, o);
+            l = fmaf(sm[(w * G + head) * W + HD + 1], cw, l);
+        }
+        if (n_splits == 1) {
+            out[out_row + i] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+        } else {
+            part_o[pb * G * HD + i] = o;
+            if (d == 0) {
+                part_ml[(pb * G + head) * 2] = m;
+                part_ml[(pb * G + head) * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// Merges the splits of every (token, head) in split order.  grid = (n_heads, n_tok), HD threads.
+template <int HD>
+__global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                             __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int n_splits) {
+    const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
+    const int G = n_heads / n_kv, kvh = h / G, head = h % G;
+    const size_t pb = ((size_t)t * n_kv + kvh) * n_splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[((pb + s) * G + head) * 2]);
+    float o = 0.0f, l = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = part_ml[((pb + s) * G + head) * 2];
+        const float c = ms == -INFINITY ? 0.0f : exp2f(ms - m);
+        o = fmaf(part_o[((pb + s) * G + head) * HD + d], c, o);
+        l = fmaf(part_ml[((pb + s) * G + head) * 2 + 1], c, l);
+    }
+    out[((size_t)t * n_heads + h) * HD + d] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+}
+
+// ---------------------------------------------------------------------------
+// Prefill: any number of new tokens per sequence.  One warp per (tile of 16
+// consecutive new tokens of one sequence, head); grid = (tiles / 4, n_heads).
+// ---------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(128)
+prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+               const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
+               const int* __restrict__ cu_seqlens, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
+               int n_seqs, int n_heads, int n_kv, float scale2, int window) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y;
+    // long tiles first: tiles are numbered from the end of the batch backwards within each sequence
+    int tile = blockIdx.x * 4 + warp;
+    int seq = -1, q0 = 0, q_end = 0;
+    for (int b = 0; b < n_seqs; ++b) {
+        const int a = cu_seqlens[b], e = cu_seqlens[b + 1];
+        const int n_tiles = (e - a + 15) >> 4;
+        if (tile < n_tiles) {
+            seq = b;
+            q0 = a + ((n_tiles - 1 - tile) << 4);
+            q_end = e;
+            break;
+        }
+        tile -= n_tiles;
+    }
+    if (seq < 0) return;
+    const int r = lane >> 2;
+    const int tok_lo = q0 + r, tok_hi = q0 + r + 8;
+    const bool has_lo = tok_lo < q_end, has_hi = tok_hi < q_end;
+    const int pos0 = tok_pos[q0];  // positions of a sequence's new tokens are consecutive
+    const int n_rows = min(16, q_end - q0);
+    int lo[2], hi[2];
+    hi[0] = has_lo ? pos0 + r : -1;
+    hi[1] = has_hi ? pos0 + r + 8 : -1;
+    lo[0] = (window > 0 && hi[0] + 1 > window) ? hi[0] + 1 - window : 0;
+    lo[1] = (window > 0 && hi[1] + 1 > window) ? hi[1] + 1 - window : 0;
+    const int key_hi = pos0 + n_rows - 1;
+    const int key_lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+
+    uint32_t qa[HD / 16][4];
+    const size_t row_stride = (size_t)n_heads * HD;
+    load_q<HD>(qa, has_lo ? q + tok_lo * row_stride + (size_t)h * HD : nullptr,
+               has_hi ? q + tok_hi * row_stride + (size_t)h * HD : nullptr, lane);
+    Pages pg{k_pages, v_pages, block_table + (size_t)seq * bt_stride, n_kv, h / (n_heads / n_kv)};
+    Acc<HD> acc;
+    acc.init();
+    run_keys<HD>(acc, qa, pg, key_lo, key_hi, lo, hi, key_lo >> 4, 1, scale2, lane);
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 1);
+        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 2);
+        const int tok = row == 0 ? tok_lo : tok_hi;
+        if (tok >= q_end) continue;
+        const float inv = acc.l[row] > 0.0f ? 1.0f / acc.l[row] : 0.0f;
+        __nv_bfloat16* o = out + tok * row_stride + (size_t)h * HD;
+#pragma unroll
+        for (int tt = 0; tt < HD / 8; ++tt) {
+            o[out_dim<HD>(tt, 0, lane)] = __float2bfloat16_rn(acc.o[tt][2 * row] * inv);
+            o[out_dim<HD>(tt, 1, lane)] = __float2bfloat16_rn(acc.o[tt][2 * row + 1] * inv);
+        }
+    }
+}
+
+template <int HD>
+int launch_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
+                  const int* tok_seq, const int* tok_pos, void* out, float* scratch, int n_tok, int n_heads, int n_kv,
+                  float scale, int window, int n_splits, cudaStream_t stream) {
+    const int G = n_heads / n_kv;
+    const size_t smem = (size_t)4 * G * (HD + 2) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 16 * (HD + 2) * 4);
+        configured = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_tok * n_kv * n_splits * G * HD : nullptr;
+    dim3 grid(n_splits, n_kv, n_tok);
+    decode_kernel<HD><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
+                                                   (const __nv_bfloat16*)v_pages, block_table, bt_stride, tok_seq,
+                                                   tok_pos, (__nv_bfloat16*)out, part_o, part_ml, n_heads, n_kv,
+                                                   scale * kLog2e, window);
+    NN_LAUNCH_OK("attention decode");
+    if (n_splits > 1) {
+        merge_kernel<HD><<<dim3(n_heads, n_tok), HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_heads, n_kv,
+                                                                  n_splits);
+        NN_LAUNCH_OK("attention merge");
+    }
+    return 0;
+}
+
+template <int HD>
+int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
+                   const int* cu_seqlens, const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads, int n_kv,
+                   float scale, int window, cudaStream_t stream) {
+    const int max_tiles = n_tok / 16 + n_seqs;
+    dim3 grid((max_tiles + 3) / 4, n_heads);
+    prefill_kernel<HD><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
+                                                 (const __nv_bfloat16*)v_pages, block_table, bt_stride, cu_seqlens,
+                                                 tok_pos, (__nv_bfloat16*)out, n_seqs, n_heads, n_kv, scale * kLog2e,
+                                                 window);
+    NN_LAUNCH_OK("attention prefill");
+    return 0;
+}
+
+}  // namespace
+
+// Whether the tensor-core attention kernels take these sizes (bfloat16 q, cache and output assumed).
+extern "C" int nncpu_attention_mma_supported(int n_heads, int n_kv, int hd) {
+    return (hd == 64 || hd == 128) && n_kv > 0 && n_heads % n_kv == 0 && n_heads / n_kv <= 16;
+}
+
+// Floats of scratch the decode kernel needs for n_tok tokens cut into n_splits splits (0 for one split).
+extern "C" long nncpu_attention_decode_scratch_floats(int n_tok, int n_heads, int n_kv, int hd, int n_splits) {
+    if (n_splits <= 1) return 0;
+    const long G = n_heads / n_kv;
+    return (long)n_tok * n_kv * n_splits * G * (hd + 2);
+}
+
+// One token per sequence: token t belongs to sequence tok_seq[t] (negative: padding) and sits at
+// position tok_pos[t]; its keys 0..tok_pos[t] (or the last `window` of them) are in the cache.
+extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, const void* v_pages,
+                                          const int* block_table, int bt_stride, const int* tok_seq,
+                                          const int* tok_pos, void* out, float* scratch, long scratch_floats,
+                                          int n_tok, int n_heads, int n_kv, int hd, float scale, int window,
+                                          int n_splits, void* stream) {
+    NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
+             "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
+             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+    NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535 && window >= 0, "attention decode: %d tokens, %d splits",
+             n_tok, n_splits);
+    NN_CHECK(scratch_floats >= nncpu_attention_decode_scratch_floats(n_tok, n_heads, n_kv, hd, n_splits),
+             "attention decode: %ld floats of scratch, %ld needed", scratch_floats,
+             nncpu_attention_decode_scratch_floats(n_tok, n_heads, n_kv, hd, n_splits));
+    if (n_tok == 0) return 0;
+    if (hd == 64)
+        return launch_decode<64>(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
+                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream);
+    return launch_decode<128>(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
+                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream);
+}
+
+// Any mix of new tokens per sequence: sequence b brings the flat tokens cu_seqlens[b] .. cu_seqlens[b + 1] - 1
+// at consecutive positions starting at tok_pos[cu_seqlens[b]]; their keys are already in the cache.
+extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, const void* v_pages,
+                                           const int* block_table, int bt_stride, const int* cu_seqlens,
+                                           const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads,
+                                           int n_kv, int hd, float scale, int window, void* stream) {
+    NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
+             "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
+             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+    NN_CHECK(n_tok >= 0 && n_seqs >= 0 && window >= 0, "attention prefill: %d tokens of %d sequences", n_tok, n_seqs);
+    if (n_tok == 0 || n_seqs == 0) return 0;
+    if (hd == 64)
+        return launch_prefill<64>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,
+                                  n_heads, n_kv, scale, window, (cudaStream_t)stream);
+    return launch_prefill<128>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,
+                               n_heads, n_kv, scale, window, (cudaStream_t)stream);
+}

@@ -61,7 +61,7 @@ class DecodeGraph:
             tok_pos=m[self.o_pos:self.o_pos + B], seq_slots=m[self.o_slot:self.o_slot + B],
             cu_seqlens=m[self.o_cu:self.o_cu + B + 1], logit_rows=m[self.o_rows:self.o_rows + B],
             block_tables=[m[o:o + B * self.width].view(B, self.width) for o in self.o_tables],
-            q_lens=[1] * B, kv_lens=[0] * B, is_decode=True)
+            q_lens=[1] * B, kv_lens=[0] * B, is_decode=True, max_kv_len=cache.max_seq_len)
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.n_kernels = 0

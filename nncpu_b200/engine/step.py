@@ -37,6 +37,7 @@ class StepContext:
     kv_lens: List[int]          # host: length of each sequence after this step
     is_decode: bool             # every sequence brings exactly one token
     h2d_bytes: int = 0          # bytes of metadata copied to the device for this step
+    max_kv_len: int = 0         # host: an upper bound of the longest sequence after this step
     memo: Dict = field(default_factory=dict)  # per-step results shared between layers
 
     def entry_cache(self, cache: Cache, entry: int) -> EntryCache:
@@ -80,7 +81,8 @@ def make_context(cache: Cache, slots: Sequence[int], tokens: Sequence[Sequence[i
     return StepContext(n_tokens=n, n_seqs=B, n_wanted=len(rows), tok_ids=views[0], tok_seq=views[1],
                        tok_pos=views[2], seq_slots=views[3], cu_seqlens=views[4], logit_rows=views[5],
                        block_tables=bts, q_lens=q_lens, kv_lens=[s + q for s, q in zip(starts, q_lens)],
-                       is_decode=all(q == 1 for q in q_lens), h2d_bytes=host.numel() * 4)
+                       is_decode=all(q == 1 for q in q_lens), h2d_bytes=host.numel() * 4,
+                       max_kv_len=max(s + q for s, q in zip(starts, q_lens)))
 
 
 class Engine:

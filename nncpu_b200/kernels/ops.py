@@ -150,6 +150,41 @@ def attention(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, n_heads: 
           _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _stream())
 
 
+def attention_mma_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) -> bool:
+    """The tensor-core attention kernels take bfloat16 q, cache and output with
+    head size 64 or 128 and at most 16 query heads per key/value head."""
+    return (head_dim in (64, 128) and n_kv > 0 and n_heads % n_kv == 0 and n_heads // n_kv <= 16
+            and all(t.dtype == torch.bfloat16 for t in tensors))
+
+
+def attention_decode_scratch_floats(n_tok: int, n_heads: int, n_kv: int, head_dim: int, n_splits: int) -> int:
+    return 0 if n_splits <= 1 else n_tok * n_kv * n_splits * (n_heads // n_kv) * (head_dim + 2)
+
+
+def attention_decode_mma(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, scratch, n_heads: int, n_kv: int,
+                         head_dim: int, scale: float, window: int, n_splits: int) -> None:
+    """One token per sequence; each token's keys are cut into ``n_splits``
+    splits that run in parallel and are merged through ``scratch`` (float32,
+    ``attention_decode_scratch_floats`` elements; None for one split)."""
+    n = q.shape[0]
+    assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape
+    assert scratch is None or scratch.dtype == torch.float32
+    _call("attention_mma", "nncpu_attention_decode_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+          _i(block_table.shape[1]), _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _ptr(scratch),
+          ctypes.c_long(0 if scratch is None else scratch.numel()), _i(n), _i(n_heads), _i(n_kv), _i(head_dim),
+          _f(scale), _i(window), _i(n_splits), _stream())
+
+
+def attention_prefill_mma(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, n_seqs: int, n_heads: int,
+                          n_kv: int, head_dim: int, scale: float, window: int) -> None:
+    """Any number of new tokens per sequence, at consecutive positions."""
+    n = q.shape[0]
+    assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape and cu_seqlens.numel() >= n_seqs + 1
+    _call("attention_mma", "nncpu_attention_prefill_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+          _i(block_table.shape[1]), _ptr(cu_seqlens), _ptr(tok_pos), _ptr(out), _i(n), _i(n_seqs), _i(n_heads),
+          _i(n_kv), _i(head_dim), _f(scale), _i(window), _stream())
+
+
 def swiglu(gate_up, out) -> None:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     n, inter = out.shape

@@ -89,6 +89,25 @@ class Attention(Mixer):
                                 ctx.tok_seq, ctx.tok_pos, cache.block_table, cache.k_pages, cache.v_pages, q,
                                 s.n_heads, 0 if self.shared_kv else s.n_kv_heads, s.head_dim)
         attn = rt.empty(n, self.q_size)
-        ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
-                      s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
+        self._attend(ctx, q, cache, attn)
         rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True)
+
+    def _attend(self, ctx, q, cache, attn):
+        """bfloat16 with a head size the tensor-core kernels take: split-key
+        decode or tiled prefill; everything else: the 32-bit kernel."""
+        s = self.spec
+        if not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
+            ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
+                          s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
+        elif ctx.is_decode:
+            # enough blocks to fill the GPU twice over, but at least 256 keys per split
+            longest = min(ctx.max_kv_len, s.window) if s.window > 0 else ctx.max_kv_len
+            pairs = ctx.n_tokens * s.n_kv_heads
+            n_splits = max(1, min(-(-296 // pairs), longest // 256))
+            floats = ops.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
+            scratch = self.rt.empty(floats, dtype=torch.float32) if floats else None
+            ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
+                                     attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits)
+        else:
+            ops.attention_prefill_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
+                                      attn, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)

@@ -234,6 +234,87 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dt):
         check(got.view(1, nh, hd), want, 2e-5 if dt == torch.float32 else 1.5e-2, f"window {w}")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 0), (8, 1, 128, 0), (32, 8, 128, 0), (16, 1, 64, 70),
+                                              (3, 3, 128, 33), (12, 2, 128, 500)])
+def test_attention_tensor_core_decode(ops, nh, nkv, hd, window):
+    seqs = [700, 1, 64, 65, 16, 17, 300]
+    kp, vp, table, ks, vs = scatter_pages(24, nkv, hd, seqs, torch.bfloat16, seed=hd + nh)
+    tok_seq = torch.tensor([0, 1, 2, -1, 3, 4, 5, 6], dtype=torch.int32)
+    tok_pos = torch.tensor([699, 0, 63, 5, 64, 15, 16, 299], dtype=torch.int32)
+    n = len(tok_seq)
+    q = torch.randn(n, nh, hd, generator=torch.Generator().manual_seed(2)).bfloat16()
+    live = [i for i in range(n) if tok_seq[i] >= 0]
+    want = plain_paged_attention(q.float().numpy()[live], ks, vs, tok_seq[live].tolist(), tok_pos[live].tolist(), window)
+    for n_splits in (1, 2, 5, 64):
+        out = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+        floats = ops.attention_decode_scratch_floats(n, nh, nkv, hd, n_splits)
+        scratch = torch.full((floats,), float("nan"), device=DEV) if floats else None
+        ops.attention_decode_mma(q.view(n, -1).to(DEV), kp, vp, table, tok_seq.to(DEV), tok_pos.to(DEV), out, scratch,
+                                 nh, nkv, hd, 1.0 / math.sqrt(hd), window, n_splits)
+        check(out.view(n, nh, hd)[live], want, 1.5e-2, f"decode attention, {n_splits} splits")
+        assert float(out[3].float().abs().sum()) == 0.0          # the padded row
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 0), (8, 1, 128, 0), (6, 3, 128, 40), (16, 1, 64, 17)])
+def test_attention_tensor_core_prefill(ops, nh, nkv, hd, window):
+    # sequence 0 adds 70 tokens to 130 cached ones, 1 starts with 1 token, 2 starts with 100, 3 adds 1 to 64, 4 adds 16 to 5
+    old, new = [130, 0, 0, 64, 5], [70, 1, 100, 1, 16]
+    seqs = [o + n for o, n in zip(old, new)]
+    kp, vp, table, ks, vs = scatter_pages(16, nkv, hd, seqs, torch.bfloat16, seed=nh)
+    tok_seq = [b for b, n in enumerate(new) for _ in range(n)]
+    tok_pos = [o + i for o, n in zip(old, new) for i in range(n)]
+    cu = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    n = len(tok_seq)
+    q = torch.randn(n, nh, hd, generator=torch.Generator().manual_seed(5)).bfloat16()
+    out = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill_mma(q.view(n, -1).to(DEV), kp, vp, table, torch.tensor(cu).to(DEV),
+                              torch.tensor(tok_pos, dtype=torch.int32).to(DEV), out, len(new), nh, nkv, hd,
+                              1.0 / math.sqrt(hd), window)
+    want = plain_paged_attention(q.float().numpy(), ks, vs, tok_seq, tok_pos, window)
+    check(out.view(n, nh, hd), want, 1.5e-2, "prefill attention")
+
+
+def test_attention_tensor_core_far_key_and_window_edge(ops):
+    nh, nkv, hd, n = 4, 1, 128, 900
+    kp, vp, table, ks, vs = scatter_pages(16, nkv, hd, [n], torch.bfloat16, seed=8)
+    q = torch.randn(1, nh, hd).bfloat16()
+    far = 3
+    page, row = int(table[0, far // PAGE]), far % PAGE
+    kp[page, 0, row] = (q[0, 2].float() * 4).bfloat16().to(DEV)
+    ks[0][far, 0] = (q[0, 2].float() * 4).bfloat16().float()
+    z, last = torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    for window, seen in ((0, True), (n - far, True), (n - far - 1, False)):
+        want = plain_paged_attention(q.float().numpy(), ks, vs, [0], [n - 1], window)
+        for n_splits in (1, 7):
+            out = torch.empty(1, nh * hd, dtype=torch.bfloat16, device=DEV)
+            floats = ops.attention_decode_scratch_floats(1, nh, nkv, hd, n_splits)
+            ops.attention_decode_mma(q.view(1, -1).to(DEV), kp, vp, table, z, last, out,
+                                     torch.empty(floats, device=DEV) if floats else None, nh, nkv, hd,
+                                     1.0 / math.sqrt(hd), window, n_splits)
+            check(out.view(1, nh, hd), want, 1.5e-2, f"decode, window {window}")
+            assert (rel_err(out.view(nh, hd)[2], vs[0][far, 0]) < 2e-2) == seen
+        out = torch.empty(1, nh * hd, dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill_mma(q.view(1, -1).to(DEV), kp, vp, table, cu, last, out, 1, nh, nkv, hd,
+                                  1.0 / math.sqrt(hd), window)
+        check(out.view(1, nh, hd), want, 1.5e-2, f"prefill, window {window}")
+
+
+def test_attention_tensor_core_refuses_other_sizes(ops):
+    assert not ops.attention_mma_supported(4, 2, 48) and not ops.attention_mma_supported(34, 1, 64)
+    assert not ops.attention_mma_supported(4, 2, 64, torch.zeros(1)) and ops.attention_mma_supported(32, 8, 128)
+    kp, vp, table, _, _ = scatter_pages(1, 1, 48, [4], torch.bfloat16)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q = torch.zeros(1, 96, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ExtensionError, match="head size 64 or 128"):
+        ops.attention_decode_mma(q, kp, vp, table, z, z, torch.empty_like(q), None, 2, 1, 48, 1.0, 0, 1)
+    kp, vp, table, _, _ = scatter_pages(1, 1, 64, [4], torch.bfloat16)
+    q = torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ExtensionError, match="scratch"):
+        ops.attention_decode_mma(q, kp, vp, table, z, z, torch.empty_like(q), torch.empty(8, device=DEV), 2, 1, 64,
+                                 1.0, 0, 4)
+
+
 def test_attention_padding_row_is_zero(ops):
     kp, vp, table, _, _ = scatter_pages(2, 1, 16, [10], torch.float32)
     out = torch.full((2, 32), 5.0, device=DEV)

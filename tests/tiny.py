@@ -29,6 +29,15 @@ TINY = {
               rms_norm_eps=3e-6, tie_word_embeddings=False, attention_bias=False, max_position_embeddings=4096,
               use_sliding_window=True, sliding_window=40,
               layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"]),
+    # head sizes the tensor-core attention kernels take: 64 with two heads per key/value head, and 128 with
+    # eight heads on one key/value head and a window on the first layer
+    "D": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=128, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=64, intermediate_size=320, vocab_size=520, rope_theta=10000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=True, attention_bias=False, max_position_embeddings=2048),
+    "E": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=192, num_attention_heads=8,
+              num_key_value_heads=1, head_dim=128, intermediate_size=256, vocab_size=333, rope_theta=1000000.0,
+              rms_norm_eps=1e-5, tie_word_embeddings=False, attention_bias=True, max_position_embeddings=2048,
+              use_sliding_window=True, sliding_window=100, layer_types=["sliding_attention", "full_attention"]),
 }
 
 
