@@ -1,21 +1,32 @@
 // bfloat16 matrix product for sm_100a on the 5th-generation tensor cores:
 //   C[M, N] (+)= X[M, K] . W[N, K]^T (+ bias[N])
-// Operand tiles are brought to shared memory by TMA (128-byte swizzle), one
-// elected thread issues tcgen05.mma with the accumulator in tensor memory,
-// and four warps read the accumulator back with tcgen05.ld for the epilogue.
+// or, with the gated-activation epilogue, C[M, N/2] = silu(gate) * up where the
+// rows of W hold gate and up rows interleaved in blocks of 8.
+//
+// Operand tiles come to shared memory by TMA (128-byte swizzle); one elected
+// thread issues tcgen05.mma with the accumulator in tensor memory; four warps
+// read the accumulator back with tcgen05.ld for the epilogue.  The kernel is
+// persistent: each block walks a list of work items (output tile x slice of K)
+// and keeps two accumulators in tensor memory, so the epilogue of one item
+// runs under the matrix instructions of the next.
 //
 // One kernel serves prefill and decode.  The tensor-core M operand is always a
 // 128-row tile of "A" and the N operand a BN-row tile of "B":
-//   * many tokens:  A = activations, B = weights           (C tile = A rows x B rows)
-//   * few tokens:   A = weights,     B = activations, and the epilogue stores
-//     the tile transposed, so every weight byte is read once and no tensor
-//     core row is wasted on padding.
+//   * many tokens:  A = activations, B = weights;
+//   * few tokens:   A = weights, B = activations, and the epilogue stores the
+//     tile transposed: every weight byte is read once and no tensor-core row
+//     is spent on padding.  With few tokens there are few output tiles, so K is
+//     cut into slices that run on different SMs; each slice writes its partial
+//     tile to scratch memory and takes a ticket, and the block that takes the
+//     last ticket of a tile adds the slices in slice order, so the sum does not
+//     depend on which block came last.  No block waits for another.
 // The reference computes the same products with its own BF16 row kernels
 // (crates/nncpu/src/kernels/mod.rs:454-485, crates/nncpu/src/kernels/scalar.rs:555-567);
 // accumulation is 32-bit here as there.
 //
-// Every wait on an mbarrier is bounded; a wait that runs out sets *status and
-// the block leaves through the common exit, which frees its tensor memory.
+// Every wait on an mbarrier is bounded in time; a wait that runs out sets
+// *status and the block leaves through the common exit, which frees its
+// tensor memory.
 
 #include <cuda.h>
 #include <map>
@@ -30,10 +41,12 @@ namespace {
 constexpr int kBlockM = 128;  // rows of the A tile = tensor-core M
 constexpr int kBlockK = 64;   // 64 bfloat16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;    // K of one tcgen05.mma for 16-bit inputs
-constexpr uint32_t kSpinLimit = 1u << 26;
 constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA and tensor memory, warps 2-5: epilogue
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
-enum GemmStatus : int { kOk = 0, kTimeoutEmpty = 101, kTimeoutFull = 102, kTimeoutAccum = 103 };
+enum GemmStatus : int { kOk = 0, kTimeoutEmpty = 101, kTimeoutFull = 102, kTimeoutAccumFull = 103,
+                        kTimeoutAccumEmpty = 104 };
+enum Epilogue : int { kPlain = 0, kSwiglu = 1 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -44,6 +57,10 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
@@ -60,11 +77,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: false when two seconds passed without the phase completing.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    while (true) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > kWaitLimitNs) return false;
+    }
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
@@ -107,51 +134,173 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                  : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* r) {
+    uint32_t u[16];
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
         "%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = __uint_as_float(u[i]);
 }
 
-struct EpilogueArgs {
-    void* out;         // [rows of the token operand, ldc]
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
+
+struct GemmParams {
+    int rows_a, rows_b, K;
+    int tiles_a, tiles_b, splits, kb_total;
+    void* out;         // [tokens, ldc]
     const void* bias;  // per output feature, or null
     int out_dt, bias_dt;
     int ldc;
     int accumulate;  // add to what `out` holds
     int swap;        // 0: A rows are tokens; 1: A rows are output features
+    int vec;         // rows of `out` may be written 16 bytes at a time
+    float* scratch;  // partial tiles of the K slices: [tile][slice][BN][128] floats
+    int* tickets;    // one counter per output tile, zero between launches
+    int* status;
 };
 
-template <int BN, int kStages>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int rows_a,
-                 int rows_b, int K, EpilogueArgs ep, int* __restrict__ status) {
+// Stores 16 accumulator values of one thread: A row `a_row`, B rows b0 .. b0 + 15.
+template <int kEpi>
+__device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, float (&v)[16]) {
+    const bool a_ok = a_row < p.rows_a;
+    if (kEpi == kSwiglu) {
+        if (!p.swap) {
+            // columns hold 8 gate values, then the 8 up values of the same outputs
+            if (!a_ok || b0 >= p.rows_b) return;
+            const size_t o = (size_t)a_row * p.ldc + (b0 >> 1);
+            float act[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) act[j] = silu_mul(v[j], v[j + 8]);
+            if (p.vec && p.out_dt == DT_BF16) {
+                __nv_bfloat162 h[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = *reinterpret_cast<uint4*>(h);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) st_f(p.out, o + j, p.out_dt, act[j]);
+            }
+        } else {
+            // rows hold 8 gate rows, then 8 up rows: lane l and lane l ^ 8 hold a pair
+            const bool is_gate = (a_row & 8) == 0;
+            const int feature = (a_row >> 4) * 8 + (a_row & 7);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
+                const int tok = b0 + j;
+                if (is_gate && a_ok && tok < p.rows_b)
+                    st_f(p.out, (size_t)tok * p.ldc + feature, p.out_dt, silu_mul(v[j], other));
+            }
+        }
+        return;
+    }
+    if (!a_ok) return;
+    if (!p.swap) {
+        const size_t o = (size_t)a_row * p.ldc + b0;
+        if (p.vec && b0 + 16 <= p.rows_b) {
+            if (p.bias) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += ld_f(p.bias, b0 + j, p.bias_dt);
+            }
+            if (p.out_dt == DT_F32) {
+                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    if (p.accumulate) {
+                        const float4 y = dst[j];
+                        x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+                    }
+                    dst[j] = x;
+                }
+            } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    __nv_bfloat162 h[4];
+                    if (p.accumulate) {
+                        const uint4 y = *reinterpret_cast<const uint4*>(dst + 8 * half);
+                        const __nv_bfloat162* yh = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __bfloat1622float2(yh[j]);
+                            h[j] = __floats2bfloat162_rn(v[8 * half + 2 * j] + f.x, v[8 * half + 2 * j + 1] + f.y);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            h[j] = __floats2bfloat162_rn(v[8 * half + 2 * j], v[8 * half + 2 * j + 1]);
+                    }
+                    *reinterpret_cast<uint4*>(dst + 8 * half) = *reinterpret_cast<uint4*>(h);
+                }
+            }
+            return;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int col = b0 + j;
+            if (col >= p.rows_b) break;
+            float x = v[j];
+            if (p.bias) x += ld_f(p.bias, col, p.bias_dt);
+            if (p.accumulate) x += ld_f(p.out, o + j, p.out_dt);
+            st_f(p.out, o + j, p.out_dt, x);
+        }
+    } else {
+        // C[b0 + j, a_row]: the lanes of a warp write neighbouring elements
+        const float b = p.bias ? ld_f(p.bias, a_row, p.bias_dt) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int tok = b0 + j;
+            if (tok >= p.rows_b) break;
+            const size_t o = (size_t)tok * p.ldc + a_row;
+            float x = v[j] + b;
+            if (p.accumulate) x += ld_f(p.out, o, p.out_dt);
+            st_f(p.out, o, p.out_dt, x);
+        }
+    }
+}
+
+template <int BN, int kStages, int kEpi>
+__global__ void __launch_bounds__(kThreads)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
     constexpr int kBytesA = kBlockM * kBlockK * 2;
     constexpr int kBytesB = BN * kBlockK * 2;
-    constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    constexpr int kAccCols = BN < 32 ? 32 : BN;   // columns of one accumulator
+    constexpr int kTmemCols = 2 * kAccCols;       // two accumulators; a power of two >= 64
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + kStages * kBytesA;
     uint64_t* full = (uint64_t*)(smem_b + kStages * kBytesB);
     uint64_t* empty = full + kStages;
-    uint64_t* accum_full = empty + kStages;
-    uint32_t* tmem_slot = (uint32_t*)(accum_full + 1);
+    uint64_t* acc_full = empty + kStages;   // [2]
+    uint64_t* acc_empty = acc_full + 2;     // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* last_flag = (volatile int*)(tmem_slot + 1);
+    volatile int* fail_flag = last_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * kBlockM, n0 = blockIdx.y * BN;
-    const int num_kb = (K + kBlockK - 1) / kBlockK;
+    const int n_tiles = p.tiles_a * p.tiles_b;
+    const int n_items = n_tiles * p.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(accum_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -166,93 +315,147 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    // Work item w: output tile (w % tiles_a, (w / tiles_a) % tiles_b), K slice w / n_tiles.
+    // Slice s covers the k-blocks [s * kb_total / splits, (s + 1) * kb_total / splits).
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
+            int kb_run = 0, issued = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t phase = (kb / kStages) & 1;
-                if (!mbar_wait(&empty[s], phase ^ 1)) {
-                    atomicExch(status, kTimeoutEmpty);
-                    ok = false;
-                    break;
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+                const int tile = w % n_tiles, split = w / n_tiles;
+                const int m0 = (tile % p.tiles_a) * kBlockM, n0 = (tile / p.tiles_a) * BN;
+                const int kb0 = (int)((long long)split * p.kb_total / p.splits);
+                const int kb1 = (int)((long long)(split + 1) * p.kb_total / p.splits);
+                for (int kb = kb0; kb < kb1; ++kb, ++kb_run) {
+                    const int s = kb_run % kStages;
+                    if (!mbar_wait(&empty[s], ((kb_run / kStages) & 1) ^ 1)) {
+                        atomicExch(p.status, kTimeoutEmpty);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full[s], kBytesA + kBytesB);
+                    tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                    tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
+                    issued = kb_run + 1;
                 }
-                mbar_expect_tx(&full[s], kBytesA + kBytesB);
-                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
-                tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
-                issued = kb + 1;
             }
             if (!ok) {
                 // let the copies already in flight land before the block gives up its shared memory
-                for (int kb = max(0, issued - kStages); kb < issued; ++kb)
-                    mbar_wait(&full[kb % kStages], (kb / kStages) & 1);
+                for (int r = max(0, issued - kStages); r < issued; ++r) mbar_wait(&full[r % kStages], (r / kStages) & 1);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16(kBlockM, BN);
+            int kb_run = 0, it = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t phase = (kb / kStages) & 1;
-                if (!mbar_wait(&full[s], phase)) {
-                    atomicExch(status, kTimeoutFull);
-                    ok = false;
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++it) {
+                const int split = w / n_tiles;
+                const int kb0 = (int)((long long)split * p.kb_total / p.splits);
+                const int kb1 = (int)((long long)(split + 1) * p.kb_total / p.splits);
+                const int buf = it & 1;
+                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1)) {
+                    atomicExch(p.status, kTimeoutAccumEmpty);
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(smem_a + s * kBytesA);
-                const uint32_t b_addr = smem_u32(smem_b + s * kBytesB);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kAccCols);
+                for (int kb = kb0; kb < kb1; ++kb, ++kb_run) {
+                    const int s = kb_run % kStages;
+                    if (!mbar_wait(&full[s], (kb_run / kStages) & 1)) {
+                        atomicExch(p.status, kTimeoutFull);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem_a + s * kBytesA);
+                    const uint32_t b_addr = smem_u32(smem_b + s * kBytesB);
 #pragma unroll
-                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                    const uint64_t a_desc = smem_desc_sw128(a_addr + k * kUmmaK * 2);
-                    const uint64_t b_desc = smem_desc_sw128(b_addr + k * kUmmaK * 2);
-                    umma_bf16(tmem_base, a_desc, b_desc, idesc, (kb | k) != 0);
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                        const uint64_t a_desc = smem_desc_sw128(a_addr + k * kUmmaK * 2);
+                        const uint64_t b_desc = smem_desc_sw128(b_addr + k * kUmmaK * 2);
+                        umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);
                 }
-                umma_commit(&empty[s]);
+                if (ok) umma_commit(&acc_full[buf]);
             }
-            if (ok) umma_commit(accum_full);
         }
     } else {
         // Epilogue: warp w may read the tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
-        const int a_row = m0 + quarter * 32 + lane;
-        if (!mbar_wait(accum_full, 0)) {
-            if (lane == 0) atomicExch(status, kTimeoutAccum);
-        } else {
+        const int row_in_tile = quarter * 32 + lane;
+        const int ep_tid = threadIdx.x - 64;
+        int it = 0;
+        for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++it) {
+            const int tile = w % n_tiles, split = w / n_tiles;
+            const int m0 = (tile % p.tiles_a) * kBlockM, n0 = (tile / p.tiles_a) * BN;
+            const int a_row = m0 + row_in_tile;
+            const int buf = it & 1;
+            const bool ok = mbar_wait(&acc_full[buf], (it >> 1) & 1);
+            if (!ok && lane == 0) {
+                atomicExch(p.status, kTimeoutAccumFull);
+                *fail_flag = 1;
+            }
             __syncwarp();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kAccCols);
+            if (p.splits == 1) {
+                if (!ok) break;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
-                if (a_row >= rows_a) continue;
-                if (!ep.swap) {
-                    // C[a_row, n0 + c0 + j]
-                    const size_t o = (size_t)a_row * ep.ldc + n0 + c0;
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + (uint32_t)c0, v);
+                    store16<kEpi>(p, a_row, n0 + c0, v);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            } else {
+                // this slice's partial tile, column by column so that a warp writes 128 contiguous bytes
+                float* mine = p.scratch + ((size_t)tile * p.splits + split) * (BN * kBlockM);
+                if (ok) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        tmem_ld16(taddr + (uint32_t)c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int col = n0 + c0 + j;
-                        if (col >= rows_b) break;
-                        float v = __uint_as_float(r[j]);
-                        if (ep.bias) v += ld_f(ep.bias, col, ep.bias_dt);
-                        if (ep.accumulate) v += ld_f(ep.out, o + j, ep.out_dt);
-                        st_f(ep.out, o + j, ep.out_dt, v);
+                        for (int j = 0; j < 16; ++j) mine[(c0 + j) * kBlockM + row_in_tile] = v[j];
                     }
-                } else {
-                    // C[n0 + c0 + j, a_row]: the lanes of a warp write neighbouring elements
-                    const float b = ep.bias ? ld_f(ep.bias, a_row, ep.bias_dt) : 0.0f;
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                }
+                __threadfence();
+                epilogue_bar();  // the four epilogue warps pass every barrier together, also after a failed wait
+                if (ep_tid == 0) {
+                    int last = 0;
+                    if (!*fail_flag) {
+                        const int ticket = atomicAdd(&p.tickets[tile], 1);
+                        last = ticket == p.splits - 1;
+                        if (last) p.tickets[tile] = 0;  // ready for the next launch
+                    }
+                    *last_flag = last;
+                }
+                epilogue_bar();
+                if (*last_flag) {
+                    __threadfence();
+                    const float* all = p.scratch + (size_t)tile * p.splits * (BN * kBlockM);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int tok = n0 + c0 + j;
-                        if (tok >= rows_b) break;
-                        const size_t o = (size_t)tok * ep.ldc + a_row;
-                        float v = __uint_as_float(r[j]) + b;
-                        if (ep.accumulate) v += ld_f(ep.out, o, ep.out_dt);
-                        st_f(ep.out, o, ep.out_dt, v);
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                        for (int s = 0; s < p.splits; ++s) {
+                            const float* src = all + (size_t)s * (BN * kBlockM) + c0 * kBlockM + row_in_tile;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + j * kBlockM);
+                        }
+                        store16<kEpi>(p, a_row, n0 + c0, v);
                     }
                 }
+                epilogue_bar();  // the flags are read before the next item overwrites them
+                if (*fail_flag) break;
             }
         }
     }
@@ -322,22 +525,47 @@ struct MapCache {
 
 MapCache g_maps;
 
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v > 0 ? v : 148;
+    }();
+    return n;
+}
+
 template <int BN, int kStages>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, int rows_a, int rows_b, int K, const EpilogueArgs& ep,
-           int* status, cudaStream_t stream) {
-    constexpr size_t smem = 1024 + (size_t)kStages * (kBlockM * kBlockK * 2 + BN * kBlockK * 2) +
-                            (2 * kStages + 1) * sizeof(uint64_t) + 16;
+constexpr size_t smem_bytes() {
+    return 1024 + (size_t)kStages * (kBlockM * kBlockK * 2 + BN * kBlockK * 2) + (2 * kStages + 4) * sizeof(uint64_t) + 16;
+}
+
+template <int BN, int kStages, int kEpi>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int blocks_per_sm, cudaStream_t stream) {
+    constexpr size_t smem = smem_bytes<BN, kStages>();
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e =
-            cudaFuncSetAttribute(gemm_bf16_kernel<BN, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, kStages, kEpi>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((rows_a + kBlockM - 1) / kBlockM, (rows_b + BN - 1) / BN);
-    gemm_bf16_kernel<BN, kStages><<<grid, kThreads, smem, stream>>>(ma, mb, rows_a, rows_b, K, ep, status);
+    const int n_items = p.tiles_a * p.tiles_b * p.splits;
+    const int grid = n_items < blocks_per_sm * sm_count() ? n_items : blocks_per_sm * sm_count();
+    gemm_bf16_kernel<BN, kStages, kEpi><<<grid, kThreads, smem, stream>>>(ma, mb, p);
     NN_LAUNCH_OK("gemm_bf16");
     return 0;
+}
+
+template <int kEpi>
+int dispatch(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
+    switch (bn) {
+        case 16: return launch<16, 4, kEpi>(ma, mb, p, 3, stream);
+        case 32: return launch<32, 4, kEpi>(ma, mb, p, 2, stream);
+        case 64: return launch<64, 4, kEpi>(ma, mb, p, 2, stream);
+        case 128: return launch<128, 6, kEpi>(ma, mb, p, 1, stream);
+        default: return launch<256, 4, kEpi>(ma, mb, p, 1, stream);
+    }
 }
 
 }  // namespace
@@ -348,38 +576,67 @@ extern "C" int nncpu_linear_tc_supported(int M, int N, int K, int lda) {
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0;
 }
 
-// C[M, N] (+)= X[M, K] . W[N, K]^T + bias.  X and W are bfloat16; C is float or
-// bfloat16 with row stride ldc; `status` is a device word that a kernel sets
-// when one of its bounded waits ran out (the host checks it when it next
-// synchronises).
+// Floats of scratch and number of tickets a workspace must hold for any product
+// this library launches with at most `max_n` output features.
+extern "C" long nncpu_linear_tc_scratch_floats() { return 4l << 20; }  // 16 MiB
+extern "C" int nncpu_linear_tc_tickets() { return 8192; }
+
+// C[M, N] (+)= X[M, K] . W[N, K]^T + bias, or with epilogue 1: C[M, N/2] = silu(gate) * up for W rows
+// interleaved in blocks of 8 (8 gate rows, the 8 up rows of the same outputs, ...).  X and W are
+// bfloat16; C is float or bfloat16 with row stride ldc.  `scratch` (nncpu_linear_tc_scratch_floats
+// floats) and `tickets` (nncpu_linear_tc_tickets ints, zero before the first launch) serve the
+// products that cut K into slices; launches that share them must not overlap on the GPU.  `status`
+// is a device word that a kernel sets when one of its bounded waits ran out.
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
-                               int N, int K, int lda, int ldc, int accumulate, int* status, void* stream_) {
+                               int N, int K, int lda, int ldc, int accumulate, int epilogue, float* scratch,
+                               int* tickets, int* status, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(nncpu_linear_tc_supported(M, N, K, lda),
              "gemm: M %d, N %d, K %d, lda %d: K and lda must be multiples of 8 for the tensor-core path", M, N, K, lda);
     NN_CHECK(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm: operands must be 16-byte aligned");
-    NN_CHECK(ldc >= N, "gemm: ldc %d is below N %d", ldc, N);
-    EpilogueArgs ep{C, bias, c_dt, bias_dt, ldc, accumulate, 0};
+    NN_CHECK(epilogue == kPlain || epilogue == kSwiglu, "gemm: unknown epilogue %d", epilogue);
+    const int n_out = epilogue == kSwiglu ? N / 2 : N;
+    NN_CHECK(ldc >= n_out, "gemm: ldc %d is below the %d output features", ldc, n_out);
+    if (epilogue == kSwiglu)
+        NN_CHECK(N % 16 == 0 && bias == nullptr && !accumulate,
+                 "gemm: the gated epilogue needs N %% 16 == 0, no bias and no accumulation (N %d)", N);
+    GemmParams p{};
+    p.K = K;
+    p.kb_total = (K + kBlockK - 1) / kBlockK;
+    p.out = C; p.bias = bias; p.out_dt = c_dt; p.bias_dt = bias_dt; p.ldc = ldc; p.accumulate = accumulate;
+    p.scratch = scratch; p.tickets = tickets; p.status = status;
+    const int esize = c_dt == DT_F32 ? 4 : 2;
+    p.vec = ((uintptr_t)C % 16 == 0) && ((size_t)ldc * esize % 16 == 0);
     CUtensorMap ma, mb;
+    int bn;
     if (M <= 256) {
         // few tokens: weights are the 128-row operand, tokens the narrow one
-        ep.swap = 1;
-        const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        p.swap = 1;
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        p.rows_a = N; p.rows_b = M;
         if (int e = g_maps.get(&ma, W, N, K, K, kBlockM)) return e;
         if (int e = g_maps.get(&mb, X, M, K, lda, bn)) return e;
-        switch (bn) {
-            case 16: return launch<16, 8>(ma, mb, N, M, K, ep, status, stream);
-            case 32: return launch<32, 8>(ma, mb, N, M, K, ep, status, stream);
-            case 64: return launch<64, 8>(ma, mb, N, M, K, ep, status, stream);
-            case 128: return launch<128, 6>(ma, mb, N, M, K, ep, status, stream);
-            default: return launch<256, 4>(ma, mb, N, M, K, ep, status, stream);
-        }
+    } else {
+        p.swap = 0;
+        bn = N >= 256 ? 256 : 128;
+        p.rows_a = M; p.rows_b = N;
+        if (int e = g_maps.get(&ma, X, M, K, lda, kBlockM)) return e;
+        if (int e = g_maps.get(&mb, W, N, K, K, bn)) return e;
     }
-    if (int e = g_maps.get(&ma, X, M, K, lda, kBlockM)) return e;
-    if (N >= 256) {
-        if (int e = g_maps.get(&mb, W, N, K, K, 256)) return e;
-        return launch<256, 4>(ma, mb, M, N, K, ep, status, stream);
+    p.tiles_a = (p.rows_a + kBlockM - 1) / kBlockM;
+    p.tiles_b = (p.rows_b + bn - 1) / bn;
+    // Cut K into slices when there are too few tiles to occupy the GPU: aim at about two blocks per SM,
+    // keep at least 4 k-blocks per slice, and stay inside the workspace.
+    const int n_tiles = p.tiles_a * p.tiles_b;
+    int splits = 1;
+    if (bn <= 64 && scratch != nullptr && tickets != nullptr && n_tiles <= nncpu_linear_tc_tickets()) {
+        const int want = (2 * sm_count() + n_tiles - 1) / n_tiles;
+        splits = want < 1 ? 1 : want;
+        if (splits > p.kb_total / 4) splits = p.kb_total / 4;
+        const long per_tile = (long)bn * kBlockM;
+        while (splits > 1 && (long)n_tiles * splits * per_tile > nncpu_linear_tc_scratch_floats()) --splits;
+        if (splits < 1) splits = 1;
     }
-    if (int e = g_maps.get(&mb, W, N, K, K, 128)) return e;
-    return launch<128, 6>(ma, mb, M, N, K, ep, status, stream);
+    p.splits = splits;
+    return epilogue == kSwiglu ? dispatch<kSwiglu>(bn, ma, mb, p, stream) : dispatch<kPlain>(bn, ma, mb, p, stream);
 }

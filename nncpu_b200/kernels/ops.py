@@ -104,14 +104,35 @@ def linear_tc_supported(m: int, n: int, k: int) -> bool:
     return m > 0 and k % 8 == 0
 
 
-def linear_tc(x, w, bias, out, status, accumulate: bool = False) -> None:
-    """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16."""
+class GemmWorkspace:
+    """Device memory the tensor-core product needs besides its operands:
+    scratch for the partial tiles of products that cut K into slices, one
+    ticket counter per output tile, and the status word that a kernel sets when
+    a bounded wait ran out.  Launches that share a workspace must not overlap
+    on the GPU (one stream)."""
+
+    def __init__(self, device):
+        lib = library.load("gemm_sm100")
+        lib.nncpu_linear_tc_scratch_floats.restype = ctypes.c_long
+        self.scratch = torch.empty(lib.nncpu_linear_tc_scratch_floats(), dtype=torch.float32, device=device)
+        self.tickets = torch.zeros(lib.nncpu_linear_tc_tickets(), dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+EPILOGUES = {"plain": 0, "swiglu": 1}
+
+
+def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = False, epilogue: str = "plain") -> None:
+    """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16.  With
+    ``epilogue="swiglu"`` the rows of w hold gate and up rows interleaved in
+    blocks of 8 and out [m, n/2] receives silu(gate) * up."""
     m, k = x.shape
     n = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    assert w.shape[1] == k and out.shape == (m, n) and status.dtype == torch.int32
+    assert w.shape[1] == k and out.shape == (m, n // 2 if epilogue == "swiglu" else n)
     _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
-          _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(n), _i(accumulate), _ptr(status), _stream())
+          _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
+          _ptr(workspace.scratch), _ptr(workspace.tickets), _ptr(workspace.status), _stream())
 
 
 def rope_table(positions, inv_freq, out, position_scale: float = 1.0) -> None:

@@ -28,8 +28,17 @@ class GatedMlp(FeedForward):
 
     def bind(self, tensors, rt):
         s, self.rt = self.spec, rt
-        self.w_gate_up = torch.cat([tensors.pop(f"{s.name}.gate_proj.weight"),
-                                    tensors.pop(f"{s.name}.up_proj.weight")], dim=0).contiguous()
+        gate, up = tensors.pop(f"{s.name}.gate_proj.weight"), tensors.pop(f"{s.name}.up_proj.weight")
+        # On the tensor-core path the activation runs in the product's epilogue, on the 32-bit
+        # accumulators; for that, gate and up rows are interleaved in blocks of 8.
+        self.fused = (gate.dtype == up.dtype and s.intermediate_size % 8 == 0
+                      and rt.tensor_cores_take(rt.dtype, gate, s.hidden_size))
+        if self.fused:
+            h = s.hidden_size
+            self.w_gate_up = torch.stack([gate.view(-1, 8, h), up.view(-1, 8, h)], dim=1).reshape(-1, h).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        del gate, up
         self.w_down = tensors[f"{s.name}.down_proj.weight"]
 
     def weight_bytes(self):
@@ -38,8 +47,11 @@ class GatedMlp(FeedForward):
     def forward(self, ctx, x, residual):
         s, rt = self.spec, self.rt
         n = x.shape[0]
-        gate_up = rt.empty(n, 2 * s.intermediate_size)
-        rt.linear(x, self.w_gate_up, None, gate_up)
         act = rt.empty(n, s.intermediate_size)
-        ops.swiglu(gate_up, act)
+        if self.fused:
+            rt.linear(x, self.w_gate_up, None, act, epilogue="swiglu")
+        else:
+            gate_up = rt.empty(n, 2 * s.intermediate_size)
+            rt.linear(x, self.w_gate_up, None, gate_up)
+            ops.swiglu(gate_up, act)
         rt.linear(act, self.w_down, None, residual, accumulate=True)

@@ -85,7 +85,7 @@ def test_linear_tensor_core(ops, m, n, k):
     x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
     w = (torch.randn(n, k, generator=g) * 0.1).bfloat16().to(DEV)
     b = torch.randn(n, generator=g).to(DEV)
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = ops.GemmWorkspace(DEV)
     want = (x.double() @ w.double().T).float()
     out = torch.full((m, n), 9.0, device=DEV)
     ops.linear_tc(x, w, b, out, status)
@@ -96,7 +96,43 @@ def test_linear_tensor_core(ops, m, n, k):
     acc = torch.full((m, n), 0.5, device=DEV)
     ops.linear_tc(x, w, None, acc, status, accumulate=True)
     check(acc, want + 0.5, 1e-5, "tensor-core linear, accumulate")
-    assert int(status.item()) == 0
+    accb = torch.full((m, n), 0.5, dtype=torch.bfloat16, device=DEV)
+    ops.linear_tc(x, w, None, accb, status, accumulate=True)
+    check(accb, want + 0.5, 8e-3, "tensor-core linear, accumulate in bfloat16")
+    assert int(status.status.item()) == 0 and int(status.tickets.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 8, 64), (7, 136, 80), (64, 12288, 512), (100, 1000, 264), (300, 320, 128),
+                                       (1000, 2048, 1024)])
+def test_linear_tensor_core_with_gated_epilogue(ops, m, inter, k):
+    g = torch.Generator().manual_seed(m + inter)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    gate = (torch.randn(inter, k, generator=g) * 0.1).bfloat16()
+    up = (torch.randn(inter, k, generator=g) * 0.1).bfloat16()
+    w = torch.stack([gate.view(-1, 8, k), up.view(-1, 8, k)], dim=1).reshape(-1, k).contiguous()
+    want = P.swiglu((x.double() @ gate.double().T).float().numpy(), (x.double() @ up.double().T).float().numpy())
+    ws = ops.GemmWorkspace(DEV)
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 8e-3)):
+        out = torch.full((m, inter), 9.0, dtype=dt, device=DEV)
+        ops.linear_tc(x.to(DEV), w.to(DEV), None, out, ws, epilogue="swiglu")
+        check(out, want, tol, "gated epilogue")
+    assert int(ws.status.item()) == 0
+
+
+def test_linear_tensor_core_is_repeatable_and_row_independent(ops):
+    # K is cut into slices for few tokens: the slices are added in slice order, so runs agree bit for bit
+    x = torch.randn(8, 4096).bfloat16().to(DEV)
+    w = (torch.randn(512, 4096) * 0.05).bfloat16().to(DEV)
+    ws = ops.GemmWorkspace(DEV)
+    outs = []
+    for _ in range(5):
+        out = torch.empty(8, 512, device=DEV)
+        ops.linear_tc(x, w, None, out, ws)
+        outs.append(out)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    one = torch.empty(1, 512, device=DEV)
+    ops.linear_tc(x[3:4].contiguous(), w, None, one, ws)
+    assert torch.equal(one[0], outs[0][3])
 
 
 def test_linear_tensor_core_refuses_unaligned(ops):
@@ -104,7 +140,7 @@ def test_linear_tensor_core_refuses_unaligned(ops):
     w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
     assert not ops.linear_tc_supported(4, 8, 20)
     with pytest.raises(ExtensionError, match="multiples of 8"):
-        ops.linear_tc(x, w, None, torch.empty(4, 8, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
+        ops.linear_tc(x, w, None, torch.empty(4, 8, device=DEV), ops.GemmWorkspace(DEV))
 
 
 def test_rope_table(ops):
