@@ -1,0 +1,184 @@
+// bfloat16 matrix product for very few tokens (at most 16):
+//   C[M, N] (+)= X[M, K] . W[N, K]^T (+ bias[N])      or      C[M, N/2] = silu(gate) * up
+// With so few tokens the product is a stream over the weights and nothing
+// else matters but keeping every SM's loads in flight: a block owns 16 weight
+// rows, its eight warps each take an eighth of K, and every lane reads its
+// rows 16 bytes at a time straight from global memory into the registers that
+// feed mma.sync (m16n8k16: the 16 rows are weight rows, the 8 columns tokens).
+// No shared-memory staging, no barriers in the stream, no scratch memory; the
+// eight partial sums meet in shared memory and are added in warp order, so the
+// result does not depend on timing.
+//
+// The 16 bytes a lane loads are 8 consecutive k of one row; the tensor core
+// wants k pairs (2c, 2c+1, 2c+8, 2c+9) per lane.  Because a dot product does
+// not care in which order k runs, weights and activations are simply loaded
+// the same way and fed as if they were in the layout the instruction expects.
+//
+// The reference computes these products with its BF16 row kernels
+// (crates/nncpu/src/kernels/mod.rs:337-360, crates/nncpu/src/kernels/scalar.rs:555-567).
+
+#include <math.h>
+
+#define NN_LIB linear_skinny
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kRows = 16;     // weight rows per block
+constexpr int kUnroll = 8;    // 32-wide k groups in flight per warp
+
+enum Epilogue : int { kPlain = 0, kSwiglu = 1 };
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Weights are read once: stream them past the caches.
+__device__ __forceinline__ uint4 ldg16_stream(const __nv_bfloat16* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
+
+// NT = number of 8-token tiles (1: up to 8 tokens, 2: up to 16).
+template <int NT, int kEpi>
+__global__ void __launch_bounds__(kWarps * 32, 2)
+skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, const void* __restrict__ bias,
+              int bias_dt, void* __restrict__ out, int out_dt, int M, int N, int K, int lda, int ldc, int accumulate) {
+    __shared__ float part[kWarps][kRows][NT * 8 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = lane & 3, r = lane >> 2;
+    const int row0 = blockIdx.x * kRows;
+    const int row_lo = row0 + r, row_hi = row0 + r + 8;
+    const __nv_bfloat16* w_lo = W + (size_t)min(row_lo, N - 1) * K;
+    const __nv_bfloat16* w_hi = W + (size_t)min(row_hi, N - 1) * K;
+    const __nv_bfloat16* x0 = X + (size_t)min(r, M - 1) * lda;
+    const __nv_bfloat16* x1 = X + (size_t)min(r + 8, M - 1) * lda;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+
+    // this warp's share of K, in groups of 32
+    const int n_groups = (K + 31) / 32;
+    const int per_warp = (n_groups + kWarps - 1) / kWarps;
+    const int g_begin = warp * per_warp, g_end = min(n_groups, g_begin + per_warp);
+    // Full blocks of kUnroll groups: every load is issued before the first product, without predicates.
+    // Columns of tokens beyond M read a valid row and are never stored.
+    const int k_full = K / 32;                        // groups that lie wholly inside K
+    const int g_fast_end = min(g_end, k_full);
+    int g0 = g_begin;
+    for (; g0 + kUnroll <= g_fast_end; g0 += kUnroll) {
+        uint4 a_lo[kUnroll], a_hi[kUnroll], b0[kUnroll], b1[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int k = (g0 + u) * 32 + c * 8;
+            a_lo[u] = ldg16_stream(w_lo + k);
+            a_hi[u] = ldg16_stream(w_hi + k);
+            b0[u] = *reinterpret_cast<const uint4*>(x0 + k);
+            if (NT > 1) b1[u] = *reinterpret_cast<const uint4*>(x1 + k);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            mma_bf16(acc[0], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b0[u].x, b0[u].y);
+            mma_bf16(acc[0], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b0[u].z, b0[u].w);
+            if (NT > 1) {
+                mma_bf16(acc[1], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b1[u].x, b1[u].y);
+                mma_bf16(acc[1], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b1[u].z, b1[u].w);
+            }
+        }
+    }
+    // The rest, one group at a time; K is a multiple of 8, so a 16-byte chunk is inside K or outside.
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (; g0 < g_end; ++g0) {
+        const int k = g0 * 32 + c * 8;
+        const bool ok = k < K;
+        const uint4 a_lo = ok ? ldg16_stream(w_lo + k) : z, a_hi = ok ? ldg16_stream(w_hi + k) : z;
+        const uint4 b0 = ok ? *reinterpret_cast<const uint4*>(x0 + k) : z;
+        mma_bf16(acc[0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b0.x, b0.y);
+        mma_bf16(acc[0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b0.z, b0.w);
+        if (NT > 1) {
+            const uint4 b1 = ok ? *reinterpret_cast<const uint4*>(x1 + k) : z;
+            mma_bf16(acc[1], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b1.x, b1.y);
+            mma_bf16(acc[1], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b1.z, b1.w);
+        }
+    }
+    // accumulator layout: [0..1] row r, tokens 2c, 2c+1; [2..3] row r + 8
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        part[warp][r][t * 8 + 2 * c] = acc[t][0];
+        part[warp][r][t * 8 + 2 * c + 1] = acc[t][1];
+        part[warp][r + 8][t * 8 + 2 * c] = acc[t][2];
+        part[warp][r + 8][t * 8 + 2 * c + 1] = acc[t][3];
+    }
+    __syncthreads();
+    if (kEpi == kSwiglu) {
+        // rows 0..7 of the block are gate rows, rows 8..15 the up rows of the same outputs
+        for (int i = threadIdx.x; i < 8 * M; i += kWarps * 32) {
+            const int tok = i / 8, j = i % 8;
+            if (row0 + j + 8 >= N) continue;
+            float g = 0.0f, u = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                g += part[w][j][tok];
+                u += part[w][j + 8][tok];
+            }
+            st_f(out, (size_t)tok * ldc + (row0 >> 1) + j, out_dt, silu_mul(g, u));
+        }
+    } else {
+        for (int i = threadIdx.x; i < kRows * M; i += kWarps * 32) {
+            const int tok = i / kRows, j = i % kRows;
+            const int row = row0 + j;
+            if (row >= N) continue;
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) v += part[w][j][tok];
+            if (bias) v += ld_f(bias, row, bias_dt);
+            const size_t o = (size_t)tok * ldc + row;
+            if (accumulate) v += ld_f(out, o, out_dt);
+            st_f(out, o, out_dt, v);
+        }
+    }
+}
+
+template <int NT, int kEpi>
+int launch(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M, int N, int K, int lda,
+           int ldc, int accumulate, cudaStream_t stream) {
+    const int blocks = (N + kRows - 1) / kRows;
+    skinny_kernel<NT, kEpi><<<blocks, kWarps * 32, 0, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias,
+                                                                bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate);
+    NN_LAUNCH_OK("linear_skinny");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int nncpu_linear_skinny_supported(int M, int N, int K, int lda) {
+    return M > 0 && M <= 16 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0;
+}
+
+// C[M, N] (+)= X[M, K] . W[N, K]^T + bias for M <= 16, or with epilogue 1: C[M, N/2] = silu(gate) * up
+// for W rows interleaved in blocks of 8.  X and W are bfloat16 and 16-byte aligned; C is float or bfloat16.
+extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt,
+                                   int M, int N, int K, int lda, int ldc, int accumulate, int epilogue, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    NN_CHECK(nncpu_linear_skinny_supported(M, N, K, lda),
+             "linear (few tokens): M %d, N %d, K %d, lda %d: at most 16 tokens, K and lda multiples of 8", M, N, K, lda);
+    NN_CHECK(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "linear (few tokens): operands must be 16-byte aligned");
+    NN_CHECK(epilogue == kPlain || epilogue == kSwiglu, "linear (few tokens): unknown epilogue %d", epilogue);
+    const int n_out = epilogue == kSwiglu ? N / 2 : N;
+    NN_CHECK(ldc >= n_out, "linear (few tokens): ldc %d is below the %d output features", ldc, n_out);
+    if (epilogue == kSwiglu) {
+        NN_CHECK(N % 16 == 0 && bias == nullptr && !accumulate,
+                 "linear (few tokens): the gated epilogue needs N %% 16 == 0, no bias and no accumulation (N %d)", N);
+        return M <= 8 ? launch<1, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream)
+                      : launch<2, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream);
+    }
+    return M <= 8 ? launch<1, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream)
+                  : launch<2, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream);
+}

@@ -135,6 +135,21 @@ def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = Fals
           _ptr(workspace.scratch), _ptr(workspace.tickets), _ptr(workspace.status), _stream())
 
 
+SKINNY_MAX_TOKENS = 16
+
+
+def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "plain") -> None:
+    """The same product for at most 16 tokens: a stream over the weights that
+    uses every SM, with no scratch memory."""
+    m, k = x.shape
+    n = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert w.shape[1] == k and out.shape == (m, n // 2 if epilogue == "swiglu" else n)
+    _call("linear_skinny", "nncpu_linear_skinny", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
+          _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
+          _stream())
+
+
 def rope_table(positions, inv_freq, out, position_scale: float = 1.0) -> None:
     """out[t, i] = (cos, sin)(positions[t] * position_scale * inv_freq[i]); out float32 [n, half, 2]."""
     n, half, two = out.shape

@@ -38,7 +38,10 @@ class Runtime:
         alignment rule go to the tensor cores; everything else, and every
         float32 product, runs in true 32-bit on CUDA cores."""
         if self.tensor_cores_take(x.dtype, w, x.shape[1]):
-            ops.linear_tc(x, w, bias, out, self.workspace, accumulate, epilogue)
+            if x.shape[0] <= ops.SKINNY_MAX_TOKENS:
+                ops.linear_skinny(x, w, bias, out, accumulate, epilogue)
+            else:
+                ops.linear_tc(x, w, bias, out, self.workspace, accumulate, epilogue)
         else:
             assert epilogue == "plain", "the fused epilogue exists on the tensor-core path only"
             ops.linear_simt(x, w, bias, out, accumulate)

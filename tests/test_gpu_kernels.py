@@ -135,6 +135,53 @@ def test_linear_tensor_core_is_repeatable_and_row_independent(ops):
     assert torch.equal(one[0], outs[0][3])
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 16, 32), (1, 307, 80), (3, 6144, 4096), (8, 100, 264), (9, 64, 4096),
+                                   (16, 1000, 1096), (5, 24, 8)])
+def test_linear_for_few_tokens(ops, m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.1).bfloat16().to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    want = (x.double() @ w.double().T).float()
+    out = torch.full((m, n), 9.0, device=DEV)
+    ops.linear_skinny(x, w, b, out)
+    check(out, want + b, 1e-5, "few tokens, float32 out")
+    outb = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.linear_skinny(x, w, b.bfloat16(), outb)
+    check(outb, want + b.bfloat16().float(), 8e-3, "few tokens, bfloat16 out")
+    acc = torch.full((m, n), 0.5, device=DEV)
+    ops.linear_skinny(x, w, None, acc, accumulate=True)
+    check(acc, want + 0.5, 1e-5, "few tokens, accumulate")
+    again = torch.full((m, n), 0.5, device=DEV)
+    ops.linear_skinny(x, w, None, again, accumulate=True)
+    assert torch.equal(acc, again)                            # the same bits every time
+    if m > 1:                                                 # a row does not depend on its neighbours
+        one = torch.empty(1, n, device=DEV)
+        ops.linear_skinny(x[m - 1:].contiguous(), w, b, one)
+        assert torch.equal(one[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 8, 64), (7, 136, 80), (8, 12288, 512), (13, 1000, 264), (16, 320, 4096)])
+def test_linear_for_few_tokens_with_gated_epilogue(ops, m, inter, k):
+    g = torch.Generator().manual_seed(m + inter)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    gate = (torch.randn(inter, k, generator=g) * 0.1).bfloat16()
+    up = (torch.randn(inter, k, generator=g) * 0.1).bfloat16()
+    w = torch.stack([gate.view(-1, 8, k), up.view(-1, 8, k)], dim=1).reshape(-1, k).contiguous()
+    want = P.swiglu((x.double() @ gate.double().T).float().numpy(), (x.double() @ up.double().T).float().numpy())
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 8e-3)):
+        out = torch.full((m, inter), 9.0, dtype=dt, device=DEV)
+        ops.linear_skinny(x.to(DEV), w.to(DEV), None, out, epilogue="swiglu")
+        check(out, want, tol, "few tokens, gated epilogue")
+
+
+def test_linear_for_few_tokens_refuses(ops):
+    x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ExtensionError, match="at most 16 tokens"):
+        ops.linear_skinny(x, w, None, torch.empty(17, 8, device=DEV))
+
+
 def test_linear_tensor_core_refuses_unaligned(ops):
     x = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
