@@ -446,7 +446,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                        for (int s = 0; s < p.splits; ++s) {
+                        // slices are added in slice order; two slices' loads are in flight at a time
+                        int s = 0;
+                        for (; s + 2 <= p.splits; s += 2) {
+                            const float* src = all + (size_t)s * (BN * kBlockM) + c0 * kBlockM + row_in_tile;
+                            float x0[16], x1[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                x0[j] = __ldcg(src + j * kBlockM);
+                                x1[j] = __ldcg(src + BN * kBlockM + j * kBlockM);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = (v[j] + x0[j]) + x1[j];
+                        }
+                        if (s < p.splits) {
                             const float* src = all + (size_t)s * (BN * kBlockM) + c0 * kBlockM + row_in_tile;
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + j * kBlockM);
@@ -633,6 +646,8 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         const int want = (2 * sm_count() + n_tiles - 1) / n_tiles;
         splits = want < 1 ? 1 : want;
         if (splits > p.kb_total / 4) splits = p.kb_total / 4;
+        const int cap = bn <= 16 ? 16 : bn <= 32 ? 6 : 4;   // wider partial tiles cost more to write and add
+        if (splits > cap) splits = cap;
         const long per_tile = (long)bn * kBlockM;
         while (splits > 1 && (long)n_tiles * splits * per_tile > nncpu_linear_tc_scratch_floats()) --splits;
         if (splits < 1) splits = 1;
