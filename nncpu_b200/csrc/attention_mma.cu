@@ -24,6 +24,7 @@
 //   * prefill: one warp per (16 consecutive tokens of a sequence, head).
 
 #include <math.h>
+#include <mutex>
 
 #define NN_LIB attention_mma
 #include "common.cuh"
@@ -495,4 +496,84 @@ extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, c
                                   n_heads, n_kv, scale, window, (cudaStream_t)stream);
     return launch_prefill<128>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,
                                n_heads, n_kv, scale, window, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that cannot bring scratch memory.
+// Declared in attention_mma_static.h; it has no counterpart in the reference.
+//
+// nncpu_attention_decode_mma merges its key splits through a scratch buffer
+// that the caller allocates.  Some callers have no way to allocate device
+// memory: a host that has already given every free byte of the GPU to its own
+// cache and weight pools, so that cudaMalloc fails; a plugin or foreign-language
+// binding that is handed raw device pointers and owns no allocator; a real-time
+// loop that must not enter the driver's allocator because that can stall the
+// whole device.  For them the scratch lives in this library's own image: a
+// file-scope __device__ array of kStaticScratchFloats floats (4 MiB), which
+// every GPU that loads the library holds until the process exits.
+//
+// In host code the array's name is only a host-side stand-in for the device
+// symbol, not a device address, so the address is looked up with
+// cudaGetSymbolAddress: once per device, with that device current, on the
+// first call made on that device.  That first call does this set-up; make it
+// before any stream capture begins.  The entry point calls no cudaMalloc,
+// cudaFree or other allocating routine.
+//
+// All calls on a device share the one array, and the array keeps what the last
+// call left in it.  Nothing in it has to start at zero: every split writes its
+// whole partial result (a split without keys writes "no keys") before the
+// merge kernel of the same call reads it, so stale contents are never read.
+// Two calls that overlap on the GPU (different streams, or graphs replayed
+// side by side) would write the same floats and race: keep calls on a device
+// in one stream, or order them yourself.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr long kStaticScratchFloats = 1l << 20;  // 4 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_lock;
+float* g_static_ptr[kMaxDevices] = {};
+
+// The device address of g_static_scratch on the current device.
+int static_scratch(float** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    NN_CHECK(e == cudaSuccess && dev >= 0 && dev < kMaxDevices, "attention decode (static scratch): no usable current device (%s)",
+             cudaGetErrorString(e));
+    std::lock_guard<std::mutex> g(g_static_lock);
+    if (g_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        NN_CHECK(e == cudaSuccess && p != nullptr, "attention decode (static scratch): cudaGetSymbolAddress failed on device %d: %s", dev,
+                 cudaGetErrorString(e));
+        g_static_ptr[dev] = static_cast<float*>(p);
+    }
+    *ptr = g_static_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" long nncpu_attention_decode_mma_static_max_floats() { return kStaticScratchFloats; }
+
+extern "C" int nncpu_attention_decode_mma_static(const void* q, const void* k_pages, const void* v_pages,
+                                                 const int* block_table, int bt_stride, const int* tok_seq,
+                                                 const int* tok_pos, void* out, int n_tok, int n_heads, int n_kv,
+                                                 int hd, float scale, int window, int n_splits, void* stream) {
+    NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
+             "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
+             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+    NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (static scratch): %d tokens, %d splits", n_tok,
+             n_splits);
+    const long need = nncpu_attention_decode_scratch_floats(n_tok, n_heads, n_kv, hd, n_splits);
+    NN_CHECK(need <= kStaticScratchFloats,
+             "attention decode (static scratch): %d tokens x %d key/value heads x %d splits need %ld floats of scratch, "
+             "the built-in buffer holds %ld; use fewer splits or tokens per call, or nncpu_attention_decode_mma with "
+             "scratch of your own", n_tok, n_kv, n_splits, need, kStaticScratchFloats);
+    float* scratch = nullptr;
+    if (int e = static_scratch(&scratch)) return e;
+    return nncpu_attention_decode_mma(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch,
+                                      kStaticScratchFloats, n_tok, n_heads, n_kv, hd, scale, window, n_splits, stream);
 }
