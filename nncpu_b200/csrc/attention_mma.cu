@@ -194,6 +194,21 @@ __device__ __forceinline__ void consume_group(Acc<HD>& acc, const uint32_t (&qa)
         }
 }
 
+// Asks for the K and V rows of the group at k0 to be brought into L2: one 128-byte line per lane.
+// Loads in registers bound how many bytes a warp can have in flight; prefetches do not.
+template <int HD>
+__device__ __forceinline__ void prefetch_group(const Pages& pg, int k0, int key_lo, int key_hi, int lane) {
+    constexpr int kLinesPerRow = HD * 2 / 128;         // 2 for head size 128, 1 for 64
+    const int key = k0 + lane / kLinesPerRow;
+    if (lane < 16 * kLinesPerRow && key >= key_lo && key <= key_hi) {
+        const size_t off = pg.row<HD>(key) + (size_t)(lane % kLinesPerRow) * 64;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pg.k + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pg.v + off));
+    }
+}
+
+constexpr int kPrefetchAhead = 4;   // groups of 16 keys ahead of the one being loaded
+
 // Runs the groups first_group, first_group + stride, ... that overlap [key_lo, key_hi].
 template <int HD>
 __device__ __forceinline__ void run_keys(Acc<HD>& acc, const uint32_t (&qa)[HD / 16][4], const Pages& pg, int key_lo,
@@ -203,10 +218,15 @@ __device__ __forceinline__ void run_keys(Acc<HD>& acc, const uint32_t (&qa)[HD /
     int gi = first_group;
     if (gi > last_group) return;
     Group<HD> cur, nxt;
+#pragma unroll
+    for (int a = 1; a <= kPrefetchAhead; ++a)
+        if (gi + a * stride <= last_group) prefetch_group<HD>(pg, (gi + a * stride) << 4, key_lo, key_hi, lane);
     load_group<HD>(cur, pg, gi << 4, key_lo, key_hi, lane);
     while (true) {
         const int gn = gi + stride;
         const bool more = gn <= last_group;
+        if (gn + kPrefetchAhead * stride <= last_group)
+            prefetch_group<HD>(pg, (gn + kPrefetchAhead * stride) << 4, key_lo, key_hi, lane);
         if (more) load_group<HD>(nxt, pg, gn << 4, key_lo, key_hi, lane);
         consume_group<HD>(acc, qa, cur, gi << 4, lo, hi, scale2, lane);
         if (!more) break;
@@ -223,8 +243,147 @@ __device__ __forceinline__ int out_dim(int t, int e, int lane) {
 
 // ---------------------------------------------------------------------------
 // Decode: one token per sequence.  grid = (n_splits, n_kv, n_tok), 128 threads.
+//
+// With one query per head there are only G = heads / kv-heads rows to fill a
+// 16-row tensor-core tile, so the decode kernel turns the products around:
+//   S^T[16 keys, 8 heads]  = K[16 keys, HD]      . Q^T[HD, 8 heads]
+//   O^T[HD,      8 heads] += V^T[HD, 16 keys]    . P^T[16 keys, 8 heads]
+// Keys fill the 16 rows, the heads that share the key/value head are the 8
+// columns (a second column tile serves 9 to 16 heads).  P^T reaches the layout
+// of a right-hand operand through movmatrix (an 8x8 transpose across the warp).
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// Registers of one group of 16 keys for the decode formulation: key rows (lane / 4) and (lane / 4 + 8)
+// of K, and the value rows of the keys 2c, 2c + 1, 2c + 8, 2c + 9 (c = lane % 4).
 template <int HD>
+struct DGroup {
+    uint4 k_lo[HD / 32], k_hi[HD / 32];
+    uint4 v[4][HD / 64];
+};
+
+template <int HD>
+__device__ __forceinline__ void d_load_group(DGroup<HD>& g, const Pages& pg, int k0, int key_lo, int key_hi, int lane) {
+    const int c = lane & 3, r = lane >> 2;
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    // the 16 keys of a group lie in one page
+    const size_t base = (((size_t)pg.table[k0 / kPage] * pg.n_kv + pg.kvh) * kPage + k0 % kPage) * HD;
+    const __nv_bfloat16* kb = pg.k + base;
+    const __nv_bfloat16* vb = pg.v + base;
+    const bool inside = k0 >= key_lo && k0 + 15 <= key_hi;
+    if (inside) {
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) {
+            g.k_lo[j] = ld16(kb + (size_t)r * HD + (c + 4 * j) * 8);
+            g.k_hi[j] = ld16(kb + (size_t)(r + 8) * HD + (c + 4 * j) * 8);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int h = 0; h < HD / 64; ++h)
+                g.v[i][h] = ld16(vb + (size_t)(2 * c + (i & 1) + 8 * (i >> 1)) * HD + h * 64 + r * 8);
+    } else {
+        const bool lo_ok = k0 + r >= key_lo && k0 + r <= key_hi, hi_ok = k0 + r + 8 >= key_lo && k0 + r + 8 <= key_hi;
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) {
+            g.k_lo[j] = lo_ok ? ld16(kb + (size_t)r * HD + (c + 4 * j) * 8) : z;
+            g.k_hi[j] = hi_ok ? ld16(kb + (size_t)(r + 8) * HD + (c + 4 * j) * 8) : z;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rel = 2 * c + (i & 1) + 8 * (i >> 1);
+            const bool ok = k0 + rel >= key_lo && k0 + rel <= key_hi;
+#pragma unroll
+            for (int h = 0; h < HD / 64; ++h) g.v[i][h] = ok ? ld16(vb + (size_t)rel * HD + h * 64 + r * 8) : z;
+        }
+    }
+}
+
+// Per-lane state of the decode formulation for NT column tiles of 8 heads: the lane's two heads
+// of each tile are 8 * t + 2c and 8 * t + 2c + 1.
+template <int HD, int NT>
+struct DAcc {
+    float o[NT][HD / 16][4];  // row tile (h, e): [0..1] head lane (h * 64 + r * 8 + e), [2..3] head lane (.. + 4)
+    float m[NT][2], l[NT][2];
+};
+
+template <int HD, int NT>
+__device__ __forceinline__ void d_consume_group(DAcc<HD, NT>& acc, const uint4 (&q)[NT][HD / 32], const DGroup<HD>& g,
+                                                int k0, int key_lo, int key_hi, float scale2, int lane) {
+    const int c = lane & 3, r = lane >> 2;
+    const bool inside = k0 >= key_lo && k0 + 15 <= key_hi;
+    const bool lo_ok = inside || (k0 + r >= key_lo && k0 + r <= key_hi);
+    const bool hi_ok = inside || (k0 + r + 8 >= key_lo && k0 + r + 8 <= key_hi);
+    uint32_t pb[NT][2];
+    bool rescale = false;
+    float corr[NT][2];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) {
+            mma_bf16(s, g.k_lo[j].x, g.k_hi[j].x, g.k_lo[j].y, g.k_hi[j].y, q[t][j].x, q[t][j].y);
+            mma_bf16(s, g.k_lo[j].z, g.k_hi[j].z, g.k_lo[j].w, g.k_hi[j].w, q[t][j].z, q[t][j].w);
+        }
+        // s[0], s[1]: key k0 + r, heads 2c, 2c + 1;  s[2], s[3]: key k0 + r + 8
+        s[0] = lo_ok ? s[0] * scale2 : -INFINITY;
+        s[1] = lo_ok ? s[1] * scale2 : -INFINITY;
+        s[2] = hi_ok ? s[2] * scale2 : -INFINITY;
+        s[3] = hi_ok ? s[3] * scale2 : -INFINITY;
+        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int sh = 4; sh <= 16; sh <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+        }
+        const float m0 = fmaxf(acc.m[t][0], mx0), m1 = fmaxf(acc.m[t][1], mx1);
+        corr[t][0] = m0 == -INFINITY ? 1.0f : fast_exp2(acc.m[t][0] - m0);
+        corr[t][1] = m1 == -INFINITY ? 1.0f : fast_exp2(acc.m[t][1] - m1);
+        rescale = rescale || corr[t][0] != 1.0f || corr[t][1] != 1.0f;
+        acc.m[t][0] = m0;
+        acc.m[t][1] = m1;
+        const float p0 = m0 == -INFINITY ? 0.0f : fast_exp2(s[0] - m0), p2 = m0 == -INFINITY ? 0.0f : fast_exp2(s[2] - m0);
+        const float p1 = m1 == -INFINITY ? 0.0f : fast_exp2(s[1] - m1), p3 = m1 == -INFINITY ? 0.0f : fast_exp2(s[3] - m1);
+        acc.l[t][0] = acc.l[t][0] * corr[t][0] + (p0 + p2);
+        acc.l[t][1] = acc.l[t][1] * corr[t][1] + (p1 + p3);
+        // (key, head pair) -> (head, key pair): the right-hand operand of the second product
+        pb[t][0] = movmatrix_trans(pack_bf16(p0, p1));
+        pb[t][1] = movmatrix_trans(pack_bf16(p2, p3));
+    }
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int i = 0; i < HD / 16; ++i) {
+                acc.o[t][i][0] *= corr[t][0]; acc.o[t][i][1] *= corr[t][1];
+                acc.o[t][i][2] *= corr[t][0]; acc.o[t][i][3] *= corr[t][1];
+            }
+    }
+#pragma unroll
+    for (int h = 0; h < HD / 64; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+            const uint32_t a0 = __byte_perm(u4_get(g.v[0][h], e >> 1), u4_get(g.v[1][h], e >> 1), sel);
+            const uint32_t a1 = __byte_perm(u4_get(g.v[0][h], 2 + (e >> 1)), u4_get(g.v[1][h], 2 + (e >> 1)), sel);
+            const uint32_t a2 = __byte_perm(u4_get(g.v[2][h], e >> 1), u4_get(g.v[3][h], e >> 1), sel);
+            const uint32_t a3 = __byte_perm(u4_get(g.v[2][h], 2 + (e >> 1)), u4_get(g.v[3][h], 2 + (e >> 1)), sel);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) mma_bf16(acc.o[t][h * 4 + e], a0, a1, a2, a3, pb[t][0], pb[t][1]);
+        }
+}
+
+template <int HD, int NT>
 __global__ void __launch_bounds__(128, 2)
 decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
               const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
@@ -234,7 +393,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
     extern __shared__ float sm[];  // [4 warps][G rows][HD + 2]
     const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = n_heads / n_kv;  // at most 16 here
+    const int G = n_heads / n_kv;  // at most 8 * NT
     const int seq = tok_seq[t];
     const size_t out_row = (size_t)t * n_heads * HD + (size_t)kvh * G * HD;
     if (seq < 0) {  // padding: zeros
@@ -255,43 +414,68 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
     const int g0 = g_first + split * per;
     const int g1 = min(g_last, g0 + per - 1);
     const int key_lo = max(first, g0 << 4), key_hi = min(pos, (g1 << 4) + 15);
+    const int c = lane & 3, r = lane >> 2;
 
-    Acc<HD> acc;
-    acc.init();
-    if (g0 <= g1) {
-        const int r = lane >> 2;
-        uint32_t qa[HD / 16][4];
-        const __nv_bfloat16* qbase = q + out_row;
-        load_q<HD>(qa, r < G ? qbase + (size_t)r * HD : nullptr, r + 8 < G ? qbase + (size_t)(r + 8) * HD : nullptr,
-                   lane);
-        Pages pg{k_pages, v_pages, block_table + (size_t)seq * bt_stride, n_kv, kvh};
-        const int lo[2] = {key_lo, key_lo}, hi[2] = {key_hi, key_hi};
-        run_keys<HD>(acc, qa, pg, key_lo, key_hi, lo, hi, g0 + warp, 4, scale2, lane);
-    }
-    // every lane's partial sums of its two rows -> the row's sum
+    DAcc<HD, NT> acc;
 #pragma unroll
-    for (int row = 0; row < 2; ++row) {
-        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 1);
-        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 2);
+    for (int tt = 0; tt < NT; ++tt) {
+#pragma unroll
+        for (int i = 0; i < HD / 16; ++i) acc.o[tt][i][0] = acc.o[tt][i][1] = acc.o[tt][i][2] = acc.o[tt][i][3] = 0.0f;
+        acc.m[tt][0] = acc.m[tt][1] = -INFINITY;
+        acc.l[tt][0] = acc.l[tt][1] = 0.0f;
     }
+    if (g0 + warp <= g1) {
+        // the query of head (8 * tt + r) as the right-hand operand of the first product
+        uint4 qf[NT][HD / 32];
+        const __nv_bfloat16* qbase = q + out_row;
+#pragma unroll
+        for (int tt = 0; tt < NT; ++tt)
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j)
+                qf[tt][j] = 8 * tt + r < G ? ld16(qbase + (size_t)(8 * tt + r) * HD + (c + 4 * j) * 8)
+                                           : make_uint4(0, 0, 0, 0);
+        Pages pg{k_pages, v_pages, block_table + (size_t)seq * bt_stride, n_kv, kvh};
+        int gi = g0 + warp;
+        DGroup<HD> cur, nxt;
+        d_load_group<HD>(cur, pg, gi << 4, key_lo, key_hi, lane);
+        while (true) {
+            const int gn = gi + 4;
+            const bool more = gn <= g1;
+            if (more) d_load_group<HD>(nxt, pg, gn << 4, key_lo, key_hi, lane);
+            d_consume_group<HD, NT>(acc, qf, cur, gi << 4, key_lo, key_hi, scale2, lane);
+            if (!more) break;
+            cur = nxt;
+            gi = gn;
+        }
+    }
+    // the lanes that share c hold partial sums of the same two heads
+#pragma unroll
+    for (int tt = 0; tt < NT; ++tt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+#pragma unroll
+            for (int sh = 4; sh <= 16; sh <<= 1) acc.l[tt][e] += __shfl_xor_sync(0xffffffffu, acc.l[tt][e], sh);
     // the four warps' results meet in shared memory
     constexpr int W = HD + 2;
     float* mine = sm + (size_t)warp * G * W;
 #pragma unroll
-    for (int row = 0; row < 2; ++row) {
-        const int head = (lane >> 2) + 8 * row;
-        if (head < G) {
+    for (int tt = 0; tt < NT; ++tt)
 #pragma unroll
-            for (int tt = 0; tt < HD / 8; ++tt) {
-                mine[head * W + out_dim<HD>(tt, 0, lane)] = acc.o[tt][2 * row];
-                mine[head * W + out_dim<HD>(tt, 1, lane)] = acc.o[tt][2 * row + 1];
-            }
-            if ((lane & 3) == 0) {
-                mine[head * W + HD] = acc.m[row];
-                mine[head * W + HD + 1] = acc.l[row];
+        for (int e = 0; e < 2; ++e) {
+            const int head = 8 * tt + 2 * c + e;
+            if (head < G) {
+#pragma unroll
+                for (int i = 0; i < HD / 16; ++i) {
+                    const int d = (i >> 2) * 64 + r * 8 + (i & 3);
+                    mine[head * W + d] = acc.o[tt][i][e];
+                    mine[head * W + d + 4] = acc.o[tt][i][2 + e];
+                }
+                if (r == 0) {
+                    mine[head * W + HD] = acc.m[tt][e];
+                    mine[head * W + HD + 1] = acc.l[tt][e];
+                }
             }
         }
-    }
     __syncthreads();
     const size_t pb = ((size_t)t * n_kv + kvh) * n_splits + split;
     for (int i = threadIdx.x; i < G * HD; i += 128) {
@@ -408,18 +592,19 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
                   float scale, int window, int n_splits, cudaStream_t stream) {
     const int G = n_heads / n_kv;
     const size_t smem = (size_t)4 * G * (HD + 2) * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 16 * (HD + 2) * 4);
-        configured = true;
-    }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_tok * n_kv * n_splits * G * HD : nullptr;
     dim3 grid(n_splits, n_kv, n_tok);
-    decode_kernel<HD><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
-                                                   (const __nv_bfloat16*)v_pages, block_table, bt_stride, tok_seq,
-                                                   tok_pos, (__nv_bfloat16*)out, part_o, part_ml, n_heads, n_kv,
-                                                   scale * kLog2e, window);
+    if (G <= 8)
+        decode_kernel<HD, 1><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
+                                                          (const __nv_bfloat16*)v_pages, block_table, bt_stride,
+                                                          tok_seq, tok_pos, (__nv_bfloat16*)out, part_o, part_ml,
+                                                          n_heads, n_kv, scale * kLog2e, window);
+    else
+        decode_kernel<HD, 2><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
+                                                          (const __nv_bfloat16*)v_pages, block_table, bt_stride,
+                                                          tok_seq, tok_pos, (__nv_bfloat16*)out, part_o, part_ml,
+                                                          n_heads, n_kv, scale * kLog2e, window);
     NN_LAUNCH_OK("attention decode");
     if (n_splits > 1) {
         merge_kernel<HD><<<dim3(n_heads, n_tok), HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_heads, n_kv,

@@ -100,10 +100,10 @@ class Attention(Mixer):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
                           s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
         elif ctx.is_decode:
-            # enough blocks to fill the GPU twice over, but at least 256 keys per split
+            # as many blocks as run at once (two per SM), never a second wave; at least 256 keys per split
             longest = min(ctx.max_kv_len, s.window) if s.window > 0 else ctx.max_kv_len
             pairs = ctx.n_tokens * s.n_kv_heads
-            n_splits = max(1, min(-(-296 // pairs), longest // 256))
+            n_splits = max(1, min(296 // pairs, longest // 256))
             floats = ops.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
             scratch = self.rt.empty(floats, dtype=torch.float32) if floats else None
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
