@@ -166,9 +166,10 @@ struct GemmParams {
     int* status;
 };
 
-// Stores 16 accumulator values of one thread: A row `a_row`, B rows b0 .. b0 + 15.
+// Stores up to 16 accumulator values of one thread: A row `a_row`, B rows b0 .. b0 + ncols - 1
+// (ncols below 16 only when A rows are output features).
 template <int kEpi>
-__device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, float (&v)[16]) {
+__device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, float (&v)[16], int ncols = 16) {
     const bool a_ok = a_row < p.rows_a;
     if (kEpi == kSwiglu) {
         if (!p.swap) {
@@ -195,7 +196,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
             for (int j = 0; j < 16; ++j) {
                 const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
                 const int tok = b0 + j;
-                if (is_gate && a_ok && tok < p.rows_b)
+                if (is_gate && a_ok && j < ncols && tok < p.rows_b)
                     st_f(p.out, (size_t)tok * p.ldc + feature, p.out_dt, silu_mul(v[j], other));
             }
         }
@@ -258,7 +259,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int tok = b0 + j;
-            if (tok >= p.rows_b) break;
+            if (tok >= p.rows_b || j >= ncols) break;
             const size_t o = (size_t)tok * p.ldc + a_row;
             float x = v[j] + b;
             if (p.accumulate) x += ld_f(p.out, o, p.out_dt);
@@ -482,6 +483,174 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------
+// Few output tiles, many SMs: a thread-block cluster shares one output tile.
+// Each block of the cluster multiplies its own slice of K into tensor memory,
+// copies the partial tile to its shared memory, and after a cluster barrier
+// every block adds up one share of the tile's columns, reading the other
+// blocks' partial tiles through distributed shared memory in rank order.  No
+// global scratch, no tickets, and the sum does not depend on timing.
+// Used when A rows are output features (few tokens); one tile per cluster.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int BN, int kStages, int kEpi>
+__global__ void __launch_bounds__(kThreads)
+gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+    constexpr int kBytesA = kBlockM * kBlockK * 2;
+    constexpr int kBytesB = BN * kBlockK * 2;
+    constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    static_assert(kStages * (kBytesA + kBytesB) >= BN * kBlockM * 4, "the partial tile reuses the stage memory");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kStages * kBytesA;
+    float* partial = (float*)smem;  // [BN][128], after the last tensor-core read of the stages
+    uint64_t* full = (uint64_t*)(smem_b + kStages * kBytesB);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_full = empty + kStages;
+    uint32_t* tmem_slot = (uint32_t*)(acc_full + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = p.splits;                     // blocks per cluster
+    const int rank = (int)cluster_rank();
+    const int tile = blockIdx.x / S;
+    const int m0 = (tile % p.tiles_a) * kBlockM, n0 = (tile / p.tiles_a) * BN;
+    const int kb0 = (int)((long long)rank * p.kb_total / S), kb1 = (int)((long long)(rank + 1) * p.kb_total / S);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                const int i = kb - kb0, s = i % kStages;
+                if (!mbar_wait(&empty[s], ((i / kStages) & 1) ^ 1)) {
+                    atomicExch(p.status, kTimeoutEmpty);
+                    ok = false;
+                    break;
+                }
+                mbar_expect_tx(&full[s], kBytesA + kBytesB);
+                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
+                issued = i + 1;
+            }
+            if (!ok)
+                for (int r = max(0, issued - kStages); r < issued; ++r) mbar_wait(&full[r % kStages], (r / kStages) & 1);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16(kBlockM, BN);
+            bool ok = true;
+            for (int kb = kb0; kb < kb1 && ok; ++kb) {
+                const int i = kb - kb0, s = i % kStages;
+                if (!mbar_wait(&full[s], (i / kStages) & 1)) {
+                    atomicExch(p.status, kTimeoutFull);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem_a + s * kBytesA);
+                const uint32_t b_addr = smem_u32(smem_b + s * kBytesB);
+#pragma unroll
+                for (int k = 0; k < kBlockK / kUmmaK; ++k)
+                    umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * kUmmaK * 2), smem_desc_sw128(b_addr + k * kUmmaK * 2),
+                              idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        // this block's partial tile: tensor memory -> shared memory, a column at a time
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const bool ok = kb1 > kb0 ? mbar_wait(acc_full, 0) : true;
+        if (!ok && lane == 0) atomicExch(p.status, kTimeoutAccumFull);
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            if (ok && kb1 > kb0) {
+                tmem_ld16(taddr + (uint32_t)c0, v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) partial[(c0 + j) * kBlockM + row_in_tile] = v[j];
+        }
+    }
+    __syncwarp();
+    cluster_barrier();  // every block's partial tile is complete and visible in the cluster
+    if (warp >= 2) {
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const int a_row = m0 + row_in_tile;
+        const int cols = BN / S;                 // this block's share of the tile's columns
+        const int c_begin = rank * cols;
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+            const int n = min(16, cols - c0);
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            for (int r = 0; r < S; ++r) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j < n)
+                        v[j] += ld_cluster_f32(smem_u32(&partial[(c_begin + c0 + j) * kBlockM + row_in_tile]), (uint32_t)r);
+            }
+            store16<kEpi>(p, a_row, n0 + c_begin + c0, v, n);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    cluster_barrier();  // nobody leaves while its partial tile may still be read
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Host side: tensor maps (cached by what they describe) and the launcher.
 // ---------------------------------------------------------------------------
 
@@ -570,6 +739,43 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int bloc
     return 0;
 }
 
+template <int BN, int kStages, int kEpi>
+int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
+    constexpr size_t smem = smem_bytes<BN, kStages>();
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_cluster_kernel<BN, kStages, kEpi>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.tiles_a * p.tiles_b * p.splits));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_cluster_kernel<BN, kStages, kEpi>, ma, mb, p);
+    NN_CHECK(e == cudaSuccess, "gemm (cluster of %d): launch failed: %s", p.splits, cudaGetErrorString(e));
+    return 0;
+}
+
+template <int kEpi>
+int dispatch_cluster(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
+    switch (bn) {
+        case 32: return launch_cluster<32, 4, kEpi>(ma, mb, p, stream);
+        case 64: return launch_cluster<64, 4, kEpi>(ma, mb, p, stream);
+        case 128: return launch_cluster<128, 4, kEpi>(ma, mb, p, stream);
+        default: return launch_cluster<256, 4, kEpi>(ma, mb, p, stream);
+    }
+}
+
 template <int kEpi>
 int dispatch(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
     switch (bn) {
@@ -642,7 +848,7 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
     // keep at least 4 k-blocks per slice, and stay inside the workspace.
     const int n_tiles = p.tiles_a * p.tiles_b;
     int splits = 1;
-    if (bn <= 64 && scratch != nullptr && tickets != nullptr && n_tiles <= nncpu_linear_tc_tickets()) {
+    if (bn <= 16 && scratch != nullptr && tickets != nullptr && n_tiles <= nncpu_linear_tc_tickets()) {
         const int want = (2 * sm_count() + n_tiles - 1) / n_tiles;
         splits = want < 1 ? 1 : want;
         if (splits > p.kb_total / 4) splits = p.kb_total / 4;
@@ -653,5 +859,15 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         if (splits < 1) splits = 1;
     }
     p.splits = splits;
+    if (p.swap && bn >= 32) {
+        // Few tokens, wide token tile: a cluster per output tile cuts K into 2, 4 or 8 slices, as many as it
+        // takes to put a block on most SMs, with at least 4 k-blocks per slice.
+        int s = 1;
+        while (s < 8 && n_tiles * s < sm_count() && p.kb_total / (2 * s) >= 4 && bn / (2 * s) >= 1) s *= 2;
+        p.splits = s;
+        if (s > 1)
+            return epilogue == kSwiglu ? dispatch_cluster<kSwiglu>(bn, ma, mb, p, stream)
+                                       : dispatch_cluster<kPlain>(bn, ma, mb, p, stream);
+    }
     return epilogue == kSwiglu ? dispatch<kSwiglu>(bn, ma, mb, p, stream) : dispatch<kPlain>(bn, ma, mb, p, stream);
 }
