@@ -49,6 +49,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
 
+__device__ __forceinline__ uint32_t smem_u32_(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
 __device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) {
     return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
 }
@@ -523,66 +525,215 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
 }
 
 // ---------------------------------------------------------------------------
-// Prefill: any number of new tokens per sequence.  One warp per (tile of 16
-// consecutive new tokens of one sequence, head); grid = (tiles / 4, n_heads).
+// Prefill: any number of new tokens per sequence.  One block per (64
+// consecutive new tokens of one sequence, head): four warps of 16 query rows
+// each share the key and value tiles, which come page by page (64 keys) into
+// shared memory with cp.async, two pages in flight, rows swizzled so that
+// ldmatrix reads without bank conflicts.  grid = (tiles, n_heads).
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// Byte offset of the 16-byte chunk `chunk` of row `row` in a tile whose rows hold HD bfloat16:
+// chunks are exchanged within groups of 8 by the row number, so 8 rows' equal chunks hit 8 bank groups.
+template <int HD>
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+    return (uint32_t)(row * (HD * 2) + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
+}
+
 template <int HD>
 __global__ void __launch_bounds__(128)
 prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                const int* __restrict__ cu_seqlens, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
                int n_seqs, int n_heads, int n_kv, float scale2, int window) {
+    constexpr int kTileBytes = kPage * HD * 2;           // one page of K or of V for one head
+    constexpr int kChunks = HD / 8;                      // 16-byte chunks per row
+    extern __shared__ __align__(128) uint8_t fa_smem[];  // [2 stages][K tile | V tile]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = lane & 3, r = lane >> 2;
     const int h = blockIdx.y;
-    // long tiles first: tiles are numbered from the end of the batch backwards within each sequence
-    int tile = blockIdx.x * 4 + warp;
+    // tiles of 64 query rows, numbered within each sequence from its end (long spans first)
+    int tile = blockIdx.x;
     int seq = -1, q0 = 0, q_end = 0;
     for (int b = 0; b < n_seqs; ++b) {
         const int a = cu_seqlens[b], e = cu_seqlens[b + 1];
-        const int n_tiles = (e - a + 15) >> 4;
+        const int n_tiles = (e - a + 63) >> 6;
         if (tile < n_tiles) {
             seq = b;
-            q0 = a + ((n_tiles - 1 - tile) << 4);
+            q0 = a + ((n_tiles - 1 - tile) << 6);
             q_end = e;
             break;
         }
         tile -= n_tiles;
     }
     if (seq < 0) return;
-    const int r = lane >> 2;
-    const int tok_lo = q0 + r, tok_hi = q0 + r + 8;
-    const bool has_lo = tok_lo < q_end, has_hi = tok_hi < q_end;
-    const int pos0 = tok_pos[q0];  // positions of a sequence's new tokens are consecutive
-    const int n_rows = min(16, q_end - q0);
-    int lo[2], hi[2];
-    hi[0] = has_lo ? pos0 + r : -1;
-    hi[1] = has_hi ? pos0 + r + 8 : -1;
-    lo[0] = (window > 0 && hi[0] + 1 > window) ? hi[0] + 1 - window : 0;
-    lo[1] = (window > 0 && hi[1] + 1 > window) ? hi[1] + 1 - window : 0;
-    const int key_hi = pos0 + n_rows - 1;
+    const int n_rows = min(64, q_end - q0);
+    const int pos0 = tok_pos[q0];                        // positions of a sequence's new tokens are consecutive
+    const int key_hi = pos0 + n_rows - 1;                // the last row's last key
     const int key_lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    const int page_lo = key_lo / kPage, page_hi = key_hi / kPage;
+    const int* table = block_table + (size_t)seq * bt_stride;
+    const int kvh = h / (n_heads / n_kv);
 
+    // this warp's rows: q0 + 16 * warp + r and + 8
+    const int row_lo = 16 * warp + r, row_hi = row_lo + 8;
+    const bool has_lo = row_lo < n_rows, has_hi = row_hi < n_rows;
+    int lim_lo[2], lim_hi[2];
+    lim_hi[0] = has_lo ? pos0 + row_lo : -1;
+    lim_hi[1] = has_hi ? pos0 + row_hi : -1;
+    lim_lo[0] = (window > 0 && lim_hi[0] + 1 > window) ? lim_hi[0] + 1 - window : 0;
+    lim_lo[1] = (window > 0 && lim_hi[1] + 1 > window) ? lim_hi[1] + 1 - window : 0;
+    const int warp_key_hi = pos0 + min(n_rows, 16 * warp + 16) - 1;   // nothing beyond this matters to the warp
+    const int warp_key_lo = (window > 0 && pos0 + 16 * warp + 1 > window) ? pos0 + 16 * warp + 1 - window : 0;
+
+    // query fragments in the layout the instruction asks for: 4-byte loads, once per block
     uint32_t qa[HD / 16][4];
-    const size_t row_stride = (size_t)n_heads * HD;
-    load_q<HD>(qa, has_lo ? q + tok_lo * row_stride + (size_t)h * HD : nullptr,
-               has_hi ? q + tok_hi * row_stride + (size_t)h * HD : nullptr, lane);
-    Pages pg{k_pages, v_pages, block_table + (size_t)seq * bt_stride, n_kv, h / (n_heads / n_kv)};
-    Acc<HD> acc;
-    acc.init();
-    run_keys<HD>(acc, qa, pg, key_lo, key_hi, lo, hi, key_lo >> 4, 1, scale2, lane);
+    {
+        const size_t stride = (size_t)n_heads * HD;
+        const __nv_bfloat16* ql = q + (size_t)(q0 + row_lo) * stride + (size_t)h * HD;
+        const __nv_bfloat16* qh = q + (size_t)(q0 + row_hi) * stride + (size_t)h * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            qa[ks][0] = has_lo ? *reinterpret_cast<const uint32_t*>(ql + ks * 16 + 2 * c) : 0u;
+            qa[ks][1] = has_hi ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * c) : 0u;
+            qa[ks][2] = has_lo ? *reinterpret_cast<const uint32_t*>(ql + ks * 16 + 8 + 2 * c) : 0u;
+            qa[ks][3] = has_hi ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 8 + 2 * c) : 0u;
+        }
+    }
+
+    auto issue = [&](int page_idx, int stage) {
+        const size_t base = ((size_t)table[page_idx] * n_kv + kvh) * (size_t)(kPage * HD);
+        const uint32_t dst = smem_u32_(fa_smem) + stage * 2 * kTileBytes;
+#pragma unroll
+        for (int i = threadIdx.x; i < kPage * kChunks; i += 128) {
+            const int row = i / kChunks, chunk = i % kChunks;
+            cp_async16(dst + tile_off<HD>(row, chunk), k_pages + base + (size_t)row * HD + chunk * 8);
+            cp_async16(dst + kTileBytes + tile_off<HD>(row, chunk), v_pages + base + (size_t)row * HD + chunk * 8);
+        }
+        cp_async_commit();
+    };
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+    issue(page_lo, 0);
+    for (int pg = page_lo; pg <= page_hi; ++pg) {
+        const int stage = (pg - page_lo) & 1;
+        if (pg + 1 <= page_hi) {
+            issue(pg + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int k_base = pg * kPage;
+        if (k_base <= warp_key_hi && k_base + kPage - 1 >= warp_key_lo) {
+            const uint32_t ks_addr = smem_u32_(fa_smem) + stage * 2 * kTileBytes;
+            const uint32_t vs_addr = ks_addr + kTileBytes;
+            // scores of 16 rows x 64 keys
+            float s[8][4];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+                for (int tp = 0; tp < 4; ++tp) {   // pairs of 8-key tiles
+                    uint32_t b[4];
+                    const int key = tp * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int chunk = ks * 2 + ((lane >> 3) & 1);
+                    ldmatrix_x4(b, ks_addr + tile_off<HD>(key, chunk));
+                    mma_bf16(s[2 * tp], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
+                    mma_bf16(s[2 * tp + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
+                }
+            }
+            // scale, mask where the tile crosses a row's limits, running maximum
+            const bool full = k_base >= max(lim_lo[0], lim_lo[1]) && has_hi && k_base + kPage - 1 <= lim_hi[0];
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int row = e >> 1;
+                    float v = s[t][e] * scale2;
+                    if (!full) {
+                        const int key = k_base + t * 8 + 2 * c + (e & 1);
+                        if (key < lim_lo[row] || key > lim_hi[row]) v = -INFINITY;
+                    }
+                    s[t][e] = v;
+                    mx[row] = fmaxf(mx[row], v);
+                }
+            float corr[2];
+#pragma unroll
+            for (int row = 0; row < 2; ++row) {
+                mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 1));
+                mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 2));
+                const float m_new = fmaxf(m[row], mx[row]);
+                corr[row] = m_new == -INFINITY ? 1.0f : fast_exp2(m[row] - m_new);
+                m[row] = m_new;
+            }
+            float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int row = e >> 1;
+                    const float pv = m[row] == -INFINITY ? 0.0f : fast_exp2(s[t][e] - m[row]);
+                    s[t][e] = pv;
+                    sum[row] += pv;
+                }
+            l[0] = l[0] * corr[0] + sum[0];
+            l[1] = l[1] * corr[1] + sum[1];
+            if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+                for (int t = 0; t < HD / 8; ++t) {
+                    o[t][0] *= corr[0]; o[t][1] *= corr[0]; o[t][2] *= corr[1]; o[t][3] *= corr[1];
+                }
+            }
+            // weighted sum of the 64 value rows
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {       // 16 keys at a time
+                const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                const uint32_t a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < HD / 16; ++dp) {   // pairs of 8-lane tiles of the head
+                    uint32_t b[4];
+                    const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                    const int chunk = dp * 2 + (lane >> 4);
+                    ldmatrix_x4_trans(b, vs_addr + tile_off<HD>(key, chunk));
+                    mma_bf16(o[2 * dp], a0, a1, a2, a3, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();   // the stage is free for the page after next
+    }
 #pragma unroll
     for (int row = 0; row < 2; ++row) {
-        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 1);
-        acc.l[row] += __shfl_xor_sync(0xffffffffu, acc.l[row], 2);
-        const int tok = row == 0 ? tok_lo : tok_hi;
-        if (tok >= q_end) continue;
-        const float inv = acc.l[row] > 0.0f ? 1.0f / acc.l[row] : 0.0f;
-        __nv_bfloat16* o = out + tok * row_stride + (size_t)h * HD;
+        l[row] += __shfl_xor_sync(0xffffffffu, l[row], 1);
+        l[row] += __shfl_xor_sync(0xffffffffu, l[row], 2);
+        if (!(row == 0 ? has_lo : has_hi)) continue;
+        const float inv = l[row] > 0.0f ? 1.0f / l[row] : 0.0f;
+        __nv_bfloat16* dst = out + (size_t)(q0 + (row == 0 ? row_lo : row_hi)) * n_heads * HD + (size_t)h * HD;
 #pragma unroll
-        for (int tt = 0; tt < HD / 8; ++tt) {
-            o[out_dim<HD>(tt, 0, lane)] = __float2bfloat16_rn(acc.o[tt][2 * row] * inv);
-            o[out_dim<HD>(tt, 1, lane)] = __float2bfloat16_rn(acc.o[tt][2 * row + 1] * inv);
-        }
+        for (int t = 0; t < HD / 8; ++t)
+            *reinterpret_cast<uint32_t*>(dst + t * 8 + 2 * c) = pack_bf16(o[t][2 * row] * inv, o[t][2 * row + 1] * inv);
     }
 }
 
@@ -618,9 +769,15 @@ template <int HD>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                    const int* cu_seqlens, const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads, int n_kv,
                    float scale, int window, cudaStream_t stream) {
-    const int max_tiles = n_tok / 16 + n_seqs;
-    dim3 grid((max_tiles + 3) / 4, n_heads);
-    prefill_kernel<HD><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
+    const int max_tiles = n_tok / 64 + n_seqs;
+    constexpr int smem = 2 * 2 * kPage * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        configured = true;
+    }
+    dim3 grid(max_tiles, n_heads);
+    prefill_kernel<HD><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                                                  (const __nv_bfloat16*)v_pages, block_table, bt_stride, cu_seqlens,
                                                  tok_pos, (__nv_bfloat16*)out, n_seqs, n_heads, n_kv, scale * kLog2e,
                                                  window);
