@@ -66,10 +66,67 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void*
     }
 }
 
+// The common case, float32 rows of a width that is a multiple of 4 and at most 256 * 4 * kVec: every
+// thread keeps its part of the row in registers between the sum of squares and the scaling, so the
+// row is read once, 16 bytes at a time.
+template <int kVec>
+__global__ void __launch_bounds__(256)
+rmsnorm_f32_kernel(const float* __restrict__ x, const void* __restrict__ gamma, int g_dt, void* __restrict__ y,
+                   int y_dt, const int* __restrict__ rows, int dim, float eps) {
+    __shared__ float scratch[33];
+    const int r_out = blockIdx.x;
+    const int r_in = rows ? rows[r_out] : r_out;
+    const int n4 = dim >> 2;
+    float4 v[kVec];
+    float ss = 0.0f;
+    if (r_in >= 0) {
+        const float4* src = reinterpret_cast<const float4*>(x + (size_t)r_in * dim);
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            const int i = threadIdx.x + j * 256;
+            v[j] = i < n4 ? src[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) v[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = r_in >= 0 ? 1.0f / sqrtf(ss * (1.0f / (float)dim) + eps) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= n4) continue;
+        float o[4] = {v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale};
+        if (gamma) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] *= ld_f(gamma, 4 * i + e, g_dt);
+        }
+        const size_t at = (size_t)r_out * dim + 4 * i;
+        if (y_dt == DT_BF16) {
+            __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(y) + at) = *reinterpret_cast<uint2*>(h);
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + at) = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_dt, void* y, int y_dt,
                              const int* rows, int n_rows, int dim, float eps, void* stream) {
     NN_CHECK(n_rows >= 0 && dim > 0, "rmsnorm: %d rows of %d", n_rows, dim);
     if (n_rows == 0) return 0;
+    if (x_dt == DT_F32 && dim % 4 == 0 && dim >= 1024 && dim <= 256 * 4 * 8 && (uintptr_t)x % 16 == 0 &&
+        (uintptr_t)y % 16 == 0) {
+        const float* xf = (const float*)x;
+        cudaStream_t st = (cudaStream_t)stream;
+        if (dim <= 256 * 4 * 2) rmsnorm_f32_kernel<2><<<n_rows, 256, 0, st>>>(xf, gamma, g_dt, y, y_dt, rows, dim, eps);
+        else if (dim <= 256 * 4 * 4) rmsnorm_f32_kernel<4><<<n_rows, 256, 0, st>>>(xf, gamma, g_dt, y, y_dt, rows, dim, eps);
+        else rmsnorm_f32_kernel<8><<<n_rows, 256, 0, st>>>(xf, gamma, g_dt, y, y_dt, rows, dim, eps);
+        NN_LAUNCH_OK("rmsnorm");
+        return 0;
+    }
     int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
     rmsnorm_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, x_dt, gamma, g_dt, y, y_dt, rows, dim, eps);
     NN_LAUNCH_OK("rmsnorm");
@@ -249,6 +306,72 @@ __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_
     for (int i = lane; i < hd; i += 32) st_f(dst, o + i, kv_dt, x[i]);
 }
 
+// The bfloat16 run's case: float32 projections in, bfloat16 q and cache out, the whole head rotated,
+// head size 64 or 128.  A lane holds EPL = hd / 32 neighbouring lanes of the head, so lanes 0-15 hold
+// the first half and lanes 16-31 the second: a rotation pair sits in lanes i and i + 16.
+template <int EPL>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_append_fast_kernel(const float* __restrict__ qkv, const void* __restrict__ q_gamma,
+                                const void* __restrict__ k_gamma, int g_dt, float eps, const float2* __restrict__ cs,
+                                const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pages,
+                                __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ q_out, int n_tok,
+                                int n_heads, int n_kv) {
+    constexpr int hd = 32 * EPL, half = hd / 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_tok = n_heads + 2 * n_kv;
+    const long item = (long)blockIdx.x * 8 + warp;
+    if (item >= (long)n_tok * per_tok) return;
+    const int t = (int)(item / per_tok), h = (int)(item % per_tok);
+    const bool is_q = h < n_heads, is_k = !is_q && h < n_heads + n_kv;
+    const float* src = qkv + ((size_t)t * per_tok + h) * hd + lane * EPL;
+    float x[EPL];
+    if (EPL == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src);
+        x[0] = v.x; x[1] = v.y; x[2 % EPL] = v.z; x[3 % EPL] = v.w;
+    } else {
+        const float2 v = *reinterpret_cast<const float2*>(src);
+        x[0] = v.x; x[1] = v.y;
+    }
+    const void* gamma = is_q ? q_gamma : (is_k ? k_gamma : nullptr);
+    if (gamma) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) ss = fmaf(x[e], x[e], ss);
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss * (1.0f / (float)hd) + eps);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) x[e] = (x[e] * scale) * ld_f(gamma, lane * EPL + e, g_dt);
+    }
+    if ((is_q || is_k) && cs != nullptr) {
+        const int i0 = (lane & 15) * EPL;   // index of the rotation pair
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+            const float2 c = cs[(size_t)t * half + i0 + e];
+            x[e] = lane < 16 ? c.x * x[e] - c.y * other : c.y * other + c.x * x[e];
+        }
+    }
+    __nv_bfloat16* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * n_heads + h) * hd;
+    } else {
+        const int seq = tok_seq[t];
+        if (seq < 0) return;
+        const int pos = tok_pos[t];
+        const int page = block_table[(size_t)seq * bt_stride + pos / kPage];
+        if (page < 0) return;
+        const int kvh = is_k ? h - n_heads : h - n_heads - n_kv;
+        dst = (is_k ? k_pages : v_pages) + (((size_t)page * n_kv + kvh) * kPage + pos % kPage) * hd;
+    }
+    if (EPL == 4) {
+        __nv_bfloat162 o[2] = {__floats2bfloat162_rn(x[0], x[1]), __floats2bfloat162_rn(x[2 % EPL], x[3 % EPL])};
+        *reinterpret_cast<uint2*>(dst + lane * 4) = *reinterpret_cast<uint2*>(o);
+    } else {
+        *reinterpret_cast<__nv_bfloat162*>(dst + lane * 2) = __floats2bfloat162_rn(x[0], x[1]);
+    }
+}
+
 extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void* q_gamma, const void* k_gamma,
                                          int g_dt, float eps, const float* cs, int rot_half, const int* tok_seq,
                                          const int* tok_pos, const int* block_table, int bt_stride, void* k_pages,
@@ -259,6 +382,21 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
              rot_half);
     NN_CHECK(hd <= 1024, "qk_norm_rope_append: head size %d is above 1024", hd);
     if (n_tok == 0) return 0;
+    if (in_dt == DT_F32 && q_dt == DT_BF16 && (n_kv == 0 || kv_dt == DT_BF16) && (hd == 64 || hd == 128) &&
+        (cs == nullptr || 2 * rot_half == hd) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0) {
+        const long n_items = (long)n_tok * (n_heads + 2 * n_kv);
+        const unsigned n_blocks = (unsigned)((n_items + 7) / 8);
+        if (hd == 128)
+            qk_norm_rope_append_fast_kernel<4><<<n_blocks, 256, 0, (cudaStream_t)stream>>>(
+                (const float*)qkv, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, tok_seq, tok_pos, block_table,
+                bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv);
+        else
+            qk_norm_rope_append_fast_kernel<2><<<n_blocks, 256, 0, (cudaStream_t)stream>>>(
+                (const float*)qkv, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, tok_seq, tok_pos, block_table,
+                bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv);
+        NN_LAUNCH_OK("qk_norm_rope_append");
+        return 0;
+    }
     const int warps = 4;
     const long items = (long)n_tok * (n_heads + 2 * n_kv);
     const long blocks = (items + warps - 1) / warps;

@@ -32,7 +32,7 @@ def test_embed(ops):
         assert torch.equal(out, want)
 
 
-@pytest.mark.parametrize("dim", [1, 7, 80, 129, 4096])
+@pytest.mark.parametrize("dim", [1, 7, 80, 129, 1024, 1028, 4096, 5120, 8192])
 @pytest.mark.parametrize("dt", DT)
 def test_rmsnorm(ops, dim, dt):
     g = torch.Generator().manual_seed(dim)
@@ -239,6 +239,44 @@ def test_qk_norm_rope_append(ops, nh, nkv, hd, rot, dt):
     for t in range(n):
         written[int(table[tok_seq[t], tok_pos[t] // PAGE]), tok_pos[t] % PAGE] = True
     untouched = ~written[:, None, :, None].expand(6, nkv, PAGE, hd)
+    assert bool((kp.float().cpu()[untouched] == 7.0).all()) and bool((vp.float().cpu()[untouched] == 7.0).all())
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (4, 2, 64), (3, 1, 128)])
+def test_qk_norm_rope_append_float32_in_bfloat16_out(ops, nh, nkv, hd):
+    """The combination a bfloat16 run uses: float32 projections in, bfloat16 q and cache out."""
+    g = torch.Generator().manual_seed(hd + nh)
+    new = [70, 3, 1]
+    starts = [65, 0, 200]
+    n = sum(new)
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd, generator=g)
+    qg, kg = (1 + 0.1 * torch.randn(hd, generator=g) for _ in range(2))
+    tok_seq = torch.tensor([b for b, k in enumerate(new) for _ in range(k)], dtype=torch.int32)
+    tok_pos = torch.tensor([s + i for s, k in zip(starts, new) for i in range(k)], dtype=torch.int32)
+    table = torch.tensor([[4, 1, 7, -1], [2, -1, -1, -1], [0, 3, 5, 6]], dtype=torch.int32)
+    theta = 1e6
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    cs = torch.empty(n, hd // 2, 2, device=DEV)
+    ops.rope_table(tok_pos.to(DEV), inv.float().to(DEV), cs)
+    kp = torch.full((8, nkv, PAGE, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    vp = torch.full((8, nkv, PAGE, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+    ops.qk_norm_rope_append(qkv.to(DEV), qg.bfloat16().to(DEV), kg.bfloat16().to(DEV), 1e-6, cs, tok_seq.to(DEV),
+                            tok_pos.to(DEV), table.to(DEV), kp, vp, q_out, nh, nkv, hd)
+    x = qkv.numpy()
+    q = x[:, :nh * hd].reshape(n, nh, hd)
+    k = x[:, nh * hd:(nh + nkv) * hd].reshape(n, nkv, hd)
+    v = x[:, (nh + nkv) * hd:].reshape(n, nkv, hd)
+    q = P.rope_neox(P.rmsnorm(q, qg.bfloat16().float().numpy(), 1e-6), tok_pos.numpy(), theta, hd)
+    k = P.rope_neox(P.rmsnorm(k, kg.bfloat16().float().numpy(), 1e-6), tok_pos.numpy(), theta, hd)
+    check(q_out.view(n, nh, hd), q, 8e-3, "q")
+    written = torch.zeros(8, PAGE, dtype=torch.bool)
+    for t in range(n):
+        page = int(table[tok_seq[t], tok_pos[t] // PAGE])
+        check(kp[page, :, tok_pos[t] % PAGE], k[t], 8e-3, f"k of token {t}")
+        check(vp[page, :, tok_pos[t] % PAGE], v[t], 8e-3, f"v of token {t}")
+        written[page, tok_pos[t] % PAGE] = True
+    untouched = ~written[:, None, :, None].expand(8, nkv, PAGE, hd)
     assert bool((kp.float().cpu()[untouched] == 7.0).all()) and bool((vp.float().cpu()[untouched] == 7.0).all())
 
 
