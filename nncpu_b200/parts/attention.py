@@ -81,7 +81,8 @@ class Attention(Mixer):
     def forward(self, ctx, x, residual, cache):
         s, rt = self.spec, self.rt
         n = x.shape[0]
-        qkv = rt.empty(n, self.q_size + 2 * self.kv_size)
+        # the projections stay in float32 until the per-head norm and the rotation have been applied
+        qkv = rt.empty(n, self.q_size + 2 * self.kv_size, dtype=torch.float32)
         rt.linear(x, self.w_qkv, self.b_qkv, qkv)
         cos_sin = None if self.position is None else self.position.tables(ctx)
         q = rt.empty(n, self.q_size)

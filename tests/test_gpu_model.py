@@ -130,10 +130,12 @@ def test_sharp_attention_shows_far_keys_window_edges_and_stale_rows(folders, nam
     folder.mkdir()
     (folder / "config.json").write_text((folders[name, dtype] / "config.json").read_text())
     write_safetensors(folder / "model.safetensors", tensors)
-    plain = PlainQwen3(folder)
+    # Peaked attention also amplifies the rounding of q and k to bfloat16 itself; so that the comparison
+    # measures the kernels and not the format, the bfloat16 oracle rounds its activations at the same places.
+    plain = PlainQwen3(folder, round_activations_to_bf16=(dtype == "bfloat16"))
     model = Model.load(folder, dtype=dtype)
     engine = Engine(model, max_tokens=64 * 12)
-    tol = TOL[dtype] * (1 if dtype == "float32" else 3)
+    tol = TOL[dtype]
     # a long request fills the pages; it ends; a short one reuses slot and pages and must not see its rows
     long_ = tokens_for(plain, 400, 7)
     s = engine.alloc_slot()
