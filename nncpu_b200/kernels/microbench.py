@@ -1,0 +1,150 @@
+"""Single kernels at chosen sizes, timed on the device: the library's
+counterpart of the reference's ignored micro-benchmarks
+(crates/nncpu/src/kernels/tests.rs:1295-1482), which print streaming GB/s and
+GFLOP/s for its row kernels and one attention block.
+
+    python -m nncpu_b200.kernels.microbench linear M N K [--epilogue swiglu] [--accumulate]
+    python -m nncpu_b200.kernels.microbench attention-decode BATCH CONTEXT [--splits S]
+    python -m nncpu_b200.kernels.microbench attention-prefill BATCH TOKENS
+    python -m nncpu_b200.kernels.microbench rmsnorm ROWS DIM
+
+Timing: the kernel is captured in a CUDA graph over enough different buffers
+that no launch finds its operands in L2, replayed, and timed with CUDA events.
+``--once`` runs three plain launches instead (for a profiler).  Shapes default
+to heads 32 / kv heads 8 / head size 128 for attention.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from . import ops
+
+DEV = "cuda:0"
+L2_BYTES = 126 << 20
+
+
+def _time(fns, once: bool) -> float:
+    """Milliseconds per call of the functions in ``fns`` (each a different buffer set)."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    if once:
+        for f in fns[:3]:
+            f()
+        torch.cuda.synchronize()
+        return float("nan")
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / len(fns)
+        best = ms if best is None else min(best, ms)
+    return best
+
+
+def linear(args) -> None:
+    m, n, k = args.m, args.n, args.k
+    copies = max(2, 4 * L2_BYTES // (n * k * 2) + 1)
+    ws = [torch.randn(n, k, device=DEV).bfloat16() for _ in range(copies)]
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    n_out = n // 2 if args.epilogue == "swiglu" else n
+    out = torch.zeros(m, n_out, device=DEV, dtype=torch.float32 if args.accumulate else torch.bfloat16)
+    work = ops.GemmWorkspace(DEV)
+
+    def call(w):
+        if m <= ops.SKINNY_MAX_TOKENS:
+            ops.linear_skinny(x, w, None, out, args.accumulate, args.epilogue)
+        else:
+            ops.linear_tc(x, w, None, out, work, args.accumulate, args.epilogue)
+    ms = _time([lambda w=w: call(w) for w in ws], args.once)
+    print(f"linear M={m} N={n} K={k} epilogue={args.epilogue}: {ms * 1e3:.1f} us, "
+          f"{n * k * 2 / ms / 1e6:.0f} GB/s of weights, {2 * m * n * k / ms / 1e9:.1f} TFLOP/s")
+
+
+def _cache(batch, ctx, nkv, hd, copies):
+    pages = batch * ((ctx + 63) // 64)
+    sets = [(torch.randn(pages, nkv, 64, hd, device=DEV).bfloat16(), torch.randn(pages, nkv, 64, hd, device=DEV).bfloat16())
+            for _ in range(copies)]
+    table = torch.randperm(pages, device=DEV).to(torch.int32).view(batch, -1)
+    return sets, table
+
+
+def attention_decode(args) -> None:
+    nh, nkv, hd, b, ctx = args.heads, args.kv_heads, args.head_dim, args.batch, args.context
+    kv_bytes = b * ctx * nkv * hd * 2 * 2
+    sets, table = _cache(b, ctx, nkv, hd, max(2, 4 * L2_BYTES // kv_bytes + 1))
+    seq = torch.arange(b, dtype=torch.int32, device=DEV)
+    pos = torch.full((b,), ctx - 1, dtype=torch.int32, device=DEV)
+    q = torch.randn(b, nh * hd, device=DEV).bfloat16()
+    out = torch.empty_like(q)
+    splits = args.splits or max(1, min(296 // (b * nkv), ctx // 256))
+    floats = ops.attention_decode_scratch_floats(b, nh, nkv, hd, splits)
+    scratch = torch.empty(floats, device=DEV) if floats else None
+    ms = _time([lambda kp=kp, vp=vp: ops.attention_decode_mma(q, kp, vp, table, seq, pos, out, scratch, nh, nkv, hd,
+                                                              1 / math.sqrt(hd), 0, splits) for kp, vp in sets], args.once)
+    print(f"attention-decode batch={b} context={ctx} splits={splits}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of cache")
+
+
+def attention_prefill(args) -> None:
+    nh, nkv, hd, b, t = args.heads, args.kv_heads, args.head_dim, args.batch, args.tokens
+    sets, table = _cache(b, t, nkv, hd, 1)
+    kp, vp = sets[0]
+    pos = torch.arange(t, dtype=torch.int32, device=DEV).repeat(b)
+    cu = torch.arange(b + 1, dtype=torch.int32, device=DEV) * t
+    q = torch.randn(b * t, nh * hd, device=DEV).bfloat16()
+    out = torch.empty_like(q)
+    ms = _time([lambda: ops.attention_prefill_mma(q, kp, vp, table, cu, pos, out, b, nh, nkv, hd, 1 / math.sqrt(hd), 0)] * 3,
+               args.once)
+    flops = 4.0 * nh * hd * b * t * (t + 1) / 2
+    print(f"attention-prefill batch={b} tokens={t}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s (causal)")
+
+
+def rmsnorm(args) -> None:
+    rows, dim = args.rows, args.dim
+    copies = max(2, 4 * L2_BYTES // (rows * dim * 4) + 1)
+    xs = [torch.randn(rows, dim, device=DEV) for _ in range(min(copies, 64))]
+    gamma = torch.ones(dim, device=DEV).bfloat16()
+    out = torch.empty(rows, dim, device=DEV, dtype=torch.bfloat16)
+    ms = _time([lambda x=x: ops.rmsnorm(x, gamma, 1e-6, out) for x in xs], args.once)
+    print(f"rmsnorm rows={rows} dim={dim}: {ms * 1e3:.1f} us, {rows * dim * 6 / ms / 1e6:.0f} GB/s")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--once", action="store_true", help="three plain launches, no timing (for a profiler)")
+    sub = ap.add_subparsers(dest="kernel", required=True)
+    p = sub.add_parser("linear")
+    p.add_argument("m", type=int); p.add_argument("n", type=int); p.add_argument("k", type=int)
+    p.add_argument("--epilogue", default="plain", choices=["plain", "swiglu"])
+    p.add_argument("--accumulate", action="store_true")
+    p.set_defaults(fn=linear)
+    for name, fn, a, b in (("attention-decode", attention_decode, "batch", "context"),
+                           ("attention-prefill", attention_prefill, "batch", "tokens")):
+        p = sub.add_parser(name)
+        p.add_argument(a, type=int); p.add_argument(b, type=int)
+        p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
+        p.add_argument("--head-dim", type=int, default=128); p.add_argument("--splits", type=int, default=0)
+        p.set_defaults(fn=fn)
+    p = sub.add_parser("rmsnorm")
+    p.add_argument("rows", type=int); p.add_argument("dim", type=int)
+    p.set_defaults(fn=rmsnorm)
+    args = ap.parse_args(argv)
+    args.fn(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
