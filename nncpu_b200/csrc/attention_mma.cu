@@ -555,7 +555,7 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                const int* __restrict__ cu_seqlens, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,

@@ -25,7 +25,7 @@ STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
-    for name in "ABCDE":
+    for name in "ABCDEF":
         for dtype in DTYPES:
             out[name, dtype] = make_folder(root / f"{name}_{dtype}", name, seed=ord(name), store_dtype=STORE[dtype])
     return out
@@ -41,7 +41,7 @@ def tokens_for(plain, n, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "ABCDE")
+@pytest.mark.parametrize("name", "ABCDEF")
 def test_whole_then_last_32_one_by_one(folders, plains, name, dtype):
     plain = plains[name, dtype]
     model = Model.load(folders[name, dtype], dtype=dtype)
@@ -62,7 +62,7 @@ def test_whole_then_last_32_one_by_one(folders, plains, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "ABCDE")
+@pytest.mark.parametrize("name", "ABCDEF")
 def test_unequal_batches_one_after_another(folders, plains, name, dtype):
     plain = plains[name, dtype]
     model = Model.load(folders[name, dtype], dtype=dtype)

@@ -38,6 +38,10 @@ TINY = {
               num_key_value_heads=1, head_dim=128, intermediate_size=256, vocab_size=333, rope_theta=1000000.0,
               rms_norm_eps=1e-5, tie_word_embeddings=False, attention_bias=True, max_position_embeddings=2048,
               use_sliding_window=True, sliding_window=100, layer_types=["sliding_attention", "full_attention"]),
+    # sizes that keep every fast path out: a width that is no multiple of 8, as many key/value heads as heads
+    "F": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=1, hidden_size=100, num_attention_heads=5,
+              num_key_value_heads=5, head_dim=16, intermediate_size=90, vocab_size=257, rope_theta=20000.0,
+              rms_norm_eps=2e-6, tie_word_embeddings=False, attention_bias=True, max_position_embeddings=512),
 }
 
 
