@@ -651,6 +651,210 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------
+// Many tokens: two SMs share one 256 x 256 output tile (tcgen05 cta_group::2).
+// With one SM per 128 x 256 tile, every k-block costs 48 KiB of operand traffic
+// from L2 into the SM for 512 tensor-core cycles, and the SM's input path, not
+// the tensor core, sets the pace.  A pair of SMs multiplies 256 rows of A by
+// 256 rows of B: each SM loads its own 128 rows of A but only half of the B
+// tile (the tensor cores read the other half from the partner's shared memory),
+// 32 KiB per k-block.  The first block of the pair issues the instructions for
+// both; operand arrival, stage release and accumulator hand-over are signalled
+// across the pair through mbarriers.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// A tile load whose completion is counted by a barrier that may live in the partner block.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+        "[%2];" ::"r"(smem_u32(dst)),
+        "l"((uint64_t)map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on the barrier at this shared-memory offset in both blocks of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"(mask)
+        : "memory");
+}
+
+template <int kStages, int kEpi>
+__global__ void __launch_bounds__(kThreads)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+    constexpr int BN = 256;                       // columns of the pair's tile; each block stages 128 of its B rows
+    constexpr int kBytesA = kBlockM * kBlockK * 2;
+    constexpr int kBytesB = (BN / 2) * kBlockK * 2;
+    constexpr int kTmemCols = 2 * BN;             // two accumulators of 128 lanes x 256 columns per block
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kStages * kBytesA;
+    uint64_t* full = (uint64_t*)(smem_b + kStages * kBytesB);   // used in the first block: both blocks' loads
+    uint64_t* empty = full + kStages;                           // in each block: its stage may be refilled
+    uint64_t* acc_full = empty + kStages;                       // [2] in each block
+    uint64_t* acc_empty = acc_full + 2;                         // [2] used in the first block: both epilogues
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_items = p.tiles_a * p.tiles_b;    // tiles of 256 x 256
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);       // the first block's loader arrives and announces both blocks' bytes
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);  // four epilogue warps in each block
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    cluster_barrier();   // both blocks' barriers exist before anyone signals across the pair
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int kb_run = 0;
+            bool ok = true;
+            for (int w = pair; w < n_items && ok; w += n_pairs) {
+                const int m0 = (w % p.tiles_a) * 256 + (int)rank * kBlockM;
+                const int n0 = (w / p.tiles_a) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
+                    const int s = kb_run % kStages;
+                    if (!mbar_wait(&empty[s], ((kb_run / kStages) & 1) ^ 1)) {
+                        atomicExch(p.status, kTimeoutEmpty);
+                        ok = false;
+                        break;
+                    }
+                    // The partner's copies are counted by the first block's barrier too.  They cannot complete a
+                    // phase early: the phase also needs the first block's own arrival, and a stage is refilled
+                    // only after the instructions that read it have retired in both blocks.
+                    const uint32_t bar = map_to_rank(smem_u32(&full[s]), 0);
+                    if (leader) mbar_expect_tx(&full[s], 2 * (kBytesA + kBytesB));
+                    tma_load_2d_pair(smem_a + s * kBytesA, &map_a, bar, kb * kBlockK, m0);
+                    tma_load_2d_pair(smem_b + s * kBytesB, &map_b, bar, kb * kBlockK, n0);
+                }
+            }
+            if (!ok) {
+                // copies already in flight are counted by the first block's barriers; give them time to land
+                const unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = instr_desc_bf16(256, BN);
+            int kb_run = 0, it = 0;
+            bool ok = true;
+            for (int w = pair; w < n_items && ok; w += n_pairs, ++it) {
+                const int buf = it & 1;
+                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1)) {
+                    atomicExch(p.status, kTimeoutAccumEmpty);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
+                    const int s = kb_run % kStages;
+                    if (!mbar_wait(&full[s], (kb_run / kStages) & 1)) {
+                        atomicExch(p.status, kTimeoutFull);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem_a + s * kBytesA);
+                    const uint32_t b_addr = smem_u32(smem_b + s * kBytesB);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k)
+                        umma_bf16_pair(tmem_d, smem_desc_sw128(a_addr + k * kUmmaK * 2),
+                                       smem_desc_sw128(b_addr + k * kUmmaK * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);
+                }
+                if (ok) umma_commit_pair(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        int it = 0;
+        for (int w = pair; w < n_items; w += n_pairs, ++it) {
+            const int m0 = (w % p.tiles_a) * 256 + (int)rank * kBlockM;
+            const int n0 = (w / p.tiles_a) * BN;
+            const int a_row = m0 + row_in_tile;
+            const int buf = it & 1;
+            if (!mbar_wait(&acc_full[buf], (it >> 1) & 1)) {
+                if (lane == 0) atomicExch(p.status, kTimeoutAccumFull);
+                break;
+            }
+            __syncwarp();
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr + (uint32_t)c0, v);
+                store16<kEpi>(p, a_row, n0 + c0, v);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    cluster_barrier();   // the partner may still be reading this block's half of B, or signalling its barriers
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Host side: tensor maps (cached by what they describe) and the launcher.
 // ---------------------------------------------------------------------------
 
@@ -766,6 +970,37 @@ int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, 
     return 0;
 }
 
+template <int kStages, int kEpi>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
+    constexpr size_t smem = 1024 + (size_t)kStages * (kBlockM * kBlockK * 2 + 128 * kBlockK * 2) +
+                            (2 * kStages + 4) * sizeof(uint64_t) + 16;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<kStages, kEpi>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int n_items = p.tiles_a * p.tiles_b;
+    const int max_pairs = sm_count() / 2;
+    const int pairs = n_items < max_pairs ? n_items : max_pairs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<kStages, kEpi>, ma, mb, p);
+    NN_CHECK(e == cudaSuccess, "gemm (pairs of SMs): launch failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 template <int kEpi>
 int dispatch_cluster(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
     switch (bn) {
@@ -806,6 +1041,10 @@ extern "C" int nncpu_linear_tc_tickets() { return 8192; }
 // floats) and `tickets` (nncpu_linear_tc_tickets ints, zero before the first launch) serve the
 // products that cut K into slices; launches that share them must not overlap on the GPU.  `status`
 // is a device word that a kernel sets when one of its bounded waits ran out.
+// 1: products of 512 or more tokens run on pairs of SMs (256 x 256 tiles); 0: one SM per 128 x 256 tile.
+static int pair_mode = 1;
+extern "C" void nncpu_linear_tc_set_pair_mode(int on) { pair_mode = on; }
+
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
                                int N, int K, int lda, int ldc, int accumulate, int epilogue, float* scratch,
                                int* tickets, int* status, void* stream_) {
@@ -840,6 +1079,15 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         bn = N >= 256 ? 256 : 128;
         p.rows_a = M; p.rows_b = N;
         if (int e = g_maps.get(&ma, X, M, K, lda, kBlockM)) return e;
+        if (M >= 512 && N >= 512 && pair_mode) {
+            // enough work for 256 x 256 tiles on pairs of SMs
+            if (int e = g_maps.get(&mb, W, N, K, K, 128)) return e;
+            p.tiles_a = (M + 255) / 256;
+            p.tiles_b = (N + 255) / 256;
+            p.splits = 1;
+            return epilogue == kSwiglu ? launch_pair<6, kSwiglu>(ma, mb, p, stream)
+                                       : launch_pair<6, kPlain>(ma, mb, p, stream);
+        }
         if (int e = g_maps.get(&mb, W, N, K, K, bn)) return e;
     }
     p.tiles_a = (p.rows_a + kBlockM - 1) / kBlockM;

@@ -79,7 +79,8 @@ def test_linear_simt_row_does_not_depend_on_the_batch(ops):
 
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 307, 80), (16, 1000, 512), (17, 130, 72), (64, 2048, 1024),
                                    (65, 100, 200), (128, 128, 128), (129, 384, 96), (256, 300, 264),
-                                   (257, 512, 128), (700, 307, 80), (1000, 1111, 1096)])
+                                   (257, 512, 128), (700, 307, 80), (1000, 1111, 1096), (512, 512, 64),
+                                   (513, 777, 4096), (2048, 6144, 512), (900, 520, 72)])
 def test_linear_tensor_core(ops, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
     x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
