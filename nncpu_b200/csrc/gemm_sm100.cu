@@ -29,6 +29,7 @@
 // tensor memory.
 
 #include <cuda.h>
+#include <stdlib.h>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -1112,6 +1113,7 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         // takes to put a block on most SMs, with at least 4 k-blocks per slice.
         int s = 1;
         while (s < 8 && n_tiles * s < sm_count() && p.kb_total / (2 * s) >= 4 && bn / (2 * s) >= 1) s *= 2;
+        if (const char* dbg = getenv("NNCPU_DEBUG_SPLITS")) s = atoi(dbg);
         p.splits = s;
         if (s > 1)
             return epilogue == kSwiglu ? dispatch_cluster<kSwiglu>(bn, ma, mb, p, stream)

@@ -91,7 +91,7 @@ def attention_decode(args) -> None:
     q = torch.randn(b, nh * hd, device=DEV).bfloat16()
     out = torch.empty_like(q)
     splits = args.splits or max(1, min(296 // (b * nkv), ctx // 256))
-    floats = ops.attention_decode_scratch_floats(b, nh, nkv, hd, splits)
+    floats = 0 if args.cluster else ops.attention_decode_scratch_floats(b, nh, nkv, hd, splits)
     scratch = torch.empty(floats, device=DEV) if floats else None
     ms = _time([lambda kp=kp, vp=vp: ops.attention_decode_mma(q, kp, vp, table, seq, pos, out, scratch, nh, nkv, hd,
                                                               1 / math.sqrt(hd), 0, splits) for kp, vp in sets], args.once)
@@ -137,6 +137,7 @@ def main(argv=None) -> int:
         p.add_argument(a, type=int); p.add_argument(b, type=int)
         p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
         p.add_argument("--head-dim", type=int, default=128); p.add_argument("--splits", type=int, default=0)
+        p.add_argument("--cluster", action="store_true", help="merge the splits inside a cluster (at most 8)")
         p.set_defaults(fn=fn)
     p = sub.add_parser("rmsnorm")
     p.add_argument("rows", type=int); p.add_argument("dim", type=int)

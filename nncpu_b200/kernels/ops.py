@@ -200,8 +200,10 @@ def attention_decode_scratch_floats(n_tok: int, n_heads: int, n_kv: int, head_di
 def attention_decode_mma(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, scratch, n_heads: int, n_kv: int,
                          head_dim: int, scale: float, window: int, n_splits: int) -> None:
     """One token per sequence; each token's keys are cut into ``n_splits``
-    splits that run in parallel and are merged through ``scratch`` (float32,
-    ``attention_decode_scratch_floats`` elements; None for one split)."""
+    splits that run in parallel.  With ``scratch`` (float32,
+    ``attention_decode_scratch_floats`` elements) a second kernel merges them;
+    with ``scratch`` None and at most 8 splits they form a thread-block
+    cluster and merge through distributed shared memory."""
     n = q.shape[0]
     assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape
     assert scratch is None or scratch.dtype == torch.float32

@@ -105,7 +105,9 @@ class Attention(Mixer):
             longest = min(ctx.max_kv_len, s.window) if s.window > 0 else ctx.max_kv_len
             pairs = ctx.n_tokens * s.n_kv_heads
             n_splits = max(1, min(296 // pairs, longest // 256))
-            floats = ops.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
+            # up to 8 splits merge inside a thread-block cluster; more go through scratch and a merge kernel
+            floats = 0 if n_splits <= 8 else ops.attention_decode_scratch_floats(
+                ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
             scratch = self.rt.empty(floats, dtype=torch.float32) if floats else None
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
                                      attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits)

@@ -367,7 +367,7 @@ def test_attention_tensor_core_decode(ops, nh, nkv, hd, window):
     q = torch.randn(n, nh, hd, generator=torch.Generator().manual_seed(2)).bfloat16()
     live = [i for i in range(n) if tok_seq[i] >= 0]
     want = plain_paged_attention(q.float().numpy()[live], ks, vs, tok_seq[live].tolist(), tok_pos[live].tolist(), window)
-    for n_splits in (1, 2, 5, 64):
+    for n_splits in (1, 2, 5, 8, 64):
         out = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
         floats = ops.attention_decode_scratch_floats(n, nh, nkv, hd, n_splits)
         scratch = torch.full((floats,), float("nan"), device=DEV) if floats else None
@@ -375,6 +375,11 @@ def test_attention_tensor_core_decode(ops, nh, nkv, hd, window):
                                  nh, nkv, hd, 1.0 / math.sqrt(hd), window, n_splits)
         check(out.view(n, nh, hd)[live], want, 1.5e-2, f"decode attention, {n_splits} splits")
         assert float(out[3].float().abs().sum()) == 0.0          # the padded row
+        if 1 < n_splits <= 8:                                    # the same splits merged inside a cluster
+            clustered = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+            ops.attention_decode_mma(q.view(n, -1).to(DEV), kp, vp, table, tok_seq.to(DEV), tok_pos.to(DEV), clustered,
+                                     None, nh, nkv, hd, 1.0 / math.sqrt(hd), window, n_splits)
+            assert torch.equal(clustered, out)
 
 
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 0), (8, 1, 128, 0), (6, 3, 128, 40), (16, 1, 64, 17)])
