@@ -7,8 +7,9 @@ sizes, random weights, bfloat16, on one B200.
 A "step" is one decode step of a batch of 8 sequences whose prompts are 2,048
 tokens long (context length 4,096).  ``value`` is decoded tokens per second,
 timed on the device with CUDA events over exactly K steps after W warm-up
-steps; ``e2e`` is the same workload through ``Session.generate`` with host
-token ids in and out.  The line also carries a prefill measurement (one
+steps; by default K extends the prompts to the full context (2,039 steps after
+8 warm-up steps).  ``e2e`` is the same workload through ``Session.generate``
+with host token ids in and out.  The line also carries a prefill measurement (one
 2,048-token prompt), the decode step's memory roofline, decode at batch 1 and
 64, and the SM clocks sampled during the timed region.
 """
@@ -180,7 +181,7 @@ def run_e2e(model, cfg, steps: int, warmup: int):
     g = torch.Generator().manual_seed(3)
     prompts = torch.randint(0, cfg.vocab_size, (BATCH, PROMPT), generator=g).tolist()
     steps = min(steps, CONTEXT - PROMPT - 1)
-    session.generate(prompts, GenerateParams(max_tokens=warmup, sampler=SamplerParams.greedy()), stop_token_ids=())
+    session.generate(prompts, GenerateParams(max_tokens=max(warmup, 1), sampler=SamplerParams.greedy()), stop_token_ids=())
     res = session.generate(prompts, GenerateParams(max_tokens=steps, sampler=SamplerParams.greedy()),
                            stop_token_ids=())
     n = sum(r.n_generated for r in res)
@@ -193,7 +194,7 @@ def run_e2e(model, cfg, steps: int, warmup: int):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--steps", type=int, default=CONTEXT - PROMPT)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
@@ -231,9 +232,9 @@ def main() -> int:
     launches = ops.launch_count() - launches0
     points = {}
     if not args.skip_points:
-        points["decode_b1"] = run_decode_point(model, cfg, 1, min(args.steps, 256), args.warmup)[0]
-        points["decode_b64"] = run_decode_point(model, cfg, 64, min(args.steps, 128), args.warmup)[0]
-    e2e = run_e2e(model, cfg, min(args.steps, 512), args.warmup)
+        points["decode_b1"] = run_decode_point(model, cfg, 1, args.steps, args.warmup)[0]
+        points["decode_b64"] = run_decode_point(model, cfg, 64, args.steps, args.warmup)[0]
+    e2e = run_e2e(model, cfg, args.steps, args.warmup)
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     line = {
         "metric": "decode tokens/s, Qwen3-8B sizes, bf16, batch 8, 2048-token prompts, context 4096",
