@@ -96,8 +96,11 @@ class Engine:
         self.h2d_bytes_last_step = 0
         requests, cache_of = model.cache_requests()
         rt = model.rt
+        # A sequence may grow as long as the cache lets it.  The model's own position range only sets a
+        # session's default context, as in the reference (crates/nncpu/src/session/engine.rs:113-117): rotary
+        # positions need no table, so nothing breaks beyond it.
         self.cache = Cache(requests, cache_of, max_tokens, kv_dtype or rt.dtype, rt.device, n_slots=n_slots,
-                           max_seq_len=min(max_seq_len or model.spec.max_positions, model.spec.max_positions))
+                           max_seq_len=max_seq_len)
         self.vocab_size = model.spec.vocab_size
 
     @property

@@ -70,8 +70,7 @@ class Session:
             raise InvalidArgument(f"n_ctx {params.n_ctx}, max_batch {params.max_batch}")
         self.model = model
         self.params = params
-        max_pos = model.spec.max_positions
-        self.n_ctx = min(params.n_ctx, max_pos) if params.n_ctx > 0 else min(4096, max_pos)
+        self.n_ctx = params.n_ctx if params.n_ctx > 0 else min(4096, model.spec.max_positions)
         per_seq = (self.n_ctx + PAGE - 1) // PAGE * PAGE
         self.engine = Engine(model, max_tokens=per_seq * (params.max_batch + 1), max_seq_len=self.n_ctx,
                              kv_dtype=torch.float32 if params.kv_f32 else None)

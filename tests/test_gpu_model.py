@@ -201,3 +201,19 @@ def test_float32_cache_in_a_bfloat16_run(folders, plains):
     toks = tokens_for(plains["A", "bfloat16"], 50, 3)
     s = engine.alloc_slot()
     check(engine.step([s], [toks], [list(range(50))]), plains["A", "bfloat16"].logits(toks), TOL["bfloat16"], "kv f32")
+
+
+def test_position_range_of_the_config_sets_only_the_default_context(tmp_path):
+    """max_position_embeddings is the default context of a session (crates/nncpu/src/session/engine.rs:113-117);
+    the engine itself runs a sequence as far as its cache reaches."""
+    from nncpu_b200 import Session, SessionParams
+    folder = make_folder(tmp_path / "m", "A", seed=5, max_position_embeddings=64)
+    plain = PlainQwen3(folder)
+    model = Model.load(folder, dtype="float32")
+    engine = Engine(model, max_tokens=256)
+    toks = tokens_for(plain, 150, 9)
+    s = engine.alloc_slot()
+    got = torch.cat([engine.step([s], [toks[:100]], [list(range(100))]).clone()] +
+                    [engine.step([s], [[t]]).clone() for t in toks[100:]])
+    check(got, plain.logits(toks), TOL["float32"], "beyond the configured position range")
+    assert Session(model).n_ctx == 64 and Session(model, SessionParams(n_ctx=300)).n_ctx == 300
