@@ -31,6 +31,12 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden
                 num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, attention_bias=False,
                 max_position_embeddings=40960)
+# The larger layer sizes of the benchmark description, for `--model 14b|32b` (not the default run).
+SIZES = {
+    "8b": {},
+    "14b": dict(num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408),
+    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600),
+}
 CONTEXT = 4096
 PROMPT = 2048
 BATCH = 8
@@ -191,6 +197,40 @@ def run_e2e(model, cfg, steps: int, warmup: int):
             "prefill_s": res[0].prefill, "generated": n}
 
 
+def fp32_check(cfg, name: str) -> dict:
+    """The same random weights (rounded to bfloat16) run in bfloat16 and in true float32: how far the
+    logits of a 96-token prompt, and of 8 tokens decoded after it, are apart."""
+    import torch
+    from nncpu_b200 import Engine, Model
+    from nncpu_b200.engine.model import parameter_list
+    from nncpu_b200.parts import Runtime
+    from nncpu_b200.weights import random_tensors_on_device
+    g = torch.Generator().manual_seed(11)
+    toks = torch.randint(0, cfg.vocab_size, (104,), generator=g).tolist()
+    out = {}
+    for dtype in ("bfloat16", "float32"):
+        rt = Runtime("cuda:0", torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+        tensors = random_tensors_on_device(parameter_list(cfg.model_spec()), 0, torch.bfloat16, rt.device)
+        if dtype == "float32":
+            tensors = {k: v.float() for k, v in tensors.items()}
+        model = Model(cfg, tensors, rt)
+        del tensors
+        engine = Engine(model, max_tokens=128)
+        slot = engine.alloc_slot()
+        rows = [engine.step([slot], [toks[:96]], [[0, 47, 95]]).clone()]
+        rows += [engine.step([slot], [[t]]).clone() for t in toks[96:]]
+        out[dtype] = torch.cat(rows).cpu()
+        model.rt.check_status()
+        del engine, model
+        torch.cuda.empty_cache()
+    diff = (out["bfloat16"] - out["float32"]).abs().max().item()
+    scale = out["float32"].abs().max().item()
+    agree = (out["bfloat16"].argmax(-1) == out["float32"].argmax(-1)).float().mean().item()
+    return {"check": "bfloat16 against float32 logits", "model": f"Qwen3-{name.upper()} sizes",
+            "layers": cfg.num_hidden_layers, "rows": out["float32"].shape[0], "max_abs_diff": diff,
+            "max_abs_logit": scale, "relative": diff / scale, "same_top_token": agree}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -199,6 +239,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--model", default="8b", choices=sorted(SIZES), help="layer sizes (default: the benchmark's 8b)")
+    ap.add_argument("--fp32-check", action="store_true",
+                    help="instead of timing: logits of a short prompt in bfloat16 against the true 32-bit path")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -216,12 +259,15 @@ def main() -> int:
     from nncpu_b200 import Model
     from nncpu_b200.kernels import ops
 
-    d = dict(QWEN3_8B)
+    d = dict(QWEN3_8B, **SIZES[args.model])
     full_layers = d["num_hidden_layers"]
     if args.layers:
         d["num_hidden_layers"] = args.layers
     cfg = config_from_dict(d)
     pk = peaks()
+    if args.fp32_check:
+        print(json.dumps(fp32_check(cfg, args.model)))
+        return 0
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
 
     prefill_ms = run_prefill(model, cfg)
@@ -237,12 +283,12 @@ def main() -> int:
     e2e = run_e2e(model, cfg, args.steps, args.warmup)
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     line = {
-        "metric": "decode tokens/s, Qwen3-8B sizes, bf16, batch 8, 2048-token prompts, context 4096",
+        "metric": f"decode tokens/s, Qwen3-{args.model.upper()} sizes, bf16, batch 8, 2048-token prompts, context 4096",
         "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": min(args.steps, CONTEXT - PROMPT - args.warmup - 1),
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
         "impl": "ours",
-        "config": {"model": "Qwen3-8B sizes", "layers": cfg.num_hidden_layers, "layers_of_config": full_layers,
+        "config": {"model": f"Qwen3-{args.model.upper()} sizes", "layers": cfg.num_hidden_layers, "layers_of_config": full_layers,
                    "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
