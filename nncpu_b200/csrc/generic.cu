@@ -590,6 +590,132 @@ extern "C" int nncpu_argmax(const float* logits, int* out, int n_rows, int vocab
 }
 
 // ---------------------------------------------------------------------------
+// The k best logits of each row in the sampler's ranking: higher logit first,
+// then lower id; NaN counts as -inf (crates/nncpu/src/session/sample.rs:69-88,
+// 130-152, where a k-element heap makes the same selection).  A radix select
+// over the order-preserving integer image of the floats finds the k-th value,
+// then everything above it and the lowest ids at it are gathered.  The k
+// candidates come out unordered; the host sorts them (k is small).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t float_order(float v) {
+    if (!(v == v)) v = -INFINITY;
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(1024)
+topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int* __restrict__ out_ids, int vocab, int k) {
+    __shared__ int hist[256];
+    __shared__ uint32_t prefix_s;
+    __shared__ int need_s, n_out;
+    __shared__ int seg[1024];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    // radix select, most significant byte first: after 4 rounds `prefix` is the image of the k-th largest value
+    uint32_t prefix = 0, mask = 0;
+    int need = k;   // how many of the values matching `prefix` so far are still wanted
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = tid; i < 256; i += nt) hist[i] = 0;
+        __syncthreads();
+        for (int i = tid; i < vocab; i += nt) {
+            const uint32_t u = float_order(row[i]);
+            if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int bin = 255, left = need;
+            for (; bin > 0; --bin) {
+                if (hist[bin] >= left) break;
+                left -= hist[bin];
+            }
+            prefix_s = prefix | ((uint32_t)bin << shift);
+            need_s = left;
+        }
+        __syncthreads();
+        prefix = prefix_s;
+        need = need_s;
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    // `need` values equal to the k-th value are wanted: the ones with the lowest ids.  Threads own
+    // contiguous id ranges so that a scan over the threads counts ties in id order.
+    const int per = (vocab + nt - 1) / nt;
+    const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
+    int ties = 0;
+    for (int i = lo; i < hi; ++i) ties += float_order(row[i]) == prefix;
+    seg[tid] = ties;
+    if (tid == 0) n_out = 0;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int i = 0; i < nt; ++i) { const int c = seg[i]; seg[i] = run; run += c; }
+    }
+    __syncthreads();
+    int tie_rank = seg[tid];
+    float* vals = out_vals + (size_t)blockIdx.x * k;
+    int* ids = out_ids + (size_t)blockIdx.x * k;
+    for (int i = lo; i < hi; ++i) {
+        const float v = row[i];
+        const uint32_t u = float_order(v);
+        bool take = u > prefix;
+        if (u == prefix) take = tie_rank++ < need;
+        if (take) {
+            const int at = atomicAdd(&n_out, 1);
+            if (at < k) { vals[at] = (v == v) ? v : -INFINITY; ids[at] = i; }
+        }
+    }
+}
+
+// Per row: sum over the vocabulary of exp(logit - largest logit), NaN as -inf: the denominator of the
+// distribution at temperature 1, which top-p and min-p are measured on.
+__global__ void __launch_bounds__(1024)
+row_exp_sum_kernel(const float* __restrict__ logits, double* __restrict__ out_sum, int vocab) {
+    __shared__ float red_f[32];
+    __shared__ double red_d[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float m = -INFINITY;
+    for (int i = tid; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v == v) m = fmaxf(m, v);
+    }
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red_f[warp] = m;
+    __syncthreads();
+    m = red_f[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red_f[w]);
+    double s = 0.0;
+    for (int i = tid; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v == v && v != -INFINITY) s += (double)expf(v - m);
+    }
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) red_d[warp] = s;
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red_d[w];
+        out_sum[blockIdx.x] = t;
+    }
+}
+
+extern "C" int nncpu_row_exp_sum(const float* logits, double* out_sum, int n_rows, int vocab, void* stream) {
+    NN_CHECK(n_rows >= 0 && vocab > 0, "row_exp_sum: %d rows of %d", n_rows, vocab);
+    if (n_rows == 0) return 0;
+    row_exp_sum_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, out_sum, vocab);
+    NN_LAUNCH_OK("row_exp_sum");
+    return 0;
+}
+
+extern "C" int nncpu_topk(const float* logits, float* out_vals, int* out_ids, int n_rows, int vocab, int k, void* stream) {
+    NN_CHECK(n_rows >= 0 && vocab > 0 && k > 0 && k <= vocab, "topk: %d rows of %d, k %d", n_rows, vocab, k);
+    if (n_rows == 0) return 0;
+    topk_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, out_vals, out_ids, vocab, k);
+    NN_LAUNCH_OK("topk");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
 // Temperature draw over the whole vocabulary, in token-id order:
 // p_i = exp((l_i - max) / T) in double, r = u * sum(p), the first i whose
 // running sum reaches r.  NaN counts as -inf.  `u[row]` is uniform in [0, 1).

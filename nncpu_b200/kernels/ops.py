@@ -244,6 +244,23 @@ def argmax(logits, out) -> None:
     _call("generic", "nncpu_argmax", _ptr(logits), _ptr(out), _i(n), _i(vocab), _stream())
 
 
+def topk(logits, vals, ids) -> None:
+    """The k = vals.shape[1] best entries of every row by (logit descending, id
+    ascending), NaN as -inf, in no particular order: vals float32 [n, k], ids int32 [n, k]."""
+    n, vocab = logits.shape
+    k = vals.shape[1]
+    assert logits.dtype == torch.float32 and vals.dtype == torch.float32 and ids.dtype == torch.int32
+    assert vals.shape == (n, k) and ids.shape == (n, k)
+    _call("generic", "nncpu_topk", _ptr(logits), _ptr(vals), _ptr(ids), _i(n), _i(vocab), _i(k), _stream())
+
+
+def row_exp_sum(logits, out) -> None:
+    """out[r] (float64) = sum over the row of exp(logit - the row's largest logit), NaN as -inf."""
+    n, vocab = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.float64 and out.shape == (n,)
+    _call("generic", "nncpu_row_exp_sum", _ptr(logits), _ptr(out), _i(n), _i(vocab), _stream())
+
+
 def sample_temperature(logits, uniforms, out, temperature: float) -> None:
     """One draw per row at ``temperature`` over the whole vocabulary in id
     order; uniforms float64 [n] in [0, 1)."""

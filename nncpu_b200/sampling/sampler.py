@@ -7,7 +7,11 @@
   walks the distribution in token-id order (the reference walks it in rank
   order; the distribution is the same, the token drawn for a given uniform
   number is not);
-* with top-k, top-p or min-p: the reference's chain on the host, in rank order.
+* with top-k (the default, 40): the top-k kernel picks the candidates on the
+  device and the host runs the rest of the reference's chain on those few;
+* with top-p or min-p but no top-k: the best 1024 candidates and the row's
+  softmax denominator come from the device; the host runs the chain on them and
+  reads the whole row only if neither cut falls among them.
 
 Each sequence has a generator of its own, seeded ``seed + index``, so what a
 sequence draws does not depend on which other sequences share its batch; a
@@ -21,9 +25,12 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .chain import sample_from_logits
+from .chain import sample_from_candidates, sample_from_logits
 from .params import SamplerParams
 from .rng import Mt19937_64
+
+
+_NO_TOPK_CANDIDATES = 1024
 
 
 class Sampler:
@@ -55,5 +62,29 @@ class Sampler:
             out = torch.empty(n, dtype=torch.int32, device=logits.device)
             ops.sample_temperature(logits, u, out, p.temperature)
             return out.tolist()
+        if 0 < p.top_k < self.vocab_size and p.top_k <= 1024:
+            # the device picks the k candidates; only they cross to the host, which runs the rest of the chain
+            vals = torch.empty(n, p.top_k, dtype=torch.float32, device=logits.device)
+            ids = torch.empty(n, p.top_k, dtype=torch.int32, device=logits.device)
+            ops.topk(logits, vals, ids)
+            vals, ids = vals.cpu().numpy(), ids.cpu().numpy()
+            return [sample_from_candidates(vals[r], ids[r], p, self.rng(i)) for r, i in enumerate(indices)]
+        if self.vocab_size > 4 * _NO_TOPK_CANDIDATES:
+            # no top-k: top-p and min-p nearly always cut among the best few, so fetch those and the
+            # row's denominator, and fall back to the whole row only where the cut lies further out
+            vals = torch.empty(n, _NO_TOPK_CANDIDATES, dtype=torch.float32, device=logits.device)
+            ids = torch.empty(n, _NO_TOPK_CANDIDATES, dtype=torch.int32, device=logits.device)
+            total = torch.empty(n, dtype=torch.float64, device=logits.device)
+            ops.topk(logits, vals, ids)
+            ops.row_exp_sum(logits, total)
+            vals, ids, total = vals.cpu().numpy(), ids.cpu().numpy(), total.cpu().numpy()
+            out = []
+            for r, i in enumerate(indices):
+                rng = self.rng(i)
+                t = sample_from_candidates(vals[r], ids[r], p, rng, whole_total=float(total[r]))
+                if t is None:
+                    t = sample_from_logits(logits[r].cpu().numpy(), p, rng)
+                out.append(t)
+            return out
         host = logits.to("cpu").numpy()
         return [sample_from_logits(host[r], p, self.rng(i)) for r, i in enumerate(indices)]

@@ -481,6 +481,24 @@ def test_argmax_first_largest(ops):
         assert out.tolist() == want
 
 
+def test_topk_candidates(ops):
+    rs = np.random.RandomState(3)
+    for vocab, k in ((5, 5), (40, 1), (307, 40), (5000, 40), (151936, 40), (151936, 1000)):
+        logits = (rs.randn(4, vocab) * 3).astype(np.float32)
+        logits[1, rs.randint(vocab, size=max(1, vocab // 7))] = np.nan      # NaN ranks last
+        logits[2, :] = np.round(logits[2, :])                                 # many ties: lower ids win
+        logits[3, :] = 1.5                                                    # all equal: the first k ids
+        vals = torch.empty(4, k, device=DEV)
+        ids = torch.empty(4, k, dtype=torch.int32, device=DEV)
+        ops.topk(torch.tensor(logits).to(DEV), vals, ids)
+        for r in range(4):
+            l = np.where(np.isnan(logits[r]), -np.inf, logits[r])
+            want = np.lexsort((np.arange(vocab), -l))[:k]
+            got = ids[r].cpu().numpy()
+            assert sorted(got.tolist()) == sorted(want.tolist()), (vocab, k, r)
+            assert np.array_equal(vals[r].cpu().numpy(), l[got])
+
+
 def plain_temperature_draw(row, u, temperature):
     """The draw in token-id order: p_i = exp((l_i - max) / T) in double, first i whose running sum reaches u * total."""
     ok = ~np.isnan(row)
@@ -513,6 +531,41 @@ def test_sample_temperature(ops):
     assert np.abs(freq - [0.6, 0.3, 0.1]).max() < 0.03
     with pytest.raises(ExtensionError, match="temperature"):
         ops.sample_temperature(logits, torch.zeros(4000, dtype=torch.float64, device=DEV), out, 0.0)
+
+
+def test_row_exp_sum(ops):
+    rs = np.random.RandomState(4)
+    for vocab in (3, 307, 151936):
+        logits = (rs.randn(3, vocab) * 4).astype(np.float32)
+        logits[1, 1] = np.nan
+        logits[2, 0] = -np.inf
+        out = torch.empty(3, dtype=torch.float64, device=DEV)
+        ops.row_exp_sum(torch.tensor(logits).to(DEV), out)
+        l = np.where(np.isnan(logits), -np.inf, logits).astype(np.float64)
+        want = np.exp(l - l.max(axis=1, keepdims=True)).sum(axis=1)
+        assert np.allclose(out.cpu().numpy(), want, rtol=1e-6, atol=0)
+
+
+def test_sampler_routes_match_the_plain_chain(ops):
+    """Every route of the sampler at a vocabulary large enough for the device candidates: top-k on the
+    device, candidates with the row's denominator when there is no top-k, and the whole row when a
+    flat distribution puts the cut beyond the candidates."""
+    from nncpu_b200.sampling import Sampler, SamplerParams
+    from plain_qwen3 import PlainMt19937_64, sample_chain
+    rs = np.random.RandomState(8)
+    vocab = 9001
+    rows = np.stack([(rs.randn(vocab) * s).astype(np.float32) for s in (6.0, 3.0, 1.0, 0.01)])
+    rows[1, 5] = np.nan
+    rows[2, 100:140] = rows[2].max()                      # ties at the top
+    dev = torch.tensor(rows).to(DEV)
+    for p in (SamplerParams(), SamplerParams(1.2, 7, 1.0, 0.0), SamplerParams(0.9, 2000, 0.99, 0.0),
+              SamplerParams(0.8, 0, 0.9, 0.0), SamplerParams(1.0, 0, 1.0, 0.1), SamplerParams(0.6, 0, 0.5, 0.2)):
+        sampler = Sampler(p, 21, vocab)
+        plain = [PlainMt19937_64(21 + i) for i in range(4)]
+        for _ in range(6):
+            got = sampler.choose(dev, range(4))
+            want = [sample_chain(rows[i], plain[i], p.temperature, p.top_k, p.top_p, p.min_p) for i in range(4)]
+            assert got == want, p
 
 
 def test_kernels_refuse_what_they_cannot_take(ops):

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from nncpu_b200.errors import InvalidArgument
-from nncpu_b200.sampling import Mt19937_64, SamplerParams, argmax_first, sample_from_logits
+from nncpu_b200.sampling import Mt19937_64, SamplerParams, argmax_first, sample_from_candidates, sample_from_logits
 from plain_qwen3 import PlainMt19937_64, sample_chain
 
 
@@ -60,6 +60,34 @@ def test_chain_matches_the_plain_one():
         got = sample_from_logits(logits, p, Mt19937_64(trial + 1))
         want = sample_chain(logits, PlainMt19937_64(trial + 1), p.temperature, p.top_k, p.top_p, p.min_p)
         assert got == want, (trial, p)
+
+
+def test_candidates_of_a_longer_row():
+    """The best few of a row, with the row's denominator, give the whole row's draw whenever top-p or
+    min-p cuts among them, and say so when neither does."""
+    rs = np.random.RandomState(5)
+    inside = outside = 0
+    for trial in range(200):
+        scale = float(rs.choice([0.2, 1.0, 4.0]))
+        logits = (rs.randn(500) * scale).astype(np.float32)
+        if trial % 6 == 0:
+            logits[rs.randint(500, size=9)] = np.nan
+        p = SamplerParams(float(rs.choice([0.5, 1.0, 1.4])), 0, float(rs.choice([1.0, 0.9, 0.3])),
+                          float(rs.choice([0.0, 0.02, 0.3])))
+        if not p.truncates(500):
+            continue
+        l = np.where(np.isnan(logits), -np.inf, logits).astype(np.float32)
+        best = np.lexsort((np.arange(500), -l))[:32]
+        total = float(np.exp((l - l.max()).astype(np.float32)).astype(np.float64).sum())
+        shuffle = rs.permutation(32)
+        got = sample_from_candidates(l[best][shuffle], best[shuffle], p, Mt19937_64(trial + 1), whole_total=total)
+        want = sample_chain(logits, PlainMt19937_64(trial + 1), p.temperature, 0, p.top_p, p.min_p)
+        if got is None:
+            outside += 1
+        else:
+            inside += 1
+            assert got == want, (trial, p)
+    assert inside > 50 and outside > 10
 
 
 def test_distribution_at_temperature():
