@@ -1,0 +1,520 @@
+// Prefill attention over the paged cache on the 5th-generation tensor cores
+// (bfloat16, head size 64 or 128, causal with an optional window).
+//
+// A block owns 128 consecutive new tokens of one sequence and one or two query
+// heads that share a key/value head.  It walks the pages of keys those tokens
+// may see; per page (64 keys):
+//   * a producer thread copies the page's K and V tiles to shared memory by TMA
+//     (128-byte swizzle), three pages in flight;
+//   * one thread issues tcgen05.mma: S = Q . K^T into tensor memory (two S
+//     buffers per head, so the next page's scores are computed while this
+//     page's are being turned into weights), then O += P . V with V read as
+//     an MN-major operand straight from the page's layout;
+//   * a warpgroup per head owns one query row per thread: it reads its row of
+//     S from tensor memory, scales and masks it, keeps the running maximum and
+//     sum in 32-bit, writes the weights P as bfloat16 into shared memory in
+//     the swizzled layout the tensor core reads, and, only when a row's
+//     maximum has grown by more than 2^8, rescales its row of O in tensor
+//     memory (between two O updates, never under one).
+// The output row is O / sum.  The reference computes the same attention row by
+// row (crates/nncpu/src/model/forward.rs:730-800); softmax runs in 32-bit here
+// as there.
+//
+// Every wait on an mbarrier is bounded in time; a wait that runs out sets
+// *status, the other roles run into their own limits, copies in flight are
+// waited for and the block frees its tensor memory on the common exit.
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#define NN_LIB attention_tc
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int kQRows = 128;   // query rows per block = tensor-core M
+constexpr int kKeys = kPage;  // keys per step = one cache page
+constexpr int kStages = 3;    // pages in flight
+constexpr int kStreamCols = 256;  // tensor-memory columns per head: S0 | S1 | O
+constexpr float kRescaleStep = 8.0f;  // a row's reference maximum follows its true maximum in steps of 2^8
+
+enum AttnStatus : int { kTimeoutQ = 201, kTimeoutStage = 202, kTimeoutK = 203, kTimeoutV = 204, kTimeoutS = 205,
+                        kTimeoutP = 206, kTimeoutPv = 207 };
+
+struct AttnParams {
+    const int* block_table;
+    int bt_stride;
+    const int* cu_seqlens;
+    const int* tok_pos;
+    __nv_bfloat16* out;
+    int n_seqs, n_heads, n_kv;
+    float scale2;   // softmax scale times log2(e)
+    int window;
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// Descriptor of an MN-major operand in 128-byte swizzle: rows of 64 elements (128 bytes) along MN,
+// consecutive k 128 bytes apart, groups of 8 k 1024 bytes apart, the next 64 along MN `lbo` bytes on.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr, uint32_t lbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&u)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31]), "=r"(u[32]), "=r"(u[33]), "=r"(u[34]), "=r"(u[35]), "=r"(u[36]), "=r"(u[37]), "=r"(u[38]), "=r"(u[39]), "=r"(u[40]), "=r"(u[41]), "=r"(u[42]), "=r"(u[43]), "=r"(u[44]), "=r"(u[45]), "=r"(u[46]), "=r"(u[47]), "=r"(u[48]), "=r"(u[49]), "=r"(u[50]), "=r"(u[51]), "=r"(u[52]), "=r"(u[53]), "=r"(u[54]), "=r"(u[55]), "=r"(u[56]), "=r"(u[57]), "=r"(u[58]), "=r"(u[59]), "=r"(u[60]), "=r"(u[61]), "=r"(u[62]), "=r"(u[63])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&u)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&u)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :
+        : "r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+        : "memory");
+}
+
+// Threads: warp 0 producer, warp 1 tensor-core issue and tensor memory, then one warpgroup per head.
+template <int HD, int kStreams>
+__global__ void __launch_bounds__(64 + 128 * kStreams, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+    constexpr int kSlabs = HD / 64;                 // 64-element (128-byte) column blocks of a head
+    constexpr int kQBytes = kQRows * HD * 2;        // one head's query tile
+    constexpr int kQSlab = kQRows * 128;
+    constexpr int kKvBytes = kKeys * HD * 2;        // one page of K or of V for one head
+    constexpr int kKvSlab = kKeys * 128;
+    constexpr int kPBytes = kQRows * kKeys * 2;     // one head's weights of a page
+    constexpr int kTmemCols = kStreams * kStreamCols;
+    static_assert(HD == 64 || HD == 128, "head size 64 or 128");
+    static_assert(2 * kKeys + HD <= kStreamCols, "S0, S1 and O fit a head's columns");
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_q = smem;                                   // [kStreams][kSlabs][128 rows][128 B]
+    uint8_t* smem_k = smem_q + kStreams * kQBytes;            // [kStages][kSlabs][64 keys][128 B]
+    uint8_t* smem_v = smem_k + kStages * kKvBytes;            // the same
+    uint8_t* smem_p = smem_v + kStages * kKvBytes;            // [kStreams][128 rows][128 B]
+    uint64_t* q_full = (uint64_t*)(smem_p + kStreams * kPBytes);
+    uint64_t* k_full = q_full + 1;                            // [kStages]
+    uint64_t* v_full = k_full + kStages;                      // [kStages]
+    uint64_t* kv_empty = v_full + kStages;                    // [kStages]
+    uint64_t* s_full = kv_empty + kStages;                    // [kStreams][2]
+    uint64_t* p_full = s_full + 2 * kStreams;                 // [kStreams]
+    uint64_t* pv_done = p_full + kStreams;                    // [kStreams]
+    uint32_t* tmem_slot = (uint32_t*)(pv_done + kStreams);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // the block's 128 query rows: tiles are numbered within each sequence from its end (long spans first)
+    int tile = blockIdx.y;
+    int seq = -1, q0 = 0, q_end = 0;
+    for (int b = 0; b < p.n_seqs; ++b) {
+        const int a = p.cu_seqlens[b], e = p.cu_seqlens[b + 1];
+        const int n_tiles = (e - a + kQRows - 1) / kQRows;
+        if (tile < n_tiles) {
+            seq = b;
+            q0 = a + (n_tiles - 1 - tile) * kQRows;
+            q_end = e;
+            break;
+        }
+        tile -= n_tiles;
+    }
+    if (seq < 0) return;   // the grid is an upper bound; the whole block leaves before anything is set up
+    const int n_rows = min(kQRows, q_end - q0);
+    const int pos0 = p.tok_pos[q0];                  // positions of a sequence's new tokens are consecutive
+    const int key_hi = pos0 + n_rows - 1;
+    const int key_lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
+    const int page_lo = key_lo / kKeys, page_hi = key_hi / kKeys;
+    const int n_steps = page_hi - page_lo + 1;
+    const int head0 = blockIdx.x * kStreams;
+    const int kvh = head0 / (p.n_heads / p.n_kv);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int t = 0; t < kStreams; ++t) {
+            mbar_init(&s_full[2 * t], 1);
+            mbar_init(&s_full[2 * t + 1], 1);
+            mbar_init(&p_full[t], 128);
+            mbar_init(&pv_done[t], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int* table = p.block_table + (size_t)seq * p.bt_stride;
+            mbar_expect_tx(q_full, kStreams * kQBytes);
+            for (int t = 0; t < kStreams; ++t)
+                for (int s = 0; s < kSlabs; ++s)
+                    tma_load_2d(smem_q + t * kQBytes + s * kQSlab, &map_q, q_full, (head0 + t) * HD + 64 * s, q0);
+            int issued = 0;
+            bool ok = true;
+            for (int j = 0; j < n_steps; ++j) {
+                const int st = j % kStages;
+                if (!mbar_wait(&kv_empty[st], ((j / kStages) & 1) ^ 1)) {
+                    atomicExch(p.status, kTimeoutStage);
+                    ok = false;
+                    break;
+                }
+                const int page = table[page_lo + j];
+                mbar_expect_tx(&k_full[st], kKvBytes);
+                for (int s = 0; s < kSlabs; ++s)
+                    tma_load_4d(smem_k + st * kKvBytes + s * kKvSlab, &map_k, &k_full[st], 64 * s, 0, kvh, page);
+                mbar_expect_tx(&v_full[st], kKvBytes);
+                for (int s = 0; s < kSlabs; ++s)
+                    tma_load_4d(smem_v + st * kKvBytes + s * kKvSlab, &map_v, &v_full[st], 64 * s, 0, kvh, page);
+                issued = j + 1;
+            }
+            if (!ok) {
+                // let the copies in flight land before the block gives up its shared memory
+                mbar_wait(q_full, 0);
+                for (int r = max(0, issued - kStages); r < issued; ++r) {
+                    mbar_wait(&k_full[r % kStages], (r / kStages) & 1);
+                    mbar_wait(&v_full[r % kStages], (r / kStages) & 1);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc_bf16(kQRows, kKeys);
+            constexpr uint32_t idesc_o = instr_desc_bf16(kQRows, HD) | (1u << 16);   // B (V) is MN-major
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) atomicExch(p.status, kTimeoutQ);
+            // S(j) = Q . K(j)^T for every head of the block, into S buffer j % 2
+            auto issue_scores = [&](int j) -> bool {
+                const int st = j % kStages;
+                if (!mbar_wait(&k_full[st], (j / kStages) & 1)) {
+                    atomicExch(p.status, kTimeoutK);
+                    return false;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = smem_u32(smem_k + st * kKvBytes);
+                for (int t = 0; t < kStreams; ++t) {
+                    const uint32_t q_addr = smem_u32(smem_q + t * kQBytes);
+                    const uint32_t tmem_s = tmem_base + (uint32_t)(t * kStreamCols + (j & 1) * kKeys);
+#pragma unroll
+                    for (int s = 0; s < kSlabs; ++s)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_bf16(tmem_s, smem_desc_sw128(q_addr + s * kQSlab + k * 32),
+                                      smem_desc_sw128(k_addr + s * kKvSlab + k * 32), idesc_s, (s | k) ? 1u : 0u);
+                    umma_commit(&s_full[2 * t + (j & 1)]);
+                }
+                return true;
+            };
+            if (ok) ok = issue_scores(0);
+            for (int j = 0; j < n_steps && ok; ++j) {
+                const int st = j % kStages;
+                if (j + 1 < n_steps) ok = issue_scores(j + 1);
+                for (int t = 0; t < kStreams && ok; ++t) {
+                    if (!mbar_wait(&p_full[t], j & 1)) {
+                        atomicExch(p.status, kTimeoutP);
+                        ok = false;
+                        break;
+                    }
+                    if (t == 0 && !mbar_wait(&v_full[st], (j / kStages) & 1)) {
+                        atomicExch(p.status, kTimeoutV);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t p_addr = smem_u32(smem_p + t * kPBytes);
+                    const uint32_t v_addr = smem_u32(smem_v + st * kKvBytes);
+                    const uint32_t tmem_o = tmem_base + (uint32_t)(t * kStreamCols + 2 * kKeys);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_o, smem_desc_sw128(p_addr + k * 32),
+                                  smem_desc_sw128_mn(v_addr + k * 16 * 128, kKvSlab), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&pv_done[t]);
+                }
+                if (ok) umma_commit(&kv_empty[st]);
+            }
+        }
+    } else {
+        const int t = (warp - 2) >> 2;            // which head of the block
+        const int quarter = warp & 3;             // the tensor-memory lanes this warp may touch
+        const int row = quarter * 32 + lane;
+        const int h = head0 + t;
+        const int lim_hi = row < n_rows ? pos0 + row : -1;
+        const int lim_lo = (p.window > 0 && lim_hi + 1 > p.window) ? lim_hi + 1 - p.window : 0;
+        const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * kStreamCols);
+        const uint32_t p_row = smem_u32(smem_p + t * kPBytes) + (uint32_t)row * 128u;
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_steps; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[2 * t + (j & 1)], (j >> 1) & 1));
+            if (!ok) {
+                if (lane == 0) atomicExch(p.status, kTimeoutS);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t u[64];
+            tmem_ld64(tmem_row + (uint32_t)((j & 1) * kKeys), u);
+            const int k_base = (page_lo + j) * kKeys;
+            const bool whole = k_base >= lim_lo && k_base + kKeys - 1 <= lim_hi;
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                float s = __uint_as_float(u[i]) * p.scale2;
+                if (!whole && (k_base + i < lim_lo || k_base + i > lim_hi)) s = -INFINITY;
+                u[i] = __float_as_uint(s);
+                tmax = fmaxf(tmax, s);
+            }
+            float alpha = 1.0f;
+            bool grow = false;
+            if (j == 0) {
+                m_ref = tmax;
+            } else if (tmax > m_ref + kRescaleStep) {
+                alpha = fast_exp2(m_ref - tmax);    // 0 when nothing was seen yet
+                m_ref = tmax;
+                grow = true;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const float e = fast_exp2(__uint_as_float(u[i]) - m_use);
+                u[i] = __float_as_uint(e);
+                sum += e;
+            }
+            l = l * alpha + sum;
+            if (j > 0) {
+                // the previous O update is complete: P may be overwritten and O may be touched
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1));
+                if (!ok) {
+                    if (lane == 0) atomicExch(p.status, kTimeoutPv);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_row + (uint32_t)(2 * kKeys + c0), o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tmem_row + (uint32_t)(2 * kKeys + c0), o);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            // the row's weights as bfloat16, 16 bytes at a time, chunks exchanged by the row number as the
+            // 128-byte swizzle has it
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t addr = p_row + (uint32_t)(((c ^ (row & 7)) << 4));
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                             "r"(pack_bf16(__uint_as_float(u[8 * c]), __uint_as_float(u[8 * c + 1]))),
+                             "r"(pack_bf16(__uint_as_float(u[8 * c + 2]), __uint_as_float(u[8 * c + 3]))),
+                             "r"(pack_bf16(__uint_as_float(u[8 * c + 4]), __uint_as_float(u[8 * c + 5]))),
+                             "r"(pack_bf16(__uint_as_float(u[8 * c + 6]), __uint_as_float(u[8 * c + 7])))
+                             : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&p_full[t]);
+        }
+        if (ok) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (n_steps - 1) & 1));
+            if (!ok && lane == 0) atomicExch(p.status, kTimeoutPv);
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            __nv_bfloat16* dst = p.out + (size_t)(q0 + row) * ((size_t)p.n_heads * HD) + (size_t)h * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_row + (uint32_t)(2 * kKeys + c0), o);
+                if (row < n_rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + i) = w;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor maps (cached by what they describe) and the launcher.
+// ---------------------------------------------------------------------------
+struct MapCache {
+    std::mutex lock;
+    std::map<std::tuple<const void*, long, long, long, int>, CUtensorMap> maps;
+
+    // kind 0: queries [rows, cols] in boxes of 128 rows x 64; kind 1: pages [n_pages, n_kv, 64, hd] in boxes of
+    // one head's 64 keys x 64
+    int get(CUtensorMap* out, const void* base, long d0, long d1, long d2, int kind) {
+        std::lock_guard<std::mutex> g(lock);
+        const auto key = std::make_tuple(base, d0, d1, d2, kind);
+        auto it = maps.find(key);
+        if (it == maps.end()) {
+            EncodeTiledFn fn = encode_tiled();
+            NN_CHECK(fn != nullptr, "attention (tensor cores): the driver does not offer cuTensorMapEncodeTiled");
+            CUtensorMap m;
+            CUresult r;
+            if (kind == 0) {
+                const cuuint64_t dims[2] = {(cuuint64_t)d1, (cuuint64_t)d0};
+                const cuuint64_t strides[1] = {(cuuint64_t)d1 * 2};
+                const cuuint32_t box[2] = {64, (cuuint32_t)kQRows};
+                const cuuint32_t elem[2] = {1, 1};
+                r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            } else {
+                const long n_pages = d0, n_kv = d1, hd = d2;
+                const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)kPage, (cuuint64_t)n_kv, (cuuint64_t)n_pages};
+                const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)hd * 2 * kPage,
+                                               (cuuint64_t)hd * 2 * kPage * n_kv};
+                const cuuint32_t box[4] = {64, (cuuint32_t)kPage, 1, 1};
+                const cuuint32_t elem[4] = {1, 1, 1, 1};
+                r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            }
+            NN_CHECK(r == CUDA_SUCCESS,
+                     "attention (tensor cores): cuTensorMapEncodeTiled failed with code %d (kind %d, %ld x %ld x %ld)",
+                     (int)r, kind, d0, d1, d2);
+            if (maps.size() > 65536) maps.clear();
+            it = maps.emplace(key, m).first;
+        }
+        *out = it->second;
+        return 0;
+    }
+};
+
+MapCache g_maps;
+
+template <int HD, int kStreams>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int n_tok,
+           cudaStream_t stream) {
+    constexpr int smem = kStreams * kQRows * HD * 2 + 2 * kStages * kKeys * HD * 2 + kStreams * kQRows * kKeys * 2 +
+                         256 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<HD, kStreams>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        NN_CHECK(e == cudaSuccess, "attention (tensor cores): %d bytes of shared memory refused: %s", smem,
+                 cudaGetErrorString(e));
+        configured = true;
+    }
+    // tiles: an upper bound, since the sequence boundaries live on the device; spare blocks leave at once
+    const dim3 grid(p.n_heads / kStreams, (n_tok + kQRows - 1) / kQRows + p.n_seqs);
+    prefill_tc_kernel<HD, kStreams><<<grid, 64 + 128 * kStreams, smem, stream>>>(mq, mk, mv, p);
+    NN_LAUNCH_OK("attention prefill (tensor cores)");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int nncpu_attention_prefill_tc_supported(int n_heads, int n_kv, int head_dim) {
+    return (head_dim == 64 || head_dim == 128) && n_kv > 0 && n_heads > 0 && n_heads % n_kv == 0;
+}
+
+// q and out: bfloat16 [n_tok, n_heads * head_dim]; K and V pages: bfloat16 [n_pages, n_kv, 64, head_dim] holding
+// every key the new tokens may see, their own included; cu_seqlens [n_seqs + 1] row ranges of the sequences;
+// tok_pos [n_tok] positions (consecutive within a sequence).  *status receives a code if a wait runs out.
+extern "C" int nncpu_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
+                                          const int* block_table, int bt_stride, const int* cu_seqlens,
+                                          const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads, int n_kv,
+                                          int head_dim, float scale, int window, int* status, void* stream_) {
+    NN_CHECK(nncpu_attention_prefill_tc_supported(n_heads, n_kv, head_dim),
+             "attention (tensor cores): head size %d with %d heads over %d key/value heads is not supported "
+             "(head size 64 or 128, heads a multiple of key/value heads)", head_dim, n_heads, n_kv);
+    NN_CHECK(n_tok >= 0 && n_seqs >= 0 && window >= 0 && n_pages > 0, "attention (tensor cores): %d tokens of %d sequences, %d pages",
+             n_tok, n_seqs, n_pages);
+    NN_CHECK(((uintptr_t)q % 16) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0 &&
+             ((uintptr_t)out % 16) == 0, "attention (tensor cores): operands must be 16-byte aligned");
+    NN_CHECK(status != nullptr, "attention (tensor cores): no status word");
+    if (n_tok == 0 || n_seqs == 0) return 0;
+    CUtensorMap mq, mk, mv;
+    if (int e = g_maps.get(&mq, q, n_tok, (long)n_heads * head_dim, 0, 0)) return e;
+    if (int e = g_maps.get(&mk, k_pages, n_pages, n_kv, head_dim, 1)) return e;
+    if (int e = g_maps.get(&mv, v_pages, n_pages, n_kv, head_dim, 1)) return e;
+    AttnParams p;
+    p.block_table = block_table;
+    p.bt_stride = bt_stride;
+    p.cu_seqlens = cu_seqlens;
+    p.tok_pos = tok_pos;
+    p.out = (__nv_bfloat16*)out;
+    p.n_seqs = n_seqs;
+    p.n_heads = n_heads;
+    p.n_kv = n_kv;
+    p.scale2 = scale * 1.4426950408889634f;
+    p.window = window;
+    p.status = status;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const bool pair = (n_heads / n_kv) % 2 == 0;   // two heads of a block must share their key/value head
+    if (head_dim == 64)
+        return pair ? launch<64, 2>(mq, mk, mv, p, n_tok, stream) : launch<64, 1>(mq, mk, mv, p, n_tok, stream);
+    return pair ? launch<128, 2>(mq, mk, mv, p, n_tok, stream) : launch<128, 1>(mq, mk, mv, p, n_tok, stream);
+}

@@ -28,7 +28,6 @@
 // *status and the block leaves through the common exit, which frees its
 // tensor memory.
 
-#include <cuda.h>
 #include <stdlib.h>
 #include <map>
 #include <mutex>
@@ -36,6 +35,7 @@
 
 #define NN_LIB gemm_sm100
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -43,110 +43,10 @@ constexpr int kBlockM = 128;  // rows of the A tile = tensor-core M
 constexpr int kBlockK = 64;   // 64 bfloat16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;    // K of one tcgen05.mma for 16-bit inputs
 constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA and tensor memory, warps 2-5: epilogue
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 enum GemmStatus : int { kOk = 0, kTimeoutEmpty = 101, kTimeoutFull = 102, kTimeoutAccumFull = 103,
                         kTimeoutAccumEmpty = 104 };
 enum Epilogue : int { kPlain = 0, kSwiglu = 1 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait: false when two seconds passed without the phase completing.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    while (true) {
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > kWaitLimitNs) return false;
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
-// swizzled in 128-byte mode: groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);  // start address
-    d |= (uint64_t)1 << 16;                  // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset
-    d |= (uint64_t)1 << 46;                  // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                  // 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor: bfloat16 inputs, float accumulator, both operands K-major.
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* r) {
-    uint32_t u[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
-        "%15}, [%16];"
-        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
-          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) r[i] = __uint_as_float(u[i]);
-}
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -858,22 +758,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // ---------------------------------------------------------------------------
 // Host side: tensor maps (cached by what they describe) and the launcher.
 // ---------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return (EncodeTiledFn)p;
-    }();
-    return fn;
-}
 
 // A [rows, K] bfloat16 matrix with row stride `ld` elements, cut in boxes of box_rows x 64.
 int make_map(CUtensorMap* map, const void* base, int rows, int K, long ld, int box_rows) {

@@ -25,7 +25,7 @@ from ..errors import ExtensionError
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared"]
-LIBRARIES = ("generic", "gemm_sm100", "linear_skinny", "attention_mma")
+LIBRARIES = ("generic", "gemm_sm100", "linear_skinny", "attention_mma", "attention_tc")
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

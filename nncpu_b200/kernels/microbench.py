@@ -106,8 +106,15 @@ def attention_prefill(args) -> None:
     cu = torch.arange(b + 1, dtype=torch.int32, device=DEV) * t
     q = torch.randn(b * t, nh * hd, device=DEV).bfloat16()
     out = torch.empty_like(q)
-    ms = _time([lambda: ops.attention_prefill_mma(q, kp, vp, table, cu, pos, out, b, nh, nkv, hd, 1 / math.sqrt(hd), 0)] * 3,
-               args.once)
+    if args.legacy:
+        run = lambda: ops.attention_prefill_mma(q, kp, vp, table, cu, pos, out, b, nh, nkv, hd, 1 / math.sqrt(hd), 0)
+    else:
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        run = lambda: ops.attention_prefill_tc(q, kp, vp, table, cu, pos, out, status, b, nh, nkv, hd,
+                                               1 / math.sqrt(hd), 0)
+    ms = _time([run] * 3, args.once)
+    if not args.legacy and int(status.item()):
+        raise SystemExit(f"the kernel gave up waiting (status {int(status.item())})")
     flops = 4.0 * nh * hd * b * t * (t + 1) / 2
     print(f"attention-prefill batch={b} tokens={t}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s (causal)")
 
@@ -138,6 +145,7 @@ def main(argv=None) -> int:
         p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
         p.add_argument("--head-dim", type=int, default=128); p.add_argument("--splits", type=int, default=0)
         p.add_argument("--cluster", action="store_true", help="merge the splits inside a cluster (at most 8)")
+        p.add_argument("--legacy", action="store_true", help="prefill: the mma.sync kernel instead of tcgen05")
         p.set_defaults(fn=fn)
     p = sub.add_parser("rmsnorm")
     p.add_argument("rows", type=int); p.add_argument("dim", type=int)

@@ -223,6 +223,27 @@ def attention_prefill_mma(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos,
           _i(n_kv), _i(head_dim), _f(scale), _i(window), _stream())
 
 
+def attention_prefill_tc_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) -> bool:
+    """Whether the tcgen05 prefill kernel takes these sizes (and these tensors: all bfloat16)."""
+    lib = library.load("attention_tc")
+    return bool(lib.nncpu_attention_prefill_tc_supported(n_heads, n_kv, head_dim)) and \
+        all(t.dtype == torch.bfloat16 for t in tensors)
+
+
+def attention_prefill_tc(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, status, n_seqs: int,
+                         n_heads: int, n_kv: int, head_dim: int, scale: float, window: int) -> None:
+    """Prefill attention on the tcgen05 tensor cores: any number of new tokens per sequence, at consecutive
+    positions; ``status`` is an int32 word on the device that receives a code if a bounded wait runs out."""
+    n = q.shape[0]
+    assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape and cu_seqlens.numel() >= n_seqs + 1
+    assert q.is_contiguous() and out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert k_pages.shape[1:] == (n_kv, 64, head_dim) and v_pages.shape == k_pages.shape
+    assert status.dtype == torch.int32
+    _call("attention_tc", "nncpu_attention_prefill_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(k_pages.shape[0]),
+          _ptr(block_table), _i(block_table.shape[1]), _ptr(cu_seqlens), _ptr(tok_pos), _ptr(out), _i(n), _i(n_seqs),
+          _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _ptr(status), _stream())
+
+
 def swiglu(gate_up, out) -> None:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     n, inter = out.shape

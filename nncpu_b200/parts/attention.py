@@ -95,7 +95,8 @@ class Attention(Mixer):
 
     def _attend(self, ctx, q, cache, attn):
         """bfloat16 with a head size the tensor-core kernels take: split-key
-        decode or tiled prefill; everything else: the 32-bit kernel."""
+        decode, tcgen05 prefill for prompts, mma.sync prefill for a few tokens
+        per sequence; everything else: the 32-bit kernel."""
         s = self.spec
         if not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
@@ -111,6 +112,13 @@ class Attention(Mixer):
             scratch = self.rt.empty(floats, dtype=torch.float32) if floats else None
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
                                      attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits)
+        elif ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(
+                s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
+            # prompts: 128-row tiles on the tcgen05 tensor cores
+            ops.attention_prefill_tc(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
+                                     attn, self.rt.workspace.status, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim,
+                                     s.scale, s.window)
         else:
+            # a few new tokens per sequence: 64-row tiles
             ops.attention_prefill_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
                                       attn, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)

@@ -401,6 +401,57 @@ def test_attention_tensor_core_prefill(ops, nh, nkv, hd, window):
     check(out.view(n, nh, hd), want, 1.5e-2, "prefill attention")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 0), (8, 1, 128, 0), (6, 3, 128, 40), (16, 1, 64, 17),
+                                              (3, 3, 128, 0), (5, 5, 64, 200), (8, 2, 128, 130)])
+def test_attention_tcgen05_prefill(ops, nh, nkv, hd, window):
+    """One and two heads per block (odd and even group sizes), spans that fill several 128-row tiles, start in
+    the middle of a page, end one row into a tile, and windows shorter and longer than a tile."""
+    old, new = [130, 0, 0, 64, 5, 0, 37], [70, 1, 100, 1, 16, 385, 129]
+    seqs = [o + n for o, n in zip(old, new)]
+    kp, vp, table, ks, vs = scatter_pages(32, nkv, hd, seqs, torch.bfloat16, seed=nh)
+    tok_seq = [b for b, n in enumerate(new) for _ in range(n)]
+    tok_pos = [o + i for o, n in zip(old, new) for i in range(n)]
+    cu = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    n = len(tok_seq)
+    q = torch.randn(n, nh, hd, generator=torch.Generator().manual_seed(5)).bfloat16()
+    out = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.attention_prefill_tc(q.view(n, -1).to(DEV), kp, vp, table, torch.tensor(cu).to(DEV),
+                             torch.tensor(tok_pos, dtype=torch.int32).to(DEV), out, status, len(new), nh, nkv, hd,
+                             1.0 / math.sqrt(hd), window)
+    assert int(status.item()) == 0
+    want = plain_paged_attention(q.float().numpy(), ks, vs, tok_seq, tok_pos, window)
+    check(out.view(n, nh, hd), want, 1.5e-2, "prefill attention (tcgen05)")
+
+
+def test_attention_tcgen05_prefill_growing_maximum(ops):
+    """Scores that grow along the keys make every page raise a row's running maximum by more than the
+    rescale step (head 0); scores that fall along the keys never raise it after the first page (head 1)."""
+    nh, nkv, hd, n = 2, 1, 128, 600
+    kp, vp, table, ks, vs = scatter_pages(16, nkv, hd, [n], torch.bfloat16, seed=9)
+    q = torch.randn(n, nh, hd, generator=torch.Generator().manual_seed(6)).bfloat16()
+    d = torch.randn(hd, generator=torch.Generator().manual_seed(7))
+    d = d / d.norm()
+    q[:, 0] = (d * 8).bfloat16()
+    q[:, 1] = (d * -8).bfloat16()
+    for j in range(n):
+        # score of key j for head 0: 8 * (j / 20) * sqrt(hd) / 8 / sqrt(hd) = j / 20, about 4.6 a page in log2 units
+        # (twice that between the first key of one page and the last of the next)
+        kj = (d * (j / 20.0) * math.sqrt(hd) / 8).bfloat16()
+        kp[int(table[0, j // PAGE]), 0, j % PAGE] = kj.to(DEV)
+        ks[0][j, 0] = kj.float()
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for window in (0, 150):
+        out = torch.empty(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill_tc(q.view(n, -1).to(DEV), kp, vp, table, cu, pos, out, status, 1, nh, nkv, hd,
+                                 1.0 / math.sqrt(hd), window)
+        assert int(status.item()) == 0
+        want = plain_paged_attention(q.float().numpy(), ks, vs, [0] * n, list(range(n)), window)
+        check(out.view(n, nh, hd), want, 1.5e-2, f"prefill (tcgen05), window {window}")
+
+
 def test_attention_tensor_core_far_key_and_window_edge(ops):
     nh, nkv, hd, n = 4, 1, 128, 900
     kp, vp, table, ks, vs = scatter_pages(16, nkv, hd, [n], torch.bfloat16, seed=8)
@@ -425,6 +476,12 @@ def test_attention_tensor_core_far_key_and_window_edge(ops):
         ops.attention_prefill_mma(q.view(1, -1).to(DEV), kp, vp, table, cu, last, out, 1, nh, nkv, hd,
                                   1.0 / math.sqrt(hd), window)
         check(out.view(1, nh, hd), want, 1.5e-2, f"prefill, window {window}")
+        out = torch.empty(1, nh * hd, dtype=torch.bfloat16, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops.attention_prefill_tc(q.view(1, -1).to(DEV), kp, vp, table, cu, last, out, status, 1, nh, nkv, hd,
+                                 1.0 / math.sqrt(hd), window)
+        check(out.view(1, nh, hd), want, 1.5e-2, f"prefill (tcgen05), window {window}")
+        assert (rel_err(out.view(nh, hd)[2], vs[0][far, 0]) < 2e-2) == seen and int(status.item()) == 0
 
 
 def test_attention_tensor_core_refuses_other_sizes(ops):
