@@ -136,8 +136,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     uint64_t* q_full = (uint64_t*)(smem_p + kStreams * kPBytes);
     uint64_t* k_full = q_full + 1;                            // [kStages]
     uint64_t* v_full = k_full + kStages;                      // [kStages]
-    uint64_t* kv_empty = v_full + kStages;                    // [kStages]
-    uint64_t* s_full = kv_empty + kStages;                    // [kStreams][2]
+    uint64_t* k_empty = v_full + kStages;                     // [kStages]
+    uint64_t* v_empty = k_empty + kStages;                    // [kStages]
+    uint64_t* s_full = v_empty + kStages;                     // [kStreams][2]
     uint64_t* p_full = s_full + 2 * kStreams;                 // [kStreams]
     uint64_t* pv_done = p_full + kStreams;                    // [kStreams]
     uint32_t* tmem_slot = (uint32_t*)(pv_done + kStreams);
@@ -173,7 +174,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_empty[s], 1);
         }
         for (int t = 0; t < kStreams; ++t) {
             mbar_init(&s_full[2 * t], 1);
@@ -202,31 +204,44 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             for (int t = 0; t < kStreams; ++t)
                 for (int s = 0; s < kSlabs; ++s)
                     tma_load_2d(smem_q + t * kQBytes + s * kQSlab, &map_q, q_full, (head0 + t) * HD + 64 * s, q0);
-            int issued = 0;
+            // K tiles are free again once their scores are computed, V tiles once O has been updated, so the two
+            // rings advance on their own: one thread polls both without blocking on either
+            int jk = 0, jv = 0;
             bool ok = true;
-            for (int j = 0; j < n_steps; ++j) {
-                const int st = j % kStages;
-                if (!mbar_wait(&kv_empty[st], ((j / kStages) & 1) ^ 1)) {
+            unsigned long long t0 = global_ns();
+            while (jk < n_steps || jv < n_steps) {
+                bool moved = false;
+                if (jk < n_steps && mbar_test_wait(&k_empty[jk % kStages], ((jk / kStages) & 1) ^ 1)) {
+                    const int st = jk % kStages;
+                    const int page = table[page_lo + jk];
+                    mbar_expect_tx(&k_full[st], kKvBytes);
+                    for (int s = 0; s < kSlabs; ++s)
+                        tma_load_4d(smem_k + st * kKvBytes + s * kKvSlab, &map_k, &k_full[st], 64 * s, 0, kvh, page);
+                    ++jk;
+                    moved = true;
+                }
+                if (jv < jk && mbar_test_wait(&v_empty[jv % kStages], ((jv / kStages) & 1) ^ 1)) {
+                    const int st = jv % kStages;
+                    const int page = table[page_lo + jv];
+                    mbar_expect_tx(&v_full[st], kKvBytes);
+                    for (int s = 0; s < kSlabs; ++s)
+                        tma_load_4d(smem_v + st * kKvBytes + s * kKvSlab, &map_v, &v_full[st], 64 * s, 0, kvh, page);
+                    ++jv;
+                    moved = true;
+                }
+                if (moved) {
+                    t0 = global_ns();
+                } else if (global_ns() - t0 > kWaitLimitNs) {
                     atomicExch(p.status, kTimeoutStage);
                     ok = false;
                     break;
                 }
-                const int page = table[page_lo + j];
-                mbar_expect_tx(&k_full[st], kKvBytes);
-                for (int s = 0; s < kSlabs; ++s)
-                    tma_load_4d(smem_k + st * kKvBytes + s * kKvSlab, &map_k, &k_full[st], 64 * s, 0, kvh, page);
-                mbar_expect_tx(&v_full[st], kKvBytes);
-                for (int s = 0; s < kSlabs; ++s)
-                    tma_load_4d(smem_v + st * kKvBytes + s * kKvSlab, &map_v, &v_full[st], 64 * s, 0, kvh, page);
-                issued = j + 1;
             }
             if (!ok) {
                 // let the copies in flight land before the block gives up its shared memory
                 mbar_wait(q_full, 0);
-                for (int r = max(0, issued - kStages); r < issued; ++r) {
-                    mbar_wait(&k_full[r % kStages], (r / kStages) & 1);
-                    mbar_wait(&v_full[r % kStages], (r / kStages) & 1);
-                }
+                for (int r = max(0, jk - kStages); r < jk; ++r) mbar_wait(&k_full[r % kStages], (r / kStages) & 1);
+                for (int r = max(0, jv - kStages); r < jv; ++r) mbar_wait(&v_full[r % kStages], (r / kStages) & 1);
             }
         }
     } else if (warp == 1) {
@@ -255,6 +270,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                                       smem_desc_sw128(k_addr + s * kKvSlab + k * 32), idesc_s, (s | k) ? 1u : 0u);
                     umma_commit(&s_full[2 * t + (j & 1)]);
                 }
+                umma_commit(&k_empty[st]);
                 return true;
             };
             if (ok) ok = issue_scores(0);
@@ -282,7 +298,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                                   smem_desc_sw128_mn(v_addr + k * 16 * 128, kKvSlab), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                     umma_commit(&pv_done[t]);
                 }
-                if (ok) umma_commit(&kv_empty[st]);
+                if (ok) umma_commit(&v_empty[st]);
             }
         }
     } else {
@@ -306,15 +322,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             uint32_t u[64];
             tmem_ld64(tmem_row + (uint32_t)((j & 1) * kKeys), u);
             const int k_base = (page_lo + j) * kKeys;
-            const bool whole = k_base >= lim_lo && k_base + kKeys - 1 <= lim_hi;
-            float tmax = -INFINITY;
+            if (!(k_base >= lim_lo && k_base + kKeys - 1 <= lim_hi)) {
+                // the page crosses this row's limits
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                float s = __uint_as_float(u[i]) * p.scale2;
-                if (!whole && (k_base + i < lim_lo || k_base + i > lim_hi)) s = -INFINITY;
-                u[i] = __float_as_uint(s);
-                tmax = fmaxf(tmax, s);
+                for (int i = 0; i < 64; ++i)
+                    if (k_base + i < lim_lo || k_base + i > lim_hi) u[i] = 0xff800000u;   // -inf
             }
+            // the maximum of the raw scores (the scale is positive), four chains side by side
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(u[i]));
+            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale2;
             float alpha = 1.0f;
             bool grow = false;
             if (j == 0) {
@@ -324,14 +342,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 m_ref = tmax;
                 grow = true;
             }
-            const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-            float sum = 0.0f;
+            const float neg_m = m_ref == -INFINITY ? 0.0f : 0.0f - m_ref;
+            float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
-                const float e = fast_exp2(__uint_as_float(u[i]) - m_use);
+                const float e = fast_exp2(fmaf(__uint_as_float(u[i]), p.scale2, neg_m));
                 u[i] = __float_as_uint(e);
-                sum += e;
+                sm[i & 3] += e;
             }
+            const float sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
             l = l * alpha + sum;
             if (j > 0) {
                 // the previous O update is complete: P may be overwritten and O may be touched
