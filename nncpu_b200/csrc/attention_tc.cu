@@ -3,19 +3,22 @@
 //
 // A block owns 128 consecutive new tokens of one sequence and one or two query
 // heads that share a key/value head.  It walks the pages of keys those tokens
-// may see; per page (64 keys):
-//   * a producer thread copies the page's K and V tiles to shared memory by TMA
-//     (128-byte swizzle), three pages in flight;
-//   * one thread issues tcgen05.mma: S = Q . K^T into tensor memory (two S
-//     buffers per head, so the next page's scores are computed while this
-//     page's are being turned into weights), then O += P . V with V read as
-//     an MN-major operand straight from the page's layout;
+// may see, two pages (128 keys) a step:
+//   * a producer thread copies the pages' K and V tiles to shared memory by TMA
+//     (128-byte swizzle); the K ring and the V ring advance separately, since K
+//     is free once the scores are computed and V once O has been updated;
+//   * one thread issues tcgen05.mma: S = Q . K^T into the head's columns of
+//     tensor memory, and O += P . V with P read from tensor memory (it lies
+//     over the first half of S) and V read as an MN-major operand straight
+//     from the pages' layout.  The head's next scores follow its O update at
+//     once, so the tensor core works for one head while the other head's
+//     warpgroup computes exponentials;
 //   * a warpgroup per head owns one query row per thread: it reads its row of
-//     S from tensor memory, scales and masks it, keeps the running maximum and
-//     sum in 32-bit, writes the weights P as bfloat16 into shared memory in
-//     the swizzled layout the tensor core reads, and, only when a row's
-//     maximum has grown by more than 2^8, rescales its row of O in tensor
-//     memory (between two O updates, never under one).
+//     S from tensor memory twice (largest score, then weights), scales and
+//     masks it, keeps the running maximum and sum in 32-bit, stores the
+//     weights P as bfloat16 pairs back into tensor memory, and, only when a
+//     row's maximum has grown by more than 2^8, rescales its row of O
+//     (between two O updates, never under one).
 // The output row is O / sum.  The reference computes the same attention row by
 // row (crates/nncpu/src/model/forward.rs:730-800); softmax runs in 32-bit here
 // as there.
@@ -35,9 +38,10 @@
 namespace {
 
 constexpr int kQRows = 128;   // query rows per block = tensor-core M
-constexpr int kKeys = kPage;  // keys per step = one cache page
-constexpr int kStages = 3;    // pages in flight
-constexpr int kStreamCols = 256;  // tensor-memory columns per head: S0 | S1 | O
+constexpr int kKeys = 2 * kPage;  // keys per step: two cache pages
+constexpr int kStages = 2;    // steps of K and of V in flight
+constexpr int kStreamCols = 256;  // tensor-memory columns per head: S (P over its first half) | O
+constexpr int kPOffset = 64;      // P lies over the second half of S
 constexpr float kRescaleStep = 8.0f;  // a row's reference maximum follows its true maximum in steps of 2^8
 
 enum AttnStatus : int { kTimeoutQ = 201, kTimeoutStage = 202, kTimeoutK = 203, kTimeoutV = 204, kTimeoutS = 205,
@@ -112,6 +116,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&u)[32
         : "memory");
 }
 
+// P . V with P taken from tensor memory (the A operand) and V from shared memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Threads: warp 0 producer, warp 1 tensor-core issue and tensor memory, then one warpgroup per head.
 template <int HD, int kStreams>
 __global__ void __launch_bounds__(64 + 128 * kStreams, 1)
@@ -120,28 +136,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     constexpr int kSlabs = HD / 64;                 // 64-element (128-byte) column blocks of a head
     constexpr int kQBytes = kQRows * HD * 2;        // one head's query tile
     constexpr int kQSlab = kQRows * 128;
-    constexpr int kKvBytes = kKeys * HD * 2;        // one page of K or of V for one head
-    constexpr int kKvSlab = kKeys * 128;
-    constexpr int kPBytes = kQRows * kKeys * 2;     // one head's weights of a page
+    constexpr int kPageBytes = kPage * HD * 2;      // one page of K or of V for one head
+    constexpr int kKvSlab = kKeys * 128;            // a stage holds kKeys rows of 128 bytes per column block
+    constexpr int kKvBytes = kSlabs * kKvSlab;      // one stage of K or of V
     constexpr int kTmemCols = kStreams * kStreamCols;
     static_assert(HD == 64 || HD == 128, "head size 64 or 128");
-    static_assert(2 * kKeys + HD <= kStreamCols, "S0, S1 and O fit a head's columns");
+    static_assert(kKeys + HD <= kStreamCols, "S (with P over its first half) and O fit a head's columns");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_q = smem;                                   // [kStreams][kSlabs][128 rows][128 B]
-    uint8_t* smem_k = smem_q + kStreams * kQBytes;            // [kStages][kSlabs][64 keys][128 B]
+    uint8_t* smem_k = smem_q + kStreams * kQBytes;            // [kStages][kSlabs][128 keys][128 B]
     uint8_t* smem_v = smem_k + kStages * kKvBytes;            // the same
-    uint8_t* smem_p = smem_v + kStages * kKvBytes;            // [kStreams][128 rows][128 B]
-    uint64_t* q_full = (uint64_t*)(smem_p + kStreams * kPBytes);
+    uint64_t* q_full = (uint64_t*)(smem_v + kStages * kKvBytes);
     uint64_t* k_full = q_full + 1;                            // [kStages]
     uint64_t* v_full = k_full + kStages;                      // [kStages]
     uint64_t* k_empty = v_full + kStages;                     // [kStages]
     uint64_t* v_empty = k_empty + kStages;                    // [kStages]
-    uint64_t* s_full = v_empty + kStages;                     // [kStreams][2]
-    uint64_t* p_full = s_full + 2 * kStreams;                 // [kStreams]
-    uint64_t* pv_done = p_full + kStreams;                    // [kStreams]
-    uint32_t* tmem_slot = (uint32_t*)(pv_done + kStreams);
+    uint64_t* s_full = v_empty + kStages;                     // [kStreams]
+    uint64_t* p_full = s_full + kStreams;                     // [kStreams]
+    uint64_t* o_done = p_full + kStreams;                     // [kStreams]
+    uint32_t* tmem_slot = (uint32_t*)(o_done + kStreams);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -164,8 +179,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int pos0 = p.tok_pos[q0];                  // positions of a sequence's new tokens are consecutive
     const int key_hi = pos0 + n_rows - 1;
     const int key_lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
-    const int page_lo = key_lo / kKeys, page_hi = key_hi / kKeys;
-    const int n_steps = page_hi - page_lo + 1;
+    const int page_lo = key_lo / kPage, page_hi = key_hi / kPage;
+    const int n_pages = page_hi - page_lo + 1;
+    const int n_steps = (n_pages + 1) / 2;           // two pages a step; the last step may hold one
     const int head0 = blockIdx.x * kStreams;
     const int kvh = head0 / (p.n_heads / p.n_kv);
 
@@ -178,10 +194,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             mbar_init(&v_empty[s], 1);
         }
         for (int t = 0; t < kStreams; ++t) {
-            mbar_init(&s_full[2 * t], 1);
-            mbar_init(&s_full[2 * t + 1], 1);
+            mbar_init(&s_full[t], 1);
             mbar_init(&p_full[t], 128);
-            mbar_init(&pv_done[t], 1);
+            mbar_init(&o_done[t], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -213,19 +228,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 bool moved = false;
                 if (jk < n_steps && mbar_test_wait(&k_empty[jk % kStages], ((jk / kStages) & 1) ^ 1)) {
                     const int st = jk % kStages;
-                    const int page = table[page_lo + jk];
-                    mbar_expect_tx(&k_full[st], kKvBytes);
-                    for (int s = 0; s < kSlabs; ++s)
-                        tma_load_4d(smem_k + st * kKvBytes + s * kKvSlab, &map_k, &k_full[st], 64 * s, 0, kvh, page);
+                    const int pages = min(2, n_pages - 2 * jk);
+                    mbar_expect_tx(&k_full[st], pages * kPageBytes);
+                    for (int pg = 0; pg < pages; ++pg)
+                        for (int s = 0; s < kSlabs; ++s)
+                            tma_load_4d(smem_k + st * kKvBytes + s * kKvSlab + pg * (kPage * 128), &map_k, &k_full[st],
+                                        64 * s, 0, kvh, table[page_lo + 2 * jk + pg]);
                     ++jk;
                     moved = true;
                 }
                 if (jv < jk && mbar_test_wait(&v_empty[jv % kStages], ((jv / kStages) & 1) ^ 1)) {
                     const int st = jv % kStages;
-                    const int page = table[page_lo + jv];
-                    mbar_expect_tx(&v_full[st], kKvBytes);
-                    for (int s = 0; s < kSlabs; ++s)
-                        tma_load_4d(smem_v + st * kKvBytes + s * kKvSlab, &map_v, &v_full[st], 64 * s, 0, kvh, page);
+                    const int pages = min(2, n_pages - 2 * jv);
+                    mbar_expect_tx(&v_full[st], pages * kPageBytes);
+                    for (int pg = 0; pg < pages; ++pg)
+                        for (int s = 0; s < kSlabs; ++s)
+                            tma_load_4d(smem_v + st * kKvBytes + s * kKvSlab + pg * (kPage * 128), &map_v, &v_full[st],
+                                        64 * s, 0, kvh, table[page_lo + 2 * jv + pg]);
                     ++jv;
                     moved = true;
                 }
@@ -246,59 +265,80 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc_s = instr_desc_bf16(kQRows, kKeys);
+            constexpr uint32_t idesc_s128 = instr_desc_bf16(kQRows, 128), idesc_s64 = instr_desc_bf16(kQRows, 64);
             constexpr uint32_t idesc_o = instr_desc_bf16(kQRows, HD) | (1u << 16);   // B (V) is MN-major
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(p.status, kTimeoutQ);
-            // S(j) = Q . K(j)^T for every head of the block, into S buffer j % 2
-            auto issue_scores = [&](int j) -> bool {
-                const int st = j % kStages;
-                if (!mbar_wait(&k_full[st], (j / kStages) & 1)) {
-                    atomicExch(p.status, kTimeoutK);
-                    return false;
-                }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t k_addr = smem_u32(smem_k + st * kKvBytes);
-                for (int t = 0; t < kStreams; ++t) {
-                    const uint32_t q_addr = smem_u32(smem_q + t * kQBytes);
-                    const uint32_t tmem_s = tmem_base + (uint32_t)(t * kStreamCols + (j & 1) * kKeys);
+            // S_t(i) = Q_t . K(i)^T into the head's S columns; K(i) has landed
+            auto issue_scores = [&](int t, int i) {
+                const int keys = min(2, n_pages - 2 * i) * kPage;
+                const uint32_t k_addr = smem_u32(smem_k + (i % kStages) * kKvBytes);
+                const uint32_t q_addr = smem_u32(smem_q + t * kQBytes);
+                const uint32_t tmem_s = tmem_base + (uint32_t)(t * kStreamCols);
+                const uint32_t idesc = keys == 128 ? idesc_s128 : idesc_s64;
 #pragma unroll
-                    for (int s = 0; s < kSlabs; ++s)
+                for (int s = 0; s < kSlabs; ++s)
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            umma_bf16(tmem_s, smem_desc_sw128(q_addr + s * kQSlab + k * 32),
-                                      smem_desc_sw128(k_addr + s * kKvSlab + k * 32), idesc_s, (s | k) ? 1u : 0u);
-                    umma_commit(&s_full[2 * t + (j & 1)]);
-                }
-                umma_commit(&k_empty[st]);
-                return true;
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_s, smem_desc_sw128(q_addr + s * kQSlab + k * 32),
+                                  smem_desc_sw128(k_addr + s * kKvSlab + k * 32), idesc, (s | k) ? 1u : 0u);
+                umma_commit(&s_full[t]);
             };
-            if (ok) ok = issue_scores(0);
-            for (int j = 0; j < n_steps && ok; ++j) {
-                const int st = j % kStages;
-                if (j + 1 < n_steps) ok = issue_scores(j + 1);
+            if (ok && !mbar_wait(&k_full[0], 0)) {
+                atomicExch(p.status, kTimeoutK);
+                ok = false;
+            }
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int t = 0; t < kStreams; ++t) issue_scores(t, 0);
+                umma_commit(&k_empty[0]);
+            }
+            // Per step and head: O += P . V, then at once the head's next scores (they overwrite P, which the
+            // tensor core has read by then: its instructions run in the order they were issued).  While one
+            // head's matrices are being multiplied the other head's warpgroup does its exponentials.
+            for (int i = 0; i < n_steps && ok; ++i) {
+                const int st = i % kStages;
+                const int ksteps = min(2, n_pages - 2 * i) * (kPage / 16);
+                const bool more = i + 1 < n_steps;
                 for (int t = 0; t < kStreams && ok; ++t) {
-                    if (!mbar_wait(&p_full[t], j & 1)) {
+                    if (!mbar_wait(&p_full[t], i & 1)) {
                         atomicExch(p.status, kTimeoutP);
                         ok = false;
                         break;
                     }
-                    if (t == 0 && !mbar_wait(&v_full[st], (j / kStages) & 1)) {
-                        atomicExch(p.status, kTimeoutV);
-                        ok = false;
-                        break;
+                    if (t == 0) {
+                        if (!mbar_wait(&v_full[st], (i / kStages) & 1)) {
+                            atomicExch(p.status, kTimeoutV);
+                            ok = false;
+                            break;
+                        }
+                        if (more && !mbar_wait(&k_full[(i + 1) % kStages], ((i + 1) / kStages) & 1)) {
+                            atomicExch(p.status, kTimeoutK);
+                            ok = false;
+                            break;
+                        }
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t p_addr = smem_u32(smem_p + t * kPBytes);
                     const uint32_t v_addr = smem_u32(smem_v + st * kKvBytes);
-                    const uint32_t tmem_o = tmem_base + (uint32_t)(t * kStreamCols + 2 * kKeys);
+                    const uint32_t tmem_p = tmem_base + (uint32_t)(t * kStreamCols + kPOffset);
+                    const uint32_t tmem_o = tmem_base + (uint32_t)(t * kStreamCols + kKeys);
+                    const uint64_t v_desc = smem_desc_sw128_mn(v_addr, kKvSlab);   // 16 keys on: 2048 bytes, 128 in the field
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_o, smem_desc_sw128(p_addr + k * 32),
-                                  smem_desc_sw128_mn(v_addr + k * 16 * 128, kKvSlab), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(&pv_done[t]);
+                        umma_bf16_ts(tmem_o, tmem_p + (uint32_t)(k * 8), v_desc + (uint64_t)(k * 128), idesc_o,
+                                     (i > 0 || k > 0) ? 1u : 0u);
+                    if (ksteps == 8) {
+#pragma unroll
+                        for (int k = 4; k < 8; ++k)
+                            umma_bf16_ts(tmem_o, tmem_p + (uint32_t)(k * 8), v_desc + (uint64_t)(k * 128), idesc_o, 1u);
+                    }
+                    if (more) issue_scores(t, i + 1);
+                    else umma_commit(&o_done[t]);
                 }
-                if (ok) umma_commit(&v_empty[st]);
+                if (ok) {
+                    umma_commit(&v_empty[st]);
+                    if (more) umma_commit(&k_empty[(i + 1) % kStages]);
+                }
             }
         }
     } else {
@@ -309,87 +349,83 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int lim_hi = row < n_rows ? pos0 + row : -1;
         const int lim_lo = (p.window > 0 && lim_hi + 1 > p.window) ? lim_hi + 1 - p.window : 0;
         const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * kStreamCols);
-        const uint32_t p_row = smem_u32(smem_p + t * kPBytes) + (uint32_t)row * 128u;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
-        for (int j = 0; j < n_steps; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[2 * t + (j & 1)], (j >> 1) & 1));
+        for (int i = 0; i < n_steps; ++i) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], i & 1));
             if (!ok) {
                 if (lane == 0) atomicExch(p.status, kTimeoutS);
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int halves = min(2, n_pages - 2 * i);
+            const int k_base = (page_lo + 2 * i) * kPage;
             uint32_t u[64];
-            tmem_ld64(tmem_row + (uint32_t)((j & 1) * kKeys), u);
-            const int k_base = (page_lo + j) * kKeys;
-            if (!(k_base >= lim_lo && k_base + kKeys - 1 <= lim_hi)) {
-                // the page crosses this row's limits
-#pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (k_base + i < lim_lo || k_base + i > lim_hi) u[i] = 0xff800000u;   // -inf
-            }
-            // the maximum of the raw scores (the scale is positive), four chains side by side
+            // first pass: the row's largest raw score of this step (the scale is positive)
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            for (int hf = 0; hf < halves; ++hf) {
+                tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
+                const int kb = k_base + 64 * hf;
+                if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
+                    // the page crosses this row's limits
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(u[i]));
+                    for (int c = 0; c < 64; ++c)
+                        if (kb + c < lim_lo || kb + c > lim_hi) u[c] = 0xff800000u;   // -inf
+                }
+#pragma unroll
+                for (int c = 0; c < 64; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(u[c]));
+            }
             const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale2;
             float alpha = 1.0f;
             bool grow = false;
-            if (j == 0) {
+            if (i == 0) {
                 m_ref = tmax;
             } else if (tmax > m_ref + kRescaleStep) {
                 alpha = fast_exp2(m_ref - tmax);    // 0 when nothing was seen yet
                 m_ref = tmax;
                 grow = true;
             }
+            // The O update of the step before is complete (these scores were issued after it), so O may be
+            // touched: only when some row's maximum has grown by more than the step.
+            if (i > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_row + (uint32_t)(kKeys + c0), o);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                    tmem_st32(tmem_row + (uint32_t)(kKeys + c0), o);
+                }
+            }
+            // second pass: weights, their sum, and P as bfloat16 pairs over the first half of S
             const float neg_m = m_ref == -INFINITY ? 0.0f : 0.0f - m_ref;
             float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int hf = halves - 1; hf >= 0; --hf) {   // the later keys first: their P lands on scores already read
+                tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
+                const int kb = k_base + 64 * hf;
+                if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float e = fast_exp2(fmaf(__uint_as_float(u[i]), p.scale2, neg_m));
-                u[i] = __float_as_uint(e);
-                sm[i & 3] += e;
-            }
-            const float sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
-            l = l * alpha + sum;
-            if (j > 0) {
-                // the previous O update is complete: P may be overwritten and O may be touched
-                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1));
-                if (!ok) {
-                    if (lane == 0) atomicExch(p.status, kTimeoutPv);
-                    break;
+                    for (int c = 0; c < 64; ++c)
+                        if (kb + c < lim_lo || kb + c > lim_hi) u[c] = 0xff800000u;
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, grow)) {
-#pragma unroll 1
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        uint32_t o[32];
-                        tmem_ld32(tmem_row + (uint32_t)(2 * kKeys + c0), o);
+                uint32_t w[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tmem_row + (uint32_t)(2 * kKeys + c0), o);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                for (int c = 0; c < 64; c += 2) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(u[c]), p.scale2, neg_m));
+                    const float e1 = fast_exp2(fmaf(__uint_as_float(u[c + 1]), p.scale2, neg_m));
+                    sm[c & 3] += e0;
+                    sm[(c & 3) + 1] += e1;
+                    w[c >> 1] = pack_bf16(e0, e1);
                 }
+                tmem_st32(tmem_row + (uint32_t)(kPOffset + 32 * hf), w);
             }
-            // the row's weights as bfloat16, 16 bytes at a time, chunks exchanged by the row number as the
-            // 128-byte swizzle has it
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint32_t addr = p_row + (uint32_t)(((c ^ (row & 7)) << 4));
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                             "r"(pack_bf16(__uint_as_float(u[8 * c]), __uint_as_float(u[8 * c + 1]))),
-                             "r"(pack_bf16(__uint_as_float(u[8 * c + 2]), __uint_as_float(u[8 * c + 3]))),
-                             "r"(pack_bf16(__uint_as_float(u[8 * c + 4]), __uint_as_float(u[8 * c + 5]))),
-                             "r"(pack_bf16(__uint_as_float(u[8 * c + 6]), __uint_as_float(u[8 * c + 7])))
-                             : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&p_full[t]);
         }
         if (ok) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (n_steps - 1) & 1));
+            ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], 0));
             if (!ok && lane == 0) atomicExch(p.status, kTimeoutPv);
         }
         if (ok) {
@@ -399,16 +435,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t o[32];
-                tmem_ld32(tmem_row + (uint32_t)(2 * kKeys + c0), o);
+                tmem_ld32(tmem_row + (uint32_t)(kKeys + c0), o);
                 if (row < n_rows) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
+                    for (int c = 0; c < 32; c += 8) {
                         uint4 w;
-                        w.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-                        w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                        w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                        w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c0 + i) = w;
+                        w.x = pack_bf16(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = w;
                     }
                 }
             }
@@ -476,8 +512,7 @@ MapCache g_maps;
 template <int HD, int kStreams>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int n_tok,
            cudaStream_t stream) {
-    constexpr int smem = kStreams * kQRows * HD * 2 + 2 * kStages * kKeys * HD * 2 + kStreams * kQRows * kKeys * 2 +
-                         256 + 1024;
+    constexpr int smem = kStreams * kQRows * HD * 2 + 2 * kStages * kKeys * HD * 2 + 256 + 1024;
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<HD, kStreams>,
