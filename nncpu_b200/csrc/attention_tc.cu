@@ -14,11 +14,12 @@
 //     once, so the tensor core works for one head while the other head's
 //     warpgroup computes exponentials;
 //   * a warpgroup per head owns one query row per thread: it reads its row of
-//     S from tensor memory twice (largest score, then weights), scales and
-//     masks it, keeps the running maximum and sum in 32-bit, stores the
-//     weights P as bfloat16 pairs back into tensor memory, and, only when a
-//     row's maximum has grown by more than 2^8, rescales its row of O
-//     (between two O updates, never under one).
+//     S from tensor memory, scales and masks it, and stores the weights P
+//     as bfloat16 pairs back into tensor memory, keeping sum and maximum in
+//     32-bit.  Weights are taken against a reference maximum that follows the
+//     true one in steps of 2^8: only when a row outgrows it are the row's O
+//     (between two O updates, never under one) and sum rescaled and the
+//     step's weights computed again.
 // The output row is O / sum.  The reference computes the same attention row by
 // row (crates/nncpu/src/model/forward.rs:730-800); softmax runs in 32-bit here
 // as there.
@@ -88,32 +89,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
-}
-
-__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&u)[64]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31]), "=r"(u[32]), "=r"(u[33]), "=r"(u[34]), "=r"(u[35]), "=r"(u[36]), "=r"(u[37]), "=r"(u[38]), "=r"(u[39]), "=r"(u[40]), "=r"(u[41]), "=r"(u[42]), "=r"(u[43]), "=r"(u[44]), "=r"(u[45]), "=r"(u[46]), "=r"(u[47]), "=r"(u[48]), "=r"(u[49]), "=r"(u[50]), "=r"(u[51]), "=r"(u[52]), "=r"(u[53]), "=r"(u[54]), "=r"(u[55]), "=r"(u[56]), "=r"(u[57]), "=r"(u[58]), "=r"(u[59]), "=r"(u[60]), "=r"(u[61]), "=r"(u[62]), "=r"(u[63])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&u)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&u)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        :
-        : "r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
-        : "memory");
 }
 
 // P . V with P taken from tensor memory (the A operand) and V from shared memory.
@@ -360,66 +335,69 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int halves = min(2, n_pages - 2 * i);
             const int k_base = (page_lo + 2 * i) * kPage;
-            uint32_t u[64];
-            // first pass: the row's largest raw score of this step (the scale is positive)
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            for (int hf = 0; hf < halves; ++hf) {
-                tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
-                const int kb = k_base + 64 * hf;
-                if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
-                    // the page crosses this row's limits
+            // One pass over the row's scores: weights against the reference maximum as it stands (as bfloat16
+            // pairs), their sum, and the largest score.
+            float tmax, sum;
+            uint32_t w[2][32];   // P of the two pages, stored once the reference maximum is settled: P overwrites S
+            auto weights = [&]() {
+                const float neg_m = m_ref == -INFINITY ? 0.0f : 0.0f - m_ref;
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                    for (int c = 0; c < 64; ++c)
-                        if (kb + c < lim_lo || kb + c > lim_hi) u[c] = 0xff800000u;   // -inf
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (hf < halves) {
+                        uint32_t u[64];
+                        tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
+                        const int kb = k_base + 64 * hf;
+                        if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
+                            // the page crosses this row's limits
+#pragma unroll
+                            for (int c = 0; c < 64; ++c)
+                                if (kb + c < lim_lo || kb + c > lim_hi) u[c] = 0xff800000u;   // -inf
+                        }
+#pragma unroll
+                        for (int c = 0; c < 64; c += 2) {
+                            const float s0 = __uint_as_float(u[c]), s1 = __uint_as_float(u[c + 1]);
+                            mx[c & 3] = fmaxf(mx[c & 3], s0);
+                            mx[(c & 3) + 1] = fmaxf(mx[(c & 3) + 1], s1);
+                            const float e0 = fast_exp2(fmaf(s0, p.scale2, neg_m));
+                            const float e1 = fast_exp2(fmaf(s1, p.scale2, neg_m));
+                            sm[c & 3] += e0;
+                            sm[(c & 3) + 1] += e1;
+                            w[hf][c >> 1] = pack_bf16(e0, e1);
+                        }
+                    }
                 }
-#pragma unroll
-                for (int c = 0; c < 64; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(u[c]));
-            }
-            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale2;
-            float alpha = 1.0f;
-            bool grow = false;
-            if (i == 0) {
-                m_ref = tmax;
-            } else if (tmax > m_ref + kRescaleStep) {
-                alpha = fast_exp2(m_ref - tmax);    // 0 when nothing was seen yet
-                m_ref = tmax;
-                grow = true;
-            }
-            // The O update of the step before is complete (these scores were issued after it), so O may be
-            // touched: only when some row's maximum has grown by more than the step.
-            if (i > 0 && __any_sync(0xffffffffu, grow)) {
+                tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale2;   // the scale is positive
+                sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
+            };
+            weights();
+            // A row whose largest score has outgrown its reference by more than the step (or that sees its first
+            // key) moves the reference; then O, the sum so far and this step's weights follow.  The O update of
+            // the step before is complete (these scores were issued after it), so O may be touched.
+            const bool grow = tmax > m_ref + kRescaleStep || (m_ref == -INFINITY && tmax > -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {
+                float alpha = 1.0f;
+                if (grow) {
+                    alpha = fast_exp2(m_ref - tmax);    // 0 when nothing was seen yet
+                    m_ref = tmax;
+                    l *= alpha;
+                }
+                if (i > 0) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < HD; c0 += 32) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem_row + (uint32_t)(kKeys + c0), o);
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_row + (uint32_t)(kKeys + c0), o);
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-                    tmem_st32(tmem_row + (uint32_t)(kKeys + c0), o);
+                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                        tmem_st32(tmem_row + (uint32_t)(kKeys + c0), o);
+                    }
                 }
+                weights();
             }
-            // second pass: weights, their sum, and P as bfloat16 pairs over the first half of S
-            const float neg_m = m_ref == -INFINITY ? 0.0f : 0.0f - m_ref;
-            float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            for (int hf = halves - 1; hf >= 0; --hf) {   // the later keys first: their P lands on scores already read
-                tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
-                const int kb = k_base + 64 * hf;
-                if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
-#pragma unroll
-                    for (int c = 0; c < 64; ++c)
-                        if (kb + c < lim_lo || kb + c > lim_hi) u[c] = 0xff800000u;
-                }
-                uint32_t w[32];
-#pragma unroll
-                for (int c = 0; c < 64; c += 2) {
-                    const float e0 = fast_exp2(fmaf(__uint_as_float(u[c]), p.scale2, neg_m));
-                    const float e1 = fast_exp2(fmaf(__uint_as_float(u[c + 1]), p.scale2, neg_m));
-                    sm[c & 3] += e0;
-                    sm[(c & 3) + 1] += e1;
-                    w[c >> 1] = pack_bf16(e0, e1);
-                }
-                tmem_st32(tmem_row + (uint32_t)(kPOffset + 32 * hf), w);
-            }
-            l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
+            l += sum;
+            tmem_st32(tmem_row + (uint32_t)kPOffset, w[0]);
+            if (halves == 2) tmem_st32(tmem_row + (uint32_t)(kPOffset + 32), w[1]);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&p_full[t]);

@@ -28,7 +28,6 @@
 // *status and the block leaves through the common exit, which frees its
 // tensor memory.
 
-#include <stdlib.h>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -46,11 +45,28 @@ constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA and tensor memory, wa
 
 enum GemmStatus : int { kOk = 0, kTimeoutEmpty = 101, kTimeoutFull = 102, kTimeoutAccumFull = 103,
                         kTimeoutAccumEmpty = 104 };
-enum Epilogue : int { kPlain = 0, kSwiglu = 1 };
+enum Epilogue : int { kPlain = 0, kSwiglu = 1, kQkv = 2 };
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
+
+// What the fused q/k/v epilogue needs: the output columns are heads of 128 (queries, then keys, then values).
+struct QkvParams {
+    __nv_bfloat16* q_out;      // [tokens, n_heads * 128]
+    __nv_bfloat16* k_pages;    // [pages, n_kv, 64, 128]
+    __nv_bfloat16* v_pages;
+    const void* q_gamma;       // per-head norm weights, or null
+    const void* k_gamma;
+    int g_dt;
+    float eps;
+    const float2* cos_sin;     // [64, tokens] (cos, sin) of pair i at each token's position, or null
+    const int* tok_seq;        // the cache slot of each token (-1: none)
+    const int* tok_pos;
+    const int* block_table;
+    int bt_stride;
+    int n_heads, n_kv;
+};
 
 struct GemmParams {
     int rows_a, rows_b, K;
@@ -65,6 +81,7 @@ struct GemmParams {
     float* scratch;  // partial tiles of the K slices: [tile][slice][BN][128] floats
     int* tickets;    // one counter per output tile, zero between launches
     int* status;
+    QkvParams qkv;     // epilogue kQkv only
 };
 
 // Stores up to 16 accumulator values of one thread: A row `a_row`, B rows b0 .. b0 + ncols - 1
@@ -568,12 +585,6 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t ra
     return remote;
 }
 
-__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
-                 "r"(bytes)
-                 : "memory");
-}
-
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -609,6 +620,95 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
         : "memory");
 }
 
+// The q/k/v epilogue of one thread: its token's 256 accumulator columns are two whole heads.  Query and key
+// heads get the per-head RMS norm (32-bit sum over the head) and the rotation of the pairs (i, i + 64); value
+// heads are only rounded.  Queries go to q_out, keys and values to the token's place in the cache pages.
+// The same arithmetic as the separate kernel (x * scale * gamma, then the rotation), so prefill and decode
+// agree to rounding (crates/nncpu/src/model/forward.rs:681-728).
+__device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float (*s_gamma)[128], uint32_t taddr,
+                                               int a_row, int n0) {
+    const QkvParams& e = p.qkv;
+    const bool row_ok = a_row < p.rows_a;
+    // where this token's keys and values go
+    long kv_row = -1;
+    if (row_ok) {
+        const int seq = e.tok_seq[a_row];
+        if (seq >= 0) {
+            const int pos = e.tok_pos[a_row];
+            const int page = e.block_table[(size_t)seq * e.bt_stride + pos / kPage];
+            if (page >= 0) kv_row = (long)page * e.n_kv * kPage + pos % kPage;
+        }
+    }
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        const int head = n0 / 128 + hh;
+        if (head >= e.n_heads + 2 * e.n_kv) break;
+        const bool is_q = head < e.n_heads, is_k = !is_q && head < e.n_heads + e.n_kv;
+        const uint32_t t0 = taddr + (uint32_t)(128 * hh);
+        const void* gamma = is_q ? e.q_gamma : (is_k ? e.k_gamma : nullptr);
+        float scale = 1.0f;
+        if (gamma) {
+            float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 64) {
+                uint32_t u[64];
+                tmem_ld64(t0 + (uint32_t)c0, u);
+#pragma unroll
+                for (int c = 0; c < 64; ++c) ss[c & 3] = fmaf(__uint_as_float(u[c]), __uint_as_float(u[c]), ss[c & 3]);
+            }
+            scale = 1.0f / sqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) * (1.0f / 128.0f) + e.eps);
+        }
+        __nv_bfloat16* dst = nullptr;
+        if (row_ok) {
+            if (is_q) {
+                dst = e.q_out + ((size_t)a_row * e.n_heads + head) * 128;
+            } else if (kv_row >= 0) {
+                const int kvh = is_k ? head - e.n_heads : head - e.n_heads - e.n_kv;
+                dst = (is_k ? e.k_pages : e.v_pages) + ((size_t)kv_row + (size_t)kvh * kPage) * 128;
+            }
+        }
+        const bool rotate = (is_q || is_k) && e.cos_sin != nullptr;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+            uint32_t lo[32], hi[32];   // dimensions c0 .. c0 + 31 and their partners 64 on
+            tmem_ld32(t0 + (uint32_t)c0, lo);
+            tmem_ld32(t0 + (uint32_t)(64 + c0), hi);
+            if (dst == nullptr) continue;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                float a = __uint_as_float(lo[c]), b = __uint_as_float(hi[c]);
+                if (gamma) {
+                    a = (a * scale) * s_gamma[is_q ? 0 : 1][c0 + c];
+                    b = (b * scale) * s_gamma[is_q ? 0 : 1][64 + c0 + c];
+                }
+                if (rotate) {
+                    const float2 cs = e.cos_sin[(size_t)(c0 + c) * p.rows_a + a_row];   // lanes are tokens
+                    const float ra = cs.x * a - cs.y * b, rb = cs.y * a + cs.x * b;
+                    a = ra;
+                    b = rb;
+                }
+                lo[c] = __float_as_uint(a);
+                hi[c] = __float_as_uint(b);
+            }
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+                uint4 w;
+                __nv_bfloat162 h2;
+                h2 = __floats2bfloat162_rn(__uint_as_float(lo[c]), __uint_as_float(lo[c + 1])); w.x = *reinterpret_cast<uint32_t*>(&h2);
+                h2 = __floats2bfloat162_rn(__uint_as_float(lo[c + 2]), __uint_as_float(lo[c + 3])); w.y = *reinterpret_cast<uint32_t*>(&h2);
+                h2 = __floats2bfloat162_rn(__uint_as_float(lo[c + 4]), __uint_as_float(lo[c + 5])); w.z = *reinterpret_cast<uint32_t*>(&h2);
+                h2 = __floats2bfloat162_rn(__uint_as_float(lo[c + 6]), __uint_as_float(lo[c + 7])); w.w = *reinterpret_cast<uint32_t*>(&h2);
+                *reinterpret_cast<uint4*>(dst + c0 + c) = w;
+                h2 = __floats2bfloat162_rn(__uint_as_float(hi[c]), __uint_as_float(hi[c + 1])); w.x = *reinterpret_cast<uint32_t*>(&h2);
+                h2 = __floats2bfloat162_rn(__uint_as_float(hi[c + 2]), __uint_as_float(hi[c + 3])); w.y = *reinterpret_cast<uint32_t*>(&h2);
+                h2 = __floats2bfloat162_rn(__uint_as_float(hi[c + 4]), __uint_as_float(hi[c + 5])); w.z = *reinterpret_cast<uint32_t*>(&h2);
+                h2 = __floats2bfloat162_rn(__uint_as_float(hi[c + 6]), __uint_as_float(hi[c + 7])); w.w = *reinterpret_cast<uint32_t*>(&h2);
+                *reinterpret_cast<uint4*>(dst + 64 + c0 + c) = w;
+            }
+        }
+    }
+}
+
 template <int kStages, int kEpi>
 __global__ void __launch_bounds__(kThreads)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -627,6 +727,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* acc_empty = acc_full + 2;                         // [2] used in the first block: both epilogues
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
+    __shared__ float s_gamma[kEpi == kQkv ? 2 : 1][128];   // the q and k norm weights of the fused q/k/v epilogue
+    if constexpr (kEpi == kQkv) {
+        for (int i = threadIdx.x; i < 256; i += kThreads) {
+            const void* gamma = i < 128 ? p.qkv.q_gamma : p.qkv.k_gamma;
+            s_gamma[i >> 7][i & 127] = gamma ? ld_f(gamma, i & 127, p.qkv.g_dt) : 1.0f;
+        }
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
@@ -734,11 +841,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+            if constexpr (kEpi == kQkv) {
+                store_qkv_tile(p, s_gamma, taddr, a_row, n0);
+            } else {
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                tmem_ld16(taddr + (uint32_t)c0, v);
-                store16<kEpi>(p, a_row, n0 + c0, v);
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + (uint32_t)c0, v);
+                    store16<kEpi>(p, a_row, n0 + c0, v);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -920,6 +1031,49 @@ extern "C" int nncpu_linear_tc_supported(int M, int N, int K, int lda) {
 extern "C" long nncpu_linear_tc_scratch_floats() { return 4l << 20; }  // 16 MiB
 extern "C" int nncpu_linear_tc_tickets() { return 8192; }
 
+// The q/k/v projection of a prompt with its epilogue fused: X[M, K] . W[(n_heads + 2 n_kv) * 128, K]^T, then per
+// head the RMS norm (q and k, if their weights are given), the rotation (if cos_sin is given) and the stores:
+// queries to q_out [M, n_heads * 128], keys and values to each token's row of the cache pages.  No bias.
+extern "C" int nncpu_linear_tc_qkv_supported(int M, int K, int lda, int n_heads, int n_kv, int head_dim) {
+    return M >= 512 && K > 0 && K % 8 == 0 && lda % 8 == 0 && head_dim == 128 && n_heads > 0 && n_kv > 0 &&
+           n_heads % 2 == 0 && n_kv % 2 == 0;
+}
+
+extern "C" int nncpu_linear_tc_qkv(const void* X, const void* W, int M, int K, int lda, void* q_out, void* k_pages,
+                                   void* v_pages, const void* q_gamma, const void* k_gamma, int g_dt, float eps,
+                                   const float* cos_sin, const int* tok_seq, const int* tok_pos, const int* block_table,
+                                   int bt_stride, int n_heads, int n_kv, int head_dim, int* status, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    NN_CHECK(nncpu_linear_tc_qkv_supported(M, K, lda, n_heads, n_kv, head_dim),
+             "gemm (q/k/v epilogue): M %d, K %d, lda %d, %d heads over %d of size %d: it takes 512 or more tokens, "
+             "head size 128, even head counts, K and lda multiples of 8", M, K, lda, n_heads, n_kv, head_dim);
+    NN_CHECK(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)q_out % 16) == 0 &&
+             ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0,
+             "gemm (q/k/v epilogue): operands must be 16-byte aligned");
+    NN_CHECK(tok_seq && tok_pos && block_table && status, "gemm (q/k/v epilogue): token places and status are needed");
+    const int N = (n_heads + 2 * n_kv) * 128;
+    GemmParams p{};
+    p.K = K;
+    p.kb_total = (K + kBlockK - 1) / kBlockK;
+    p.status = status;
+    p.swap = 0;
+    p.rows_a = M; p.rows_b = N;
+    p.tiles_a = (M + 255) / 256;
+    p.tiles_b = N / 256;
+    p.splits = 1;
+    p.qkv.q_out = (__nv_bfloat16*)q_out;
+    p.qkv.k_pages = (__nv_bfloat16*)k_pages;
+    p.qkv.v_pages = (__nv_bfloat16*)v_pages;
+    p.qkv.q_gamma = q_gamma; p.qkv.k_gamma = k_gamma; p.qkv.g_dt = g_dt; p.qkv.eps = eps;
+    p.qkv.cos_sin = (const float2*)cos_sin;
+    p.qkv.tok_seq = tok_seq; p.qkv.tok_pos = tok_pos; p.qkv.block_table = block_table; p.qkv.bt_stride = bt_stride;
+    p.qkv.n_heads = n_heads; p.qkv.n_kv = n_kv;
+    CUtensorMap ma, mb;
+    if (int e = g_maps.get(&ma, X, M, K, lda, kBlockM)) return e;
+    if (int e = g_maps.get(&mb, W, N, K, K, 128)) return e;
+    return launch_pair<6, kQkv>(ma, mb, p, stream);
+}
+
 // C[M, N] (+)= X[M, K] . W[N, K]^T + bias, or with epilogue 1: C[M, N/2] = silu(gate) * up for W rows
 // interleaved in blocks of 8 (8 gate rows, the 8 up rows of the same outputs, ...).  X and W are
 // bfloat16; C is float or bfloat16 with row stride ldc.  `scratch` (nncpu_linear_tc_scratch_floats
@@ -997,7 +1151,6 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         // takes to put a block on most SMs, with at least 4 k-blocks per slice.
         int s = 1;
         while (s < 8 && n_tiles * s < sm_count() && p.kb_total / (2 * s) >= 4 && bn / (2 * s) >= 1) s *= 2;
-        if (const char* dbg = getenv("NNCPU_DEBUG_SPLITS")) s = atoi(dbg);
         p.splits = s;
         if (s > 1)
             return epilogue == kSwiglu ? dispatch_cluster<kSwiglu>(bn, ma, mb, p, stream)

@@ -218,14 +218,15 @@ extern "C" int nncpu_linear_simt(const void* A, int a_dt, const void* W, int w_d
 }
 
 // ---------------------------------------------------------------------------
-// Rotation table of a step: cs[t, i] = (cos, sin)(float(pos_t) * pos_scale * inv_freq[i]).
+// Rotation table of a step: cs[t, i] = (cos, sin)(float(pos_t) * pos_scale * inv_freq[i]), or with
+// by_pair the same values laid out [i, t] for readers whose lanes are tokens.
 // Computed once per step and read by every layer that shares the encoding.
 // ---------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ cs, int n_tok, int half, float pos_scale) {
+                                  float2* __restrict__ cs, int n_tok, int half, float pos_scale, int by_pair) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_tok * half) return;
-    const int t = idx / half, i = idx % half;
+    const int t = by_pair ? idx % n_tok : idx / half, i = by_pair ? idx / n_tok : idx % half;
     const float theta = ((float)pos[t] * pos_scale) * inv_freq[i];
     float s, c;
     sincosf(theta, &s, &c);
@@ -233,12 +234,12 @@ __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __re
 }
 
 extern "C" int nncpu_rope_table(const int* pos, const float* inv_freq, float* cs, int n_tok, int half,
-                                float pos_scale, void* stream) {
+                                float pos_scale, int by_pair, void* stream) {
     NN_CHECK(n_tok >= 0 && half > 0, "rope_table: %d tokens, %d pairs", n_tok, half);
     if (n_tok == 0) return 0;
     const int total = n_tok * half;
     rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(pos, inv_freq, (float2*)cs, n_tok,
-                                                                             half, pos_scale);
+                                                                             half, pos_scale, by_pair);
     NN_LAUNCH_OK("rope_table");
     return 0;
 }

@@ -135,6 +135,33 @@ def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = Fals
           _ptr(workspace.scratch), _ptr(workspace.tickets), _ptr(workspace.status), _stream())
 
 
+def linear_tc_qkv_supported(x, n_heads: int, n_kv: int, head_dim: int) -> bool:
+    """Whether the q/k/v projection of these tokens can run with its epilogue fused."""
+    lib = library.load("gemm_sm100")
+    return x.dtype == torch.bfloat16 and bool(
+        lib.nncpu_linear_tc_qkv_supported(x.shape[0], x.shape[1], x.stride(0), n_heads, n_kv, head_dim))
+
+
+def linear_tc_qkv(x, w_qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, block_table, k_pages, v_pages, q_out,
+                  workspace: GemmWorkspace, n_heads: int, n_kv: int, head_dim: int) -> None:
+    """x . w_qkv^T with the per-head norm, the rotation and the stores fused into the product's epilogue:
+    queries to ``q_out``, keys and values to the tokens' rows of the cache pages.  bfloat16 throughout,
+    32-bit accumulators, norm and rotation.  ``cos_sin`` is the rotation table laid out by pair:
+    float32 [head_dim / 2, tokens, 2]."""
+    m, k = x.shape
+    assert w_qkv.shape == ((n_heads + 2 * n_kv) * head_dim, k) and q_out.shape == (m, n_heads * head_dim)
+    assert x.dtype == w_qkv.dtype == q_out.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16
+    assert q_out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert k_pages.shape[1:] == (n_kv, 64, head_dim) and v_pages.shape == k_pages.shape
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (head_dim // 2, m, 2))
+    assert q_gamma is None or k_gamma is None or q_gamma.dtype == k_gamma.dtype
+    g = q_gamma if q_gamma is not None else k_gamma
+    _call("gemm_sm100", "nncpu_linear_tc_qkv", _ptr(x), _ptr(w_qkv), _i(m), _i(k), _i(x.stride(0)), _ptr(q_out),
+          _ptr(k_pages), _ptr(v_pages), _ptr(q_gamma), _ptr(k_gamma), _i(_code(g)), _f(eps), _ptr(cos_sin),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table), _i(block_table.shape[1]), _i(n_heads), _i(n_kv),
+          _i(head_dim), _ptr(workspace.status), _stream())
+
+
 SKINNY_MAX_TOKENS = 16
 
 
@@ -150,13 +177,17 @@ def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "pl
           _stream())
 
 
-def rope_table(positions, inv_freq, out, position_scale: float = 1.0) -> None:
-    """out[t, i] = (cos, sin)(positions[t] * position_scale * inv_freq[i]); out float32 [n, half, 2]."""
-    n, half, two = out.shape
+def rope_table(positions, inv_freq, out, position_scale: float = 1.0, by_pair: bool = False) -> None:
+    """out[t, i] = (cos, sin)(positions[t] * position_scale * inv_freq[i]); out float32 [n, half, 2], or with
+    ``by_pair`` [half, n, 2] holding the same values as out[i, t]."""
+    if by_pair:
+        half, n, two = out.shape
+    else:
+        n, half, two = out.shape
     assert two == 2 and out.dtype == torch.float32 and inv_freq.dtype == torch.float32
     assert inv_freq.numel() == half and positions.dtype == torch.int32 and positions.numel() >= n
     _call("generic", "nncpu_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(out), _i(n), _i(half),
-          _f(position_scale), _stream())
+          _f(position_scale), _i(by_pair), _stream())
 
 
 def qk_norm_rope_append(qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, block_table, k_pages, v_pages,

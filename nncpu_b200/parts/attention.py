@@ -81,17 +81,33 @@ class Attention(Mixer):
     def forward(self, ctx, x, residual, cache):
         s, rt = self.spec, self.rt
         n = x.shape[0]
-        # the projections stay in float32 until the per-head norm and the rotation have been applied
-        qkv = rt.empty(n, self.q_size + 2 * self.kv_size, dtype=torch.float32)
-        rt.linear(x, self.w_qkv, self.b_qkv, qkv)
-        cos_sin = None if self.position is None else self.position.tables(ctx)
+        eps = s.qk_norm.eps if s.qk_norm else 0.0
         q = rt.empty(n, self.q_size)
-        ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, s.qk_norm.eps if s.qk_norm else 0.0, cos_sin,
-                                ctx.tok_seq, ctx.tok_pos, cache.block_table, cache.k_pages, cache.v_pages, q,
-                                s.n_heads, 0 if self.shared_kv else s.n_kv_heads, s.head_dim)
+        if self._fused_qkv(x, cache):
+            # a prompt: norm, rotation and the cache append happen in the projection's epilogue, on its
+            # float32 accumulators; its threads are tokens, so the rotation table is laid out by pair
+            cos_sin = None if self.position is None else self.position.tables(ctx, by_pair=True)
+            ops.linear_tc_qkv(x, self.w_qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
+                              cache.block_table, cache.k_pages, cache.v_pages, q, rt.workspace, s.n_heads,
+                              s.n_kv_heads, s.head_dim)
+        else:
+            # the projections stay in float32 until the per-head norm and the rotation have been applied
+            qkv = rt.empty(n, self.q_size + 2 * self.kv_size, dtype=torch.float32)
+            rt.linear(x, self.w_qkv, self.b_qkv, qkv)
+            cos_sin = None if self.position is None else self.position.tables(ctx)
+            ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
+                                    cache.block_table, cache.k_pages, cache.v_pages, q, s.n_heads,
+                                    0 if self.shared_kv else s.n_kv_heads, s.head_dim)
         attn = rt.empty(n, self.q_size)
         self._attend(ctx, q, cache, attn)
         rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True)
+
+    def _fused_qkv(self, x, cache) -> bool:
+        s = self.spec
+        return (not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
+                and self.w_qkv.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
+                and (self.position is None or self.position.half * 2 == s.head_dim)
+                and ops.linear_tc_qkv_supported(x, s.n_heads, s.n_kv_heads, s.head_dim))
 
     def _attend(self, ctx, q, cache, attn):
         """bfloat16 with a head size the tensor-core kernels take: split-key

@@ -30,12 +30,14 @@ class RopeNeox(PositionEncoding):
         inv = torch.pow(torch.tensor(float(self.spec.theta), dtype=torch.float64), -2.0 * i / self.spec.rotary_dim)
         self.inv_freq = inv.to(torch.float32).to(rt.device)
 
-    def tables(self, ctx):
-        """float32 [n_tokens, half, 2] of (cos, sin), memoised in the step."""
-        key = ("rope_neox", self.spec)
+    def tables(self, ctx, by_pair: bool = False):
+        """float32 [n_tokens, half, 2] of (cos, sin), or with ``by_pair`` the same
+        values as [half, n_tokens, 2]; memoised in the step."""
+        key = ("rope_neox", self.spec, by_pair)
         t = ctx.memo.get(key)
         if t is None:
-            t = self.rt.empty(ctx.n_tokens, self.half, 2, dtype=torch.float32)
-            ops.rope_table(ctx.tok_pos, self.inv_freq, t, self.spec.position_scale)
+            shape = (self.half, ctx.n_tokens, 2) if by_pair else (ctx.n_tokens, self.half, 2)
+            t = self.rt.empty(*shape, dtype=torch.float32)
+            ops.rope_table(ctx.tok_pos, self.inv_freq, t, self.spec.position_scale, by_pair)
             ctx.memo[key] = t
         return t

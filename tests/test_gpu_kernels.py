@@ -281,6 +281,73 @@ def test_qk_norm_rope_append_float32_in_bfloat16_out(ops, nh, nkv, hd):
     assert bool((kp.float().cpu()[untouched] == 7.0).all()) and bool((vp.float().cpu()[untouched] == 7.0).all())
 
 
+@pytest.mark.parametrize("nh,nkv,k,with_norm,with_rope", [(4, 2, 256, True, True), (2, 2, 136, False, True),
+                                                          (6, 4, 64, True, False)])
+def test_linear_qkv_fused_epilogue(ops, nh, nkv, k, with_norm, with_rope):
+    """The q/k/v projection of prompts with norm, rotation and cache append in its epilogue: three sequences
+    (one continuing at position 130, one with a padded row in the middle), a token count that does not fill
+    the last 256-row tile."""
+    hd = 128
+    g = torch.Generator().manual_seed(nh + k)
+    new, starts = [300, 257, 43], [130, 0, 64]
+    n = sum(new)
+    x = (torch.randn(n, k, generator=g) * 0.5).bfloat16()
+    w = (torch.randn((nh + 2 * nkv) * hd, k, generator=g) / math.sqrt(k)).bfloat16()
+    qg, kg = ((1 + 0.1 * torch.randn(hd, generator=g)).bfloat16() for _ in range(2))
+    tok_seq = torch.tensor([b for b, c in enumerate(new) for _ in range(c)], dtype=torch.int32)
+    tok_pos = torch.tensor([s0 + i for s0, c in zip(starts, new) for i in range(c)], dtype=torch.int32)
+    pad = 310
+    tok_seq[pad] = -1                                                     # a padded row: q is written, the cache is not
+    n_pages = 16
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((3, 8), -1, dtype=torch.int32)
+    it = iter(perm)
+    for b, (s0, c) in enumerate(zip(starts, new)):
+        for pg in range((s0 + c + PAGE - 1) // PAGE):
+            table[b, pg] = next(it)
+    theta = 1e6
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    cs = None
+    if with_rope:
+        cs = torch.empty(hd // 2, n, 2, device=DEV)
+        ops.rope_table(tok_pos.to(DEV), inv.float().to(DEV), cs, by_pair=True)
+        by_token = torch.empty(n, hd // 2, 2, device=DEV)
+        ops.rope_table(tok_pos.to(DEV), inv.float().to(DEV), by_token)
+        assert torch.equal(cs.transpose(0, 1), by_token)
+    kp = torch.full((n_pages, nkv, PAGE, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    vp = torch.full((n_pages, nkv, PAGE, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+    xd = x.to(DEV)
+    assert ops.linear_tc_qkv_supported(xd, nh, nkv, hd) and not ops.linear_tc_qkv_supported(xd[:100], nh, nkv, hd)
+    assert not ops.linear_tc_qkv_supported(xd, nh, nkv, 64) and not ops.linear_tc_qkv_supported(xd, 3, nkv, hd)
+    ws = ops.GemmWorkspace(DEV)
+    ops.linear_tc_qkv(xd, w.to(DEV), qg.to(DEV) if with_norm else None, kg.to(DEV) if with_norm else None, 1e-6, cs,
+                      tok_seq.to(DEV), tok_pos.to(DEV), table.to(DEV), kp, vp, q_out, ws, nh, nkv, hd)
+    assert int(ws.status.item()) == 0
+    y = P.linear(x.float().numpy(), w.float().numpy())
+    q = y[:, :nh * hd].reshape(n, nh, hd)
+    kk = y[:, nh * hd:(nh + nkv) * hd].reshape(n, nkv, hd)
+    v = y[:, (nh + nkv) * hd:].reshape(n, nkv, hd)
+    if with_norm:
+        q, kk = P.rmsnorm(q, qg.float().numpy(), 1e-6), P.rmsnorm(kk, kg.float().numpy(), 1e-6)
+    if with_rope:
+        q, kk = P.rope_neox(q, tok_pos.numpy(), theta, hd), P.rope_neox(kk, tok_pos.numpy(), theta, hd)
+    check(q_out.view(n, nh, hd), q, 8e-3, "q")
+    written = torch.zeros(n_pages, PAGE, dtype=torch.bool)
+    for t in list(range(0, n, 7)) + [299, 300, 556, 557, n - 1]:
+        if t == pad:
+            continue
+        page = int(table[tok_seq[t], tok_pos[t] // PAGE])
+        check(kp[page, :, tok_pos[t] % PAGE], kk[t], 8e-3, f"k of token {t}")
+        check(vp[page, :, tok_pos[t] % PAGE], v[t], 8e-3, f"v of token {t}")
+    for t in range(n):
+        if t != pad:
+            written[int(table[tok_seq[t], tok_pos[t] // PAGE]), tok_pos[t] % PAGE] = True
+    untouched = ~written[:, None, :, None].expand(n_pages, nkv, PAGE, hd)
+    assert bool((kp.float().cpu()[untouched] == 7.0).all()) and bool((vp.float().cpu()[untouched] == 7.0).all())
+    assert bool((kp.float().cpu()[~untouched] != 7.0).any())
+
+
 def test_qk_norm_rope_append_padding_and_no_norm(ops):
     n, nh, nkv, hd = 3, 2, 1, 16
     qkv = torch.randn(n, (nh + 2 * nkv) * hd, device=DEV)
