@@ -25,7 +25,7 @@ STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
-    for name in "ABCDEF":
+    for name in "ABCDEFG":
         for dtype in DTYPES:
             out[name, dtype] = make_folder(root / f"{name}_{dtype}", name, seed=ord(name), store_dtype=STORE[dtype])
     return out
@@ -41,7 +41,7 @@ def tokens_for(plain, n, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "ABCDEF")
+@pytest.mark.parametrize("name", "ABCDEFG")
 def test_whole_then_last_32_one_by_one(folders, plains, name, dtype):
     plain = plains[name, dtype]
     model = Model.load(folders[name, dtype], dtype=dtype)
@@ -62,7 +62,7 @@ def test_whole_then_last_32_one_by_one(folders, plains, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "ABCDEF")
+@pytest.mark.parametrize("name", "ABCDEFG")
 def test_unequal_batches_one_after_another(folders, plains, name, dtype):
     plain = plains[name, dtype]
     model = Model.load(folders[name, dtype], dtype=dtype)
@@ -96,6 +96,38 @@ def test_unequal_batches_one_after_another(folders, plains, name, dtype):
             check(torch.cat(got[i]), want[i], TOL[dtype], f"batch {round_}, request {i} of lengths {lens}")
         engine.cache.check()
         assert engine.cache.slots.n_held == 0 and all(g.pool.n_held == 0 for g in engine.cache.groups)
+    model.rt.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_whole_cut_and_batched(folders, plains, dtype):
+    """Prompts of more than 512 tokens: in bfloat16 the q/k/v projection runs with its fused epilogue and
+    attention on 128-row tiles.  A request whole, the same request cut into a long and a short step and
+    then decoded, and two long requests of unequal lengths in one batch all agree with the plain model."""
+    plain = plains["G", dtype]
+    model = Model.load(folders["G", dtype], dtype=dtype)
+    engine = Engine(model, max_tokens=64 * 40)
+    a, b = tokens_for(plain, 700, 11), tokens_for(plain, 530, 12)
+    want_a, want_b = plain.logits(a), plain.logits(b)
+    places = sorted(set(range(0, 700, 37)) | {127, 128, 255, 256, 511, 512, 639, 640, 699})
+    s = engine.alloc_slot()
+    whole = engine.step([s], [a], [places])
+    check(whole, want_a[places], TOL[dtype], "whole request")
+    engine.free_slot(s)
+    s = engine.alloc_slot()
+    head = engine.step([s], [a[:560]], [[p for p in places if p < 560]]).clone()
+    mid = engine.step([s], [a[560:690]], [[p - 560 for p in places if 560 <= p < 690]]).clone()
+    tail = torch.cat([engine.step([s], [[t]]).clone() for t in a[690:]])
+    cut = torch.cat([head, mid])
+    n_cut = cut.shape[0]
+    check(cut, want_a[[p for p in places if p < 690]], TOL[dtype], "cut into 560 + 130")
+    check(tail, want_a[690:], TOL[dtype], "then one by one")
+    check(cut, whole[:n_cut], 1e-5 if dtype == "float32" else TOL[dtype], "cut against whole")
+    engine.free_slot(s)
+    s1, s2 = engine.alloc_slot(), engine.alloc_slot()
+    both = engine.step([s1, s2], [a, b], [[0, 300, 699], [0, 529]])
+    check(both[:3], want_a[[0, 300, 699]], TOL[dtype], "batched, first request")
+    check(both[3:], want_b[[0, 529]], TOL[dtype], "batched, second request")
     model.rt.check_status()
 
 

@@ -38,6 +38,12 @@ TINY = {
               num_key_value_heads=1, head_dim=128, intermediate_size=256, vocab_size=333, rope_theta=1000000.0,
               rms_norm_eps=1e-5, tie_word_embeddings=False, attention_bias=True, max_position_embeddings=2048,
               use_sliding_window=True, sliding_window=100, layer_types=["sliding_attention", "full_attention"]),
+    # what the prompt kernels want: head size 128, even head counts (two heads of a block share a key/value
+    # head; the q/k/v epilogue takes two heads a tile), a window longer than a 128-row tile on one layer
+    "G": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=128, intermediate_size=384, vocab_size=410, rope_theta=1000000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=False, attention_bias=False, max_position_embeddings=4096,
+              use_sliding_window=True, sliding_window=200, layer_types=["full_attention", "sliding_attention"]),
     # sizes that keep every fast path out: a width that is no multiple of 8, as many key/value heads as heads
     "F": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=1, hidden_size=100, num_attention_heads=5,
               num_key_value_heads=5, head_dim=16, intermediate_size=90, vocab_size=257, rope_theta=20000.0,
