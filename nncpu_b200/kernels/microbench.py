@@ -4,6 +4,7 @@ counterpart of the reference's ignored micro-benchmarks
 GFLOP/s for its row kernels and one attention block.
 
     python -m nncpu_b200.kernels.microbench linear M N K [--epilogue swiglu] [--accumulate]
+    python -m nncpu_b200.kernels.microbench linear-qkv TOKENS [--hidden K]
     python -m nncpu_b200.kernels.microbench attention-decode BATCH CONTEXT [--splits S]
     python -m nncpu_b200.kernels.microbench attention-prefill BATCH TOKENS
     python -m nncpu_b200.kernels.microbench rmsnorm ROWS DIM
@@ -72,6 +73,32 @@ def linear(args) -> None:
     ms = _time([lambda w=w: call(w) for w in ws], args.once)
     print(f"linear M={m} N={n} K={k} epilogue={args.epilogue}: {ms * 1e3:.1f} us, "
           f"{n * k * 2 / ms / 1e6:.0f} GB/s of weights, {2 * m * n * k / ms / 1e9:.1f} TFLOP/s")
+
+
+def linear_qkv(args) -> None:
+    """The q/k/v projection of one prompt with norm, rotation and cache append in its epilogue."""
+    m, k, nh, nkv, hd = args.tokens, args.hidden, args.heads, args.kv_heads, args.head_dim
+    n = (nh + 2 * nkv) * hd
+    copies = max(2, 4 * L2_BYTES // (n * k * 2) + 1)
+    ws = [(torch.randn(n, k, device=DEV) / math.sqrt(k)).bfloat16() for _ in range(copies)]
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    gamma = torch.ones(hd, device=DEV).bfloat16()
+    seq = torch.zeros(m, dtype=torch.int32, device=DEV)
+    pos = torch.arange(m, dtype=torch.int32, device=DEV)
+    pages = (m + 63) // 64
+    table = torch.randperm(pages, device=DEV).to(torch.int32).view(1, -1)
+    kp = torch.zeros(pages, nkv, 64, hd, device=DEV).bfloat16()
+    vp = torch.zeros_like(kp)
+    inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    cs = torch.empty(hd // 2, m, 2, device=DEV)
+    ops.rope_table(pos, inv.float().to(DEV), cs, by_pair=True)
+    q = torch.empty(m, nh * hd, device=DEV).bfloat16()
+    work = ops.GemmWorkspace(DEV)
+    ms = _time([lambda w=w: ops.linear_tc_qkv(x, w, gamma, gamma, 1e-6, cs, seq, pos, table, kp, vp, q, work, nh, nkv, hd)
+                for w in ws], args.once)
+    if int(work.status.item()):
+        raise SystemExit(f"the kernel gave up waiting (status {int(work.status.item())})")
+    print(f"linear-qkv M={m} N={n} K={k}: {ms * 1e3:.1f} us, {2 * m * n * k / ms / 1e9:.1f} TFLOP/s")
 
 
 def _cache(batch, ctx, nkv, hd, copies):
@@ -147,6 +174,11 @@ def main(argv=None) -> int:
         p.add_argument("--cluster", action="store_true", help="merge the splits inside a cluster (at most 8)")
         p.add_argument("--legacy", action="store_true", help="prefill: the mma.sync kernel instead of tcgen05")
         p.set_defaults(fn=fn)
+    p = sub.add_parser("linear-qkv")
+    p.add_argument("tokens", type=int); p.add_argument("--hidden", type=int, default=4096)
+    p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.set_defaults(fn=linear_qkv)
     p = sub.add_parser("rmsnorm")
     p.add_argument("rows", type=int); p.add_argument("dim", type=int)
     p.set_defaults(fn=rmsnorm)
