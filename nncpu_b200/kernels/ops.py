@@ -119,6 +119,12 @@ class GemmWorkspace:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
 
+def set_streamk_mode(mode: int) -> None:
+    """How products of 17 to 256 tokens are cut: 1 (default) evenly over the SMs from 65 tokens on and a
+    cluster per output tile below, 2 evenly from 17 tokens on, 0 never evenly.  For measurements and tests."""
+    library.load("gemm_sm100").nncpu_linear_tc_set_streamk_mode(int(mode))
+
+
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 

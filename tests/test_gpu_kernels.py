@@ -120,6 +120,39 @@ def test_linear_tensor_core_with_gated_epilogue(ops, m, inter, k):
     assert int(ws.status.item()) == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(20, 1000, 1096), (40, 25600, 512), (70, 640, 4096), (100, 25000, 264),
+                                   (130, 4096, 1024), (256, 19000, 520), (200, 128, 8192)])
+def test_linear_tensor_core_with_work_cut_evenly(ops, m, n, k):
+    """17 to 256 tokens with the k-blocks of all tiles dealt out evenly to the blocks: fewer tiles than SMs
+    (every tile in parts), more tiles than SMs (whole tiles and parts), one tile, every epilogue; twice, and
+    the runs agree bit for bit."""
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.1).bfloat16().to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    ws = ops.GemmWorkspace(DEV)
+    want = (x.double() @ w.double().T).float()
+    ops.set_streamk_mode(2)
+    try:
+        out = torch.full((m, n), 9.0, device=DEV)
+        ops.linear_tc(x, w, b, out, ws)
+        check(out, want + b, 1e-5, "float32 out with bias")
+        again = torch.full((m, n), 9.0, device=DEV)
+        ops.linear_tc(x, w, b, again, ws)
+        assert torch.equal(out, again)
+        acc = torch.full((m, n), 0.5, dtype=torch.bfloat16, device=DEV)
+        ops.linear_tc(x, w, None, acc, ws, accumulate=True)
+        check(acc, want + 0.5, 8e-3, "accumulate in bfloat16")
+        if n % 16 == 0:
+            gated = torch.full((m, n // 2), 9.0, device=DEV)
+            ops.linear_tc(x, w, None, gated, ws, epilogue="swiglu")
+            y = want.cpu().numpy().reshape(m, -1, 2, 8)
+            check(gated, P.swiglu(y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)), 1e-5, "gated epilogue")
+    finally:
+        ops.set_streamk_mode(1)
+    assert int(ws.status.item()) == 0
+
+
 def test_linear_tensor_core_is_repeatable_and_row_independent(ops):
     # K is cut into slices for few tokens: the slices are added in slice order, so runs agree bit for bit
     x = torch.randn(8, 4096).bfloat16().to(DEV)
