@@ -130,15 +130,18 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
             }
             if (p.out_dt == DT_F32) {
                 float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+                if (p.accumulate) {
+                    // all four loads before the first store: one round trip instead of four
+                    float4 y[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    if (p.accumulate) {
-                        const float4 y = dst[j];
-                        x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+                    for (int j = 0; j < 4; ++j) y[j] = dst[j];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        v[4 * j] += y[j].x; v[4 * j + 1] += y[j].y; v[4 * j + 2] += y[j].z; v[4 * j + 3] += y[j].w;
                     }
-                    dst[j] = x;
                 }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             } else {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
 #pragma unroll
