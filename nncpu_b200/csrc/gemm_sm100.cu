@@ -1437,7 +1437,10 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
     p.splits = splits;
     // 65 to 256 tokens: the work is cut evenly over the SMs; fewer tokens: a cluster per output tile (measured:
     // at 96 tokens 139 us against 220 us for the four products of a Qwen3-8B layer, at 64 tokens 123 against 117)
-    if (p.swap && bn >= (streamk_mode == 2 ? 32 : 128) && streamk_mode && scratch != nullptr &&
+    // The same for 257 and more tokens that do not fill the SMs with 128 x 256 tiles at least twice.
+    const bool even_swap = p.swap && bn >= (streamk_mode == 2 ? 32 : 128);
+    const bool even_plain = !p.swap && n_tiles < 2 * sm_count();
+    if ((even_swap || even_plain) && streamk_mode && scratch != nullptr &&
         2l * sm_count() * bn * kBlockM <= nncpu_linear_tc_scratch_floats()) {
         p.splits = 1;
         return epilogue == kSwiglu ? dispatch_streamk<kSwiglu>(bn, ma, mb, p, stream)
