@@ -28,6 +28,8 @@ constexpr int kWarps = 8;
 constexpr int kRows = 16;     // weight rows per block
 constexpr int kUnroll = 8;    // 32-wide k groups in flight per warp
 
+static_assert(kRows * 16 <= kWarps * 32, "one output element per thread with 16 tokens");
+
 enum Epilogue : int { kPlain = 0, kSwiglu = 1 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -63,6 +65,14 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+
+    // What the product is added to is fetched now, under the weight stream, not after it: thread i of the
+    // epilogue owns output (token i / 16, row i % 16); with at most 16 tokens that is one element per thread.
+    float before = 0.0f;
+    if (kEpi == kPlain && accumulate) {
+        const int tok = threadIdx.x / kRows, row = row0 + threadIdx.x % kRows;
+        if (tok < M && row < N) before = ld_f(out, (size_t)tok * ldc + row, out_dt);
+    }
 
     // this warp's share of K, in groups of 32
     const int n_groups = (K + 31) / 32;
@@ -140,7 +150,7 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
             for (int w = 0; w < kWarps; ++w) v += part[w][j][tok];
             if (bias) v += ld_f(bias, row, bias_dt);
             const size_t o = (size_t)tok * ldc + row;
-            if (accumulate) v += ld_f(out, o, out_dt);
+            if (accumulate) v += before;   // i == threadIdx.x: kRows * M is at most the block's 256 threads
             st_f(out, o, out_dt, v);
         }
     }
