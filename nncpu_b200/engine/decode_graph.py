@@ -116,6 +116,17 @@ class DecodeGraph:
         ev.record()
         self.events[i] = ev
 
+    def fetch_ids(self, n: int):
+        """Copies the greedy choices of the step just launched to pinned memory, in stream order (so before a
+        later step overwrites them).  Returns (event, int32 host tensor)."""
+        i = self.fetch_turn = (getattr(self, "fetch_turn", -1) + 1) % _RING
+        if not hasattr(self, "ids_host"):
+            self.ids_host = [torch.empty(self.size, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+            self.ids_events = [torch.cuda.Event() for _ in range(_RING)]
+        self.ids_host[i][:n].copy_(self.next_ids[:n], non_blocking=True)
+        self.ids_events[i].record()
+        return self.ids_events[i], self.ids_host[i]
+
     def _forward(self) -> None:
         self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
         ops.argmax(self.logits, self.next_ids)

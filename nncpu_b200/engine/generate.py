@@ -17,6 +17,15 @@ take on new members.
 The loop talks to an engine through ``alloc_slot``, ``free_slot``, ``step``
 and ``max_seq_len`` only, and to a chooser through ``choose(logits, indices)``,
 so its decisions can be tested with scripted stand-ins for both.
+
+Greedy decoding does not wait for the host: when the chooser says its choice
+is the engine's own device-side greedy choice (``greedy_on_device``) and the
+engine offers ``greedy_fetch`` and ``step_again``, the next step is launched
+with the tokens still on the device while the host reads the previous step's
+tokens and takes its decisions one step behind.  A sequence that the host
+then stops has run one step too many, which nobody sees: its slot is freed.
+Steps in which a count limit (context, ``max_tokens``) can end a sequence are
+not run ahead.
 """
 from __future__ import annotations
 
@@ -77,6 +86,32 @@ def generate(engine, chooser, prompts: Sequence[Sequence[int]], params: Generate
 
 def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_ctx, results) -> None:
     live = []  # [index, slot, tokens so far (prompt + generated), result]
+    device_greedy = (getattr(chooser, "greedy_on_device", False) and hasattr(engine, "greedy_fetch")
+                     and hasattr(engine, "step_again"))
+
+    def settle(rows, chosen):
+        """Takes one chosen token per sequence of ``rows``; returns the sequences that go on."""
+        still = []
+        for (idx, slot, toks, r), tok in zip(rows, chosen):
+            tok = int(tok)
+            toks.append(tok)
+            if tok in stops:
+                r.stop = StopReason.END_OF_TURN
+            else:
+                r.n_generated += 1
+                r.tokens.append(tok)
+                if on_token is not None and on_token(idx, tok) is False:
+                    r.stop = StopReason.CALLBACK
+                elif len(toks) >= n_ctx:
+                    r.stop = StopReason.CONTEXT_FULL
+                elif params.max_tokens > 0 and r.n_generated >= params.max_tokens:
+                    r.stop = StopReason.MAX_TOKENS
+                else:
+                    still.append([idx, slot, toks, r])
+                    continue
+            engine.free_slot(slot)
+        return still
+
     try:
         for idx, prompt in members:
             live.append([idx, engine.alloc_slot(), prompt, GenerateResult(n_prompt=len(prompt))])
@@ -90,29 +125,35 @@ def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_c
                 for _, _, _, r in live:
                     r.stop = StopReason.CANCELLED
                 break
-            chosen = chooser.choose(logits, [idx for idx, _, _, _ in live])
+            ahead = None
+            fetch = engine.greedy_fetch(len(live)) if device_greedy and prefill is not None else None
+            if fetch is not None:
+                # The step in flight chose its tokens on the device: start their copy to the host and, unless a
+                # count limit may end a sequence with this very token, launch the next step on top of them.
+                event, ids = fetch
+                if all(len(toks) + 2 <= n_ctx and (params.max_tokens <= 0 or r.n_generated + 2 <= params.max_tokens)
+                       for _, _, toks, r in live):
+                    ahead = engine.step_again([s for _, s, _, _ in live])
+                event.synchronize()
+                chosen = ids[:len(live)].tolist()
+            else:
+                chosen = chooser.choose(logits, [idx for idx, _, _, _ in live])
             if prefill is None:  # the first choice waits for the prompt step to finish
                 t1 = time.perf_counter()
                 prefill = t1 - t0
-            still = []
-            for (idx, slot, toks, r), tok in zip(live, chosen):
-                tok = int(tok)
-                toks.append(tok)
-                if tok in stops:
-                    r.stop = StopReason.END_OF_TURN
-                else:
-                    r.n_generated += 1
-                    r.tokens.append(tok)
-                    if on_token is not None and on_token(idx, tok) is False:
-                        r.stop = StopReason.CALLBACK
-                    elif len(toks) >= n_ctx:
-                        r.stop = StopReason.CONTEXT_FULL
-                    elif params.max_tokens > 0 and r.n_generated >= params.max_tokens:
-                        r.stop = StopReason.MAX_TOKENS
-                    else:
-                        still.append([idx, slot, toks, r])
-                        continue
-                engine.free_slot(slot)
+            still = settle(live, chosen)
+            if ahead is not None and len(still) == len(live):
+                live, logits = still, ahead     # nobody stopped: the step run ahead is the step in flight
+                continue
+            if ahead is not None and still:
+                # Somebody stopped, so the step run ahead carried sequences that are gone; for the others it is
+                # their next step all the same.  Its choices are read by row and settled like any others; the
+                # next round starts with a plain step.
+                going_on = {m[0] for m in still}
+                rows = [k for k, m in enumerate(live) if m[0] in going_on]
+                event, ids = engine.greedy_fetch(len(live))
+                event.synchronize()
+                still = settle(still, [int(ids[k]) for k in rows])
             live = still
             if live:
                 logits = engine.step([s for _, s, _, _ in live], [[t[-1]] for _, _, t, _ in live])

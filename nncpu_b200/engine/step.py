@@ -93,6 +93,7 @@ class Engine:
         from .decode_graph import DecodeGraphs
         self.model = model
         self.graphs = DecodeGraphs(self) if use_graphs else None
+        self._last_graph = None   # the graph of the last step, if that step ran through one
         self.h2d_bytes_last_step = 0
         requests, cache_of = model.cache_requests()
         rt = model.rt
@@ -157,10 +158,39 @@ class Engine:
             logits = g.run(slots, [t[0] for t in tokens])
             self.h2d_bytes_last_step = g.h2d_bytes
             self.cache.commit(slots, [1] * len(slots))
+            self._last_graph = g
             return logits
+        self._last_graph = None
         ctx = self.build_context(slots, tokens, want)
         logits = self.model.forward(ctx, self.cache)
         self.cache.commit(slots, ctx.q_lens)
+        return logits
+
+    # -- greedy decoding without a host round trip per step ----------------------
+
+    def greedy_fetch(self, n: int):
+        """Starts the copy of the last graph step's greedy choices (one per
+        sequence, made by the graph itself) to pinned host memory.  Returns
+        ``(event, ids)``: after ``event.synchronize()`` ``ids[:n]`` holds them.
+        None if the last step did not run through a graph."""
+        g = self._last_graph
+        if g is None:
+            return None
+        return g.fetch_ids(n)
+
+    def step_again(self, slots: Sequence[int]) -> torch.Tensor:
+        """One more decode step for exactly the sequences of the last graph
+        step, each fed its own greedy choice of that step, which never leaves
+        the device."""
+        slots = [int(s) for s in slots]
+        g = self._last_graph
+        if g is None or g.slots != tuple(slots):
+            raise InvalidArgument("step_again needs the sequences of the last decode step, in its order")
+        n = len(slots)
+        self.cache.prepare(slots, [1] * n)
+        logits = g.run(slots, None)
+        self.h2d_bytes_last_step = g.h2d_bytes
+        self.cache.commit(slots, [1] * n)
         return logits
 
     def decode_run(self, slots: Sequence[int], first_tokens, n_steps: int) -> torch.Tensor:

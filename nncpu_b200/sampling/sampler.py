@@ -41,6 +41,11 @@ class Sampler:
         self.vocab_size = vocab_size
         self._rngs: Dict[int, Mt19937_64] = {}
 
+    @property
+    def greedy_on_device(self) -> bool:
+        """Greedy choices are the first largest logit, which the engine's decode graph computes itself."""
+        return self.params.is_greedy
+
     def rng(self, index: int) -> Mt19937_64:
         r = self._rngs.get(index)
         if r is None:

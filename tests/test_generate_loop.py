@@ -139,3 +139,112 @@ def test_engine_failure_gives_every_slot_back():
     with pytest.raises(RuntimeError):
         generate(eng, Script(), [[1], [2]], GenerateParams(8, GREEDY))
     assert not eng.held
+
+
+# -- greedy choices that stay on the device: the loop runs one step ahead ---------------------------------------
+
+class AheadEngine(FakeEngine):
+    """A FakeEngine whose decode steps choose their tokens themselves, by the Script's rule, and can be run
+    again on top of those choices (``step_again``) before the host has read them (``greedy_fetch``)."""
+
+    class _Event:
+        def synchronize(self):
+            pass
+
+    class _Ids(list):
+        def tolist(self):
+            return list(self)
+
+        def __getitem__(self, k):
+            got = list.__getitem__(self, k)
+            return AheadEngine._Ids(got) if isinstance(k, slice) else got
+
+    def __init__(self, special=None, **kw):
+        super().__init__(**kw)
+        self.special, self.owner, self.n_alloc, self.last, self.again = special or {}, {}, 0, None, 0
+
+    def alloc_slot(self):
+        s = super().alloc_slot()
+        self.owner[s] = self.n_alloc           # requests take their slots in request order
+        self.n_alloc += 1
+        return s
+
+    def step(self, slots, tokens):
+        out = super().step(slots, tokens)
+        decode = all(len(t) == 1 for t in tokens)
+        self.last = (list(slots), [self.special.get((self.owner[s], n), 100 + n) for s, n in out]) if decode else None
+        return out
+
+    def greedy_fetch(self, n):
+        if self.last is None:
+            return None
+        assert n == len(self.last[0])
+        return self._Event(), self._Ids(self.last[1])
+
+    def step_again(self, slots):
+        assert self.last is not None and list(slots) == self.last[0], "only the sequences of the last decode step"
+        self.again += 1
+        return self.step(slots, [[t] for t in self.last[1]])
+
+
+def run_ahead(prompts, max_tokens=0, stops=(), special=None, engine=None, **kw):
+    engine = engine or AheadEngine(special)
+    chooser = Script(special)
+    chooser.greedy_on_device = True
+    res = generate(engine, chooser, prompts, GenerateParams(max_tokens, GREEDY), stops, **kw)
+    assert not engine.held, "every slot goes back"
+    return res, engine, chooser
+
+
+def same(a, b):
+    return [(r.stop, r.tokens, r.n_generated, r.n_prompt) for r in a] == [(r.stop, r.tokens, r.n_generated, r.n_prompt) for r in b]
+
+
+def test_running_ahead_changes_no_result():
+    cases = [
+        dict(prompts=[[1, 2, 3]], max_tokens=4),
+        dict(prompts=[[1, 2]], max_tokens=10, stops=[7], special={(0, 4): 7}),
+        dict(prompts=[[1, 2]], stops=[102]),
+        dict(prompts=[[1] * 5, [1] * 9, [1] * 13], stops=[107, 112], max_tokens=6),
+        dict(prompts=[[1] * 5, [1] * 9, [1] * 13], stops=[107, 112, 114]),
+        dict(prompts=[[1] * (i + 1) for i in range(7)], max_tokens=3, max_batch=3),
+        dict(prompts=[[1] * 3, [2] * 4], max_tokens=1),
+        dict(prompts=[[1] * 3, [2] * 4], max_tokens=2),
+    ]
+    for case in cases:
+        plain, _ = run(**case)
+        ahead, eng, chooser = run_ahead(**case)
+        assert same(plain, ahead), case
+        # the chooser is asked for the first token of a batch only: every later token came from the device
+        assert all(len(eng.steps[0]) >= len(c) for c in chooser.calls)
+    # a context that fills up
+    plain, _ = run([[1] * 60], engine=FakeEngine(max_seq_len=64))
+    ahead, eng, _ = run_ahead([[1] * 60], engine=AheadEngine(max_seq_len=64))
+    assert same(plain, ahead) and ahead[0].stop == StopReason.CONTEXT_FULL
+
+
+def test_running_ahead_launches_before_it_reads_and_never_past_a_count_limit():
+    # 8 tokens: the first from the prompt step, decode steps for tokens 2..8 = 7 steps as without running ahead
+    res, eng, chooser = run_ahead([[1, 2, 3]], max_tokens=8)
+    assert res[0].n_generated == 8 and eng.steps == [[3]] + [[1]] * 7
+    assert len(chooser.calls) == 1                  # the first token only
+    assert eng.again == 6                           # decode steps 2..7 were launched on device tokens; step 1 needs the
+    #                                                 host's first token, and nothing runs on top of the last counted token
+    # a stop token: the step run ahead has already happened, and nobody sees it
+    res, eng, _ = run_ahead([[1, 2]], stops=[7], special={(0, 5): 7}, max_tokens=20)
+    assert res[0].stop == StopReason.END_OF_TURN and res[0].tokens == [102, 103, 104]
+    assert eng.steps == [[2], [1], [1], [1], [1]]   # one step more than the three tokens needed
+    # a callback stop is seen one step late as well
+    res, eng, _ = run_ahead([[1]], on_token=lambda i, t: t != 103, max_tokens=20)
+    assert res[0].stop == StopReason.CALLBACK and res[0].tokens == [101, 102, 103]
+
+
+def test_running_ahead_when_one_sequence_stops_the_others_keep_their_step():
+    # sequence 0 stops on its third token; the step that ran ahead is sequence 1's next step all the same
+    special = {(0, 7): 9}
+    plain, _ = run([[1] * 5, [1] * 9], stops=[9], special=special, max_tokens=7)
+    ahead, eng, _ = run_ahead([[1] * 5, [1] * 9], stops=[9], special=special, max_tokens=7)
+    assert same(plain, ahead)
+    assert ahead[0].stop == StopReason.END_OF_TURN and ahead[1].stop == StopReason.MAX_TOKENS
+    # every decode step of sequence 1 ran exactly once: prompt + 6 steps for 7 tokens
+    assert sum(1 for s in eng.steps[1:]) >= 6
