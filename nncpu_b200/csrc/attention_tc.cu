@@ -9,7 +9,7 @@
 //     is free once the scores are computed and V once O has been updated;
 //   * one thread issues tcgen05.mma: S = Q . K^T into the head's columns of
 //     tensor memory, and O += P . V with P read from tensor memory (it lies
-//     over the first half of S) and V read as an MN-major operand straight
+//     over the second half of S) and V read as an MN-major operand straight
 //     from the pages' layout.  The head's next scores follow its O update at
 //     once, so the tensor core works for one head while the other head's
 //     warpgroup computes exponentials;
@@ -41,7 +41,7 @@ namespace {
 constexpr int kQRows = 128;   // query rows per block = tensor-core M
 constexpr int kKeys = 2 * kPage;  // keys per step: two cache pages
 constexpr int kStages = 2;    // steps of K and of V in flight
-constexpr int kStreamCols = 256;  // tensor-memory columns per head: S (P over its first half) | O
+constexpr int kStreamCols = 256;  // tensor-memory columns per head: S (P over its second half) | O
 constexpr int kPOffset = 64;      // P lies over the second half of S
 constexpr float kRescaleStep = 8.0f;  // a row's reference maximum follows its true maximum in steps of 2^8
 
@@ -116,7 +116,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     constexpr int kKvBytes = kSlabs * kKvSlab;      // one stage of K or of V
     constexpr int kTmemCols = kStreams * kStreamCols;
     static_assert(HD == 64 || HD == 128, "head size 64 or 128");
-    static_assert(kKeys + HD <= kStreamCols, "S (with P over its first half) and O fit a head's columns");
+    static_assert(kKeys + HD <= kStreamCols, "S (with P over its second half) and O fit a head's columns");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -157,8 +157,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int page_lo = key_lo / kPage, page_hi = key_hi / kPage;
     const int n_pages = page_hi - page_lo + 1;
     const int n_steps = (n_pages + 1) / 2;           // two pages a step; the last step may hold one
-    const int head0 = blockIdx.x * kStreams;
-    const int kvh = head0 / (p.n_heads / p.n_kv);
+    // the heads of a key/value head are dealt out two to a block; an odd group's last block has one
+    const int group = p.n_heads / p.n_kv;
+    const int per_kv = (group + kStreams - 1) / kStreams;
+    const int kvh = blockIdx.x / per_kv;
+    const int head0 = kvh * group + (blockIdx.x % per_kv) * kStreams;
+    const int n_streams = min(kStreams, group - (blockIdx.x % per_kv) * kStreams);
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -190,8 +194,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             const int* table = p.block_table + (size_t)seq * p.bt_stride;
-            mbar_expect_tx(q_full, kStreams * kQBytes);
-            for (int t = 0; t < kStreams; ++t)
+            mbar_expect_tx(q_full, n_streams * kQBytes);
+            for (int t = 0; t < n_streams; ++t)
                 for (int s = 0; s < kSlabs; ++s)
                     tma_load_2d(smem_q + t * kQBytes + s * kQSlab, &map_q, q_full, (head0 + t) * HD + 64 * s, q0);
             // K tiles are free again once their scores are computed, V tiles once O has been updated, so the two
@@ -265,7 +269,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int t = 0; t < kStreams; ++t) issue_scores(t, 0);
+                for (int t = 0; t < n_streams; ++t) issue_scores(t, 0);
                 umma_commit(&k_empty[0]);
             }
             // Per step and head: O += P . V, then at once the head's next scores (they overwrite P, which the
@@ -275,7 +279,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const int st = i % kStages;
                 const int ksteps = min(2, n_pages - 2 * i) * (kPage / 16);
                 const bool more = i + 1 < n_steps;
-                for (int t = 0; t < kStreams && ok; ++t) {
+                for (int t = 0; t < n_streams && ok; ++t) {
                     if (!mbar_wait(&p_full[t], i & 1)) {
                         atomicExch(p.status, kTimeoutP);
                         ok = false;
@@ -325,8 +329,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int lim_lo = (p.window > 0 && lim_hi + 1 > p.window) ? lim_hi + 1 - p.window : 0;
         const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * kStreamCols);
         float m_ref = -INFINITY, l = 0.0f;
-        bool ok = true;
-        for (int i = 0; i < n_steps; ++i) {
+        bool ok = t < n_streams;   // the second warpgroup of a block with one head has nothing to do
+        for (int i = 0; ok && i < n_steps; ++i) {
             ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], i & 1));
             if (!ok) {
                 if (lane == 0) atomicExch(p.status, kTimeoutS);
@@ -500,7 +504,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         configured = true;
     }
     // tiles: an upper bound, since the sequence boundaries live on the device; spare blocks leave at once
-    const dim3 grid(p.n_heads / kStreams, (n_tok + kQRows - 1) / kQRows + p.n_seqs);
+    const int group = p.n_heads / p.n_kv;
+    const dim3 grid(p.n_kv * ((group + kStreams - 1) / kStreams), (n_tok + kQRows - 1) / kQRows + p.n_seqs);
     prefill_tc_kernel<HD, kStreams><<<grid, 64 + 128 * kStreams, smem, stream>>>(mq, mk, mv, p);
     NN_LAUNCH_OK("attention prefill (tensor cores)");
     return 0;
@@ -545,8 +550,8 @@ extern "C" int nncpu_attention_prefill_tc(const void* q, const void* k_pages, co
     p.window = window;
     p.status = status;
     cudaStream_t stream = (cudaStream_t)stream_;
-    const bool pair = (n_heads / n_kv) % 2 == 0;   // two heads of a block must share their key/value head
-    if (head_dim == 64)
-        return pair ? launch<64, 2>(mq, mk, mv, p, n_tok, stream) : launch<64, 1>(mq, mk, mv, p, n_tok, stream);
-    return pair ? launch<128, 2>(mq, mk, mv, p, n_tok, stream) : launch<128, 1>(mq, mk, mv, p, n_tok, stream);
+    // two heads to a block where a key/value head has two to give; one head per block otherwise
+    if (n_heads == n_kv)
+        return head_dim == 64 ? launch<64, 1>(mq, mk, mv, p, n_tok, stream) : launch<128, 1>(mq, mk, mv, p, n_tok, stream);
+    return head_dim == 64 ? launch<64, 2>(mq, mk, mv, p, n_tok, stream) : launch<128, 2>(mq, mk, mv, p, n_tok, stream);
 }

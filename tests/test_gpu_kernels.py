@@ -502,9 +502,10 @@ def test_attention_tensor_core_prefill(ops, nh, nkv, hd, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 0), (8, 1, 128, 0), (6, 3, 128, 40), (16, 1, 64, 17),
-                                              (3, 3, 128, 0), (5, 5, 64, 200), (8, 2, 128, 130)])
+                                              (3, 3, 128, 0), (5, 5, 64, 200), (8, 2, 128, 130), (10, 2, 128, 0),
+                                              (3, 1, 64, 90)])
 def test_attention_tcgen05_prefill(ops, nh, nkv, hd, window):
-    """One and two heads per block (odd and even group sizes), spans that fill several 128-row tiles, start in
+    """One and two heads per block (groups of 1, 2, 3, 4, 5, 8, 16: an odd group's last block has one head), spans that fill several 128-row tiles, start in
     the middle of a page, end one row into a tile, and windows shorter and longer than a tile."""
     old, new = [130, 0, 0, 64, 5, 0, 37], [70, 1, 100, 1, 16, 385, 129]
     seqs = [o + n for o, n in zip(old, new)]
