@@ -16,9 +16,11 @@
 //   * a warpgroup per head owns one query row per thread: it reads its row of
 //     S from tensor memory, scales and masks it, and stores the weights P
 //     as bfloat16 pairs back into tensor memory, keeping sum and maximum in
-//     32-bit.  Weights are taken against a reference maximum that follows the
-//     true one in steps of 2^8: only when a row outgrows it are the row's O
-//     (between two O updates, never under one) and sum rescaled and the
+//     32-bit.  Weights are taken against a reference maximum that lags behind
+//     the true one: as long as a step's weights of a row add up to at most
+//     2^8 nothing can have overflowed and the reference stays; otherwise the
+//     row's largest score is found, the reference moves up to it, the row's O
+//     (between two O updates, never under one) and sum are rescaled and the
 //     step's weights computed again.
 // The output row is O / sum.  The reference computes the same attention row by
 // row (crates/nncpu/src/model/forward.rs:730-800); softmax runs in 32-bit here
@@ -43,7 +45,7 @@ constexpr int kKeys = 2 * kPage;  // keys per step: two cache pages
 constexpr int kStages = 2;    // steps of K and of V in flight
 constexpr int kStreamCols = 256;  // tensor-memory columns per head: S (P over its second half) | O
 constexpr int kPOffset = 64;      // P lies over the second half of S
-constexpr float kRescaleStep = 8.0f;  // a row's reference maximum follows its true maximum in steps of 2^8
+constexpr float kSumLimit = 256.0f;  // a step's weights of a row may add up to this before the row's reference maximum is moved
 
 enum AttnStatus : int { kTimeoutQ = 201, kTimeoutStage = 202, kTimeoutK = 203, kTimeoutV = 204, kTimeoutS = 205,
                         kTimeoutP = 206, kTimeoutPv = 207 };
@@ -339,50 +341,60 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int halves = min(2, n_pages - 2 * i);
             const int k_base = (page_lo + 2 * i) * kPage;
-            // One pass over the row's scores: weights against the reference maximum as it stands (as bfloat16
-            // pairs), their sum, and the largest score.
-            float tmax, sum;
+            // A step costs one pass over the row's scores: weights against the reference maximum as it stands (as
+            // bfloat16 pairs) and their sum.  The largest score is not looked for: a sum of at most 2^8 proves that
+            // no weight is above 2^8.  Only when a row's sum says otherwise (or the row has seen no key yet) is the
+            // largest score found in a pass of its own; then the reference moves up to it, O and the sum so far
+            // follow, and the weights are computed again.  The O update of the step before is complete (these
+            // scores were issued after it), so O may be touched.
+            float sum = 0.0f;
             uint32_t w[2][32];   // P of the two pages, stored once the reference maximum is settled: P overwrites S
+            auto load_half = [&](int hf, uint32_t (&u)[64]) {
+                tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
+                const int kb = k_base + 64 * hf;
+                if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
+                    // the page crosses this row's limits
+#pragma unroll
+                    for (int c = 0; c < 64; ++c)
+                        if (kb + c < lim_lo || kb + c > lim_hi) u[c] = 0xff800000u;   // -inf
+                }
+            };
             auto weights = [&]() {
                 const float neg_m = m_ref == -INFINITY ? 0.0f : 0.0f - m_ref;
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     if (hf < halves) {
                         uint32_t u[64];
-                        tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
-                        const int kb = k_base + 64 * hf;
-                        if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
-                            // the page crosses this row's limits
-#pragma unroll
-                            for (int c = 0; c < 64; ++c)
-                                if (kb + c < lim_lo || kb + c > lim_hi) u[c] = 0xff800000u;   // -inf
-                        }
+                        load_half(hf, u);
 #pragma unroll
                         for (int c = 0; c < 64; c += 2) {
-                            const float s0 = __uint_as_float(u[c]), s1 = __uint_as_float(u[c + 1]);
-                            mx[c & 3] = fmaxf(mx[c & 3], s0);
-                            mx[(c & 3) + 1] = fmaxf(mx[(c & 3) + 1], s1);
-                            const float e0 = fast_exp2(fmaf(s0, p.scale2, neg_m));
-                            const float e1 = fast_exp2(fmaf(s1, p.scale2, neg_m));
+                            const float e0 = fast_exp2(fmaf(__uint_as_float(u[c]), p.scale2, neg_m));
+                            const float e1 = fast_exp2(fmaf(__uint_as_float(u[c + 1]), p.scale2, neg_m));
                             sm[c & 3] += e0;
                             sm[(c & 3) + 1] += e1;
                             w[hf][c >> 1] = pack_bf16(e0, e1);
                         }
                     }
                 }
-                tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale2;   // the scale is positive
                 sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
             };
-            weights();
-            // A row whose largest score has outgrown its reference by more than the step (or that sees its first
-            // key) moves the reference; then O, the sum so far and this step's weights follow.  The O update of
-            // the step before is complete (these scores were issued after it), so O may be touched.
-            const bool grow = tmax > m_ref + kRescaleStep || (m_ref == -INFINITY && tmax > -INFINITY);
-            if (__any_sync(0xffffffffu, grow)) {
+            const bool unseen = __any_sync(0xffffffffu, m_ref == -INFINITY && lim_hi >= 0);
+            if (!unseen) weights();
+            if (unseen || __any_sync(0xffffffffu, !(sum <= kSumLimit))) {
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (hf < halves) {
+                        uint32_t u[64];
+                        load_half(hf, u);
+#pragma unroll
+                        for (int c = 0; c < 64; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(u[c]));
+                    }
+                }
+                const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale2;   // the scale is positive
                 float alpha = 1.0f;
-                if (grow) {
+                if (tmax > m_ref) {
                     alpha = fast_exp2(m_ref - tmax);    // 0 when nothing was seen yet
                     m_ref = tmax;
                     l *= alpha;
