@@ -11,8 +11,9 @@ for its one-sequence forward pass (crates/nncpu/src/model/forward.rs:851-886).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache import Cache
@@ -48,40 +49,73 @@ class StepContext:
         return EntryCache(k, v, self.block_tables[g], cache.owns_kv(entry), cache.state(entry))
 
 
+class Staging:
+    """A ring of pinned host buffers for the metadata of steps: a buffer is
+    reused only after the copy that read it has finished."""
+
+    def __init__(self, n: int = 4):
+        self.bufs: List[Optional[torch.Tensor]] = [None] * n
+        self.events: List[Optional[torch.cuda.Event]] = [None] * n
+        self.turn = 0
+
+    def take(self, n_ints: int) -> Tuple[torch.Tensor, int]:
+        i = self.turn = (self.turn + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i]
+        if buf is None or buf.numel() < n_ints:
+            buf = self.bufs[i] = torch.empty(max(n_ints, 4096), dtype=torch.int32).pin_memory()
+        return buf[:n_ints], i
+
+    def sent(self, i: int) -> None:
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
 def make_context(cache: Cache, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-                 want: Sequence[Sequence[int]]) -> StepContext:
+                 want: Sequence[Sequence[int]], staging: Optional[Staging] = None) -> StepContext:
     """The step's metadata as one block of int32, copied to the device once.
     Call after ``cache.prepare``: the page tables must already cover the new tokens."""
     starts = [cache.length(s) for s in slots]
     q_lens = [len(t) for t in tokens]
-    n = sum(q_lens)
-    tok_ids, tok_seq, tok_pos, cu, rows = [], [], [], [0], []
-    for b, toks in enumerate(tokens):
-        base = cu[-1]
-        tok_ids += list(toks)
-        tok_seq += [b] * len(toks)
-        tok_pos += list(range(starts[b], starts[b] + len(toks)))
-        rows += [base + i for i in want[b]]
-        cu.append(base + len(toks))
+    n, B = sum(q_lens), len(slots)
+    cu = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(q_lens, out=cu[1:])
+    rows = [int(cu[b]) + i for b in range(B) for i in want[b]]
     tables = [cache.block_table(g, slots) for g in range(len(cache.groups))]
-    flat = tok_ids + tok_seq + tok_pos + list(slots) + cu + rows
-    B = len(slots)
     offsets = [0, n, 2 * n, 3 * n, 3 * n + B, 3 * n + 2 * B + 1]
+    total = offsets[5] + len(rows)
     table_at = []
     for t in tables:
-        table_at.append(len(flat))
-        for row in t:
-            flat += row
-    host = torch.tensor(flat, dtype=torch.int32)
-    if cache.device.type == "cuda":
-        host = host.pin_memory()
+        table_at.append(total)
+        total += B * len(t[0])
+    on_gpu = cache.device.type == "cuda"
+    if staging is not None and on_gpu:
+        host, turn = staging.take(total)
+    else:
+        host = torch.empty(total, dtype=torch.int32)
+        if on_gpu:
+            host = host.pin_memory()
+    a = host.numpy()
+    if n:
+        a[0:n] = np.concatenate([np.asarray(t, dtype=np.int64) for t in tokens if len(t)])
+        a[n:2 * n] = np.repeat(np.arange(B), q_lens)
+        a[2 * n:3 * n] = np.arange(n) - np.repeat(cu[:-1] - np.asarray(starts, dtype=np.int64), q_lens)
+    a[offsets[3]:offsets[4]] = slots
+    a[offsets[4]:offsets[5]] = cu
+    a[offsets[5]:offsets[5] + len(rows)] = rows
+    for at, t in zip(table_at, tables):
+        a[at:at + B * len(t[0])] = np.asarray(t, dtype=np.int64).reshape(-1)
     dev = host.to(cache.device, non_blocking=True)
+    if staging is not None and on_gpu:
+        staging.sent(turn)
     views = [dev[offsets[i]:offsets[i + 1]] for i in range(5)] + [dev[offsets[5]:offsets[5] + len(rows)]]
-    bts = [dev[a:a + B * len(t[0])].view(B, len(t[0])) for a, t in zip(table_at, tables)]
+    bts = [dev[at:at + B * len(t[0])].view(B, len(t[0])) for at, t in zip(table_at, tables)]
     return StepContext(n_tokens=n, n_seqs=B, n_wanted=len(rows), tok_ids=views[0], tok_seq=views[1],
                        tok_pos=views[2], seq_slots=views[3], cu_seqlens=views[4], logit_rows=views[5],
                        block_tables=bts, q_lens=q_lens, kv_lens=[s + q for s, q in zip(starts, q_lens)],
-                       is_decode=all(q == 1 for q in q_lens), h2d_bytes=host.numel() * 4,
+                       is_decode=all(q == 1 for q in q_lens), h2d_bytes=total * 4,
                        max_kv_len=max(s + q for s, q in zip(starts, q_lens)))
 
 
@@ -94,6 +128,7 @@ class Engine:
         self.model = model
         self.graphs = DecodeGraphs(self) if use_graphs else None
         self._last_graph = None   # the graph of the last step, if that step ran through one
+        self._staging = Staging()
         self.h2d_bytes_last_step = 0
         requests, cache_of = model.cache_requests()
         rt = model.rt
@@ -137,7 +172,7 @@ class Engine:
                     raise InvalidArgument(f"sequence {b}: wanted place {i} is outside its {len(toks)} tokens")
 
     def build_context(self, slots, tokens, want) -> StepContext:
-        ctx = make_context(self.cache, slots, tokens, want)
+        ctx = make_context(self.cache, slots, tokens, want, self._staging)
         self.h2d_bytes_last_step = ctx.h2d_bytes
         return ctx
 
