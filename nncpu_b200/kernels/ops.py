@@ -38,7 +38,14 @@ def _ptr(t: Optional[torch.Tensor]):
     return _vp(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream of the current device as a raw handle (the short way when torch offers it: this is
+    asked once per kernel launch)."""
+    if _raw_stream is not None:
+        return _vp(_raw_stream(torch._C._cuda_getDevice()))
     return _vp(torch.cuda.current_stream().cuda_stream)
 
 
