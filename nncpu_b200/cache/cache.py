@@ -119,6 +119,9 @@ class Cache:
         self.n_slots = n_slots if n_slots is not None else self.n_pages
         self.slots = IndexPool(self.n_slots, "sequence slot")
         self.lengths = [0] * self.n_slots
+        # counts the sequences a slot has held: whoever remembers a slot's page table must forget it when
+        # the number has changed
+        self.generation = [0] * self.n_slots
         self.groups: List[KVGroup] = []
         self._entry_group: List[Optional[Tuple[int, int]]] = [None] * len(requests)
         self._owns: List[bool] = [False] * len(requests)
@@ -149,6 +152,7 @@ class Cache:
     def alloc_slot(self) -> int:
         slot = self.slots.take()
         self.lengths[slot] = 0
+        self.generation[slot] += 1
         return slot
 
     def free_slot(self, slot: int) -> None:

@@ -66,6 +66,7 @@ class DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.n_kernels = 0
         self.slots: Optional[tuple] = None
+        self.gens: Optional[tuple] = None
         self.pages_seen: List[List[int]] = []
         self.h2d_bytes = 0
 
@@ -81,7 +82,9 @@ class DecodeGraph:
             self.events[i].synchronize()
         a = self.host_np[i]
         prev = self.host_np[(i - 1) % _RING]
-        same = self.slots == tuple(slots)
+        # the tables of the step before may be built upon only if these are the same sequences in the same slots
+        gens = tuple(cache.generation[s] for s in slots)
+        same = self.slots == tuple(slots) and self.gens == gens
         if same:
             a[:] = prev
         else:
@@ -93,6 +96,7 @@ class DecodeGraph:
             a[self.o_cu:self.o_cu + B + 1] = np.arange(B + 1)
             a[self.o_rows:self.o_rows + n] = np.arange(n)
             self.slots = tuple(slots)
+            self.gens = gens
             self.pages_seen = [[0] * n for _ in cache.groups]
         a[self.o_pos:self.o_pos + n] = [cache.lengths[s] for s in slots]
         for g, group in enumerate(cache.groups):

@@ -132,6 +132,34 @@ def test_long_prompts_whole_cut_and_batched(folders, plains, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_reused_slots_with_other_pages_and_the_same_lengths(folders, plains, dtype):
+    """Two pairs of requests of the same lengths, one after the other in the same slots.  The second pair's
+    prompts run in the other order, so the slots hold other pages while every length is what it was: a
+    decode step that remembered the first pair's page tables would read the first pair's keys."""
+    plain = plains["B", dtype]
+    model = Model.load(folders["B", dtype], dtype=dtype)
+    engine = Engine(model, max_tokens=64 * 8)
+    for round_ in range(2):
+        a, b = tokens_for(plain, 70 + 6, 21 + 10 * round_), tokens_for(plain, 130 + 6, 22 + 10 * round_)
+        want_a, want_b = plain.logits(a), plain.logits(b)
+        slots = sorted([engine.alloc_slot(), engine.alloc_slot()])
+        if round_ == 0:
+            engine.step(slots, [a[:70], b[:130]])
+        else:
+            engine.step([slots[1]], [b[:130]])
+            engine.step([slots[0]], [a[:70]])
+        got_a, got_b = [], []
+        for i in range(6):
+            out = engine.step(slots, [[a[70 + i]], [b[130 + i]]])
+            got_a.append(out[0:1].clone())
+            got_b.append(out[1:2].clone())
+        check(torch.cat(got_a), want_a[70:], TOL[dtype], f"round {round_}, first request")
+        check(torch.cat(got_b), want_b[130:], TOL[dtype], f"round {round_}, second request")
+        for s_ in slots:
+            engine.free_slot(s_)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding_and_first_tokens(folders, plains, dtype):
     plain = plains["B", dtype]
     model = Model.load(folders["B", dtype], dtype=dtype)
