@@ -179,3 +179,45 @@ def test_command_line_token_run(setup):
     assert p.returncode == 0, p.stderr[-2000:]
     assert [int(t) for t in p.stdout.split()] == plain_greedy(plain, [5, 6, 7, 8], 6, stops=(255,))
     assert "tok/s" in p.stderr
+
+
+def plain_run(plain, prompt, max_tokens, stops, n_ctx):
+    """The generation loop's decisions on one request, with the plain model and greedy choices."""
+    toks, out = list(prompt), []
+    while True:
+        t = argmax_first(plain.logits(toks)[-1])
+        toks.append(t)
+        if t in stops:
+            return out, StopReason.END_OF_TURN
+        out.append(t)
+        if len(toks) >= n_ctx:
+            return out, StopReason.CONTEXT_FULL
+        if max_tokens > 0 and len(out) >= max_tokens:
+            return out, StopReason.MAX_TOKENS
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_generate_calls_on_one_session(tmp_path, seed):
+    """Random configurations, three generate() calls each on one session (slots and pages are reused, batches
+    follow one another), stop tokens taken from the continuation itself, count and context limits: tokens and
+    stop reasons are the plain greedy loop's, in float32."""
+    from test_gpu_random_configs import random_config
+    from tiny import make_folder
+    rs = np.random.RandomState(5000 + seed)
+    folder = make_folder(tmp_path / "m", "A", seed=seed, store_dtype=torch.float32, **random_config(rs))
+    plain = PlainQwen3(folder)
+    n_ctx = int(rs.choice([64, 128, 200]))
+    session = Session(Model.load(folder, dtype="float32"),
+                      SessionParams(n_ctx=n_ctx, seed=1, max_batch=int(rs.choice([1, 2, 3, 4]))))
+    for call in range(3):
+        prompts = [rs.randint(0, plain.cfg.vocab, size=int(rs.choice([1, 2, 5, 17, 40, 60]))).tolist()
+                   for _ in range(int(rs.randint(1, 7)))]
+        max_tokens = int(rs.choice([0, 1, 2, 5, 12, 30]))
+        continuation, _ = plain_run(plain, prompts[0], 12, (), n_ctx)
+        stops = sorted(set(continuation[2:4])) if rs.rand() < 0.6 else []
+        res = session.generate(prompts, GenerateParams(max_tokens, SamplerParams.greedy()), stop_token_ids=stops)
+        for i, (p, r) in enumerate(zip(prompts, res)):
+            want, why = plain_run(plain, p, max_tokens, stops, n_ctx)
+            assert (r.tokens, r.stop) == (want, why), (seed, call, i)
+        session.engine.cache.check()
+        assert session.engine.cache.slots.n_held == 0
