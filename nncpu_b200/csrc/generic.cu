@@ -604,13 +604,13 @@ __device__ __forceinline__ uint32_t float_order(float v) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-__global__ void __launch_bounds__(1024)
-topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int* __restrict__ out_ids, int vocab, int k) {
+// The selection itself, for a block of 1024 threads: vals and ids (global or shared memory) receive the k
+// candidates of `row` in no particular order.
+__device__ void select_topk(const float* __restrict__ row, int vocab, int k, float* vals, int* ids) {
     __shared__ int hist[256];
     __shared__ uint32_t prefix_s;
     __shared__ int need_s, n_out;
     __shared__ int seg[1024];
-    const float* row = logits + (size_t)blockIdx.x * vocab;
     const int tid = threadIdx.x, nt = blockDim.x;
     // radix select, most significant byte first: after 4 rounds `prefix` is the image of the k-th largest value
     uint32_t prefix = 0, mask = 0;
@@ -653,8 +653,6 @@ topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int*
     }
     __syncthreads();
     int tie_rank = seg[tid];
-    float* vals = out_vals + (size_t)blockIdx.x * k;
-    int* ids = out_ids + (size_t)blockIdx.x * k;
     for (int i = lo; i < hi; ++i) {
         const float v = row[i];
         const uint32_t u = float_order(v);
@@ -665,6 +663,101 @@ topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int*
             if (at < k) { vals[at] = (v == v) ? v : -INFINITY; ids[at] = i; }
         }
     }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(1024)
+topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int* __restrict__ out_ids, int vocab, int k) {
+    select_topk(logits + (size_t)blockIdx.x * vocab, vocab, k, out_vals + (size_t)blockIdx.x * k,
+                out_ids + (size_t)blockIdx.x * k);
+}
+
+// ---------------------------------------------------------------------------
+// The whole sampling chain of one row on the device, for 0 < top-k <= 1024: the k candidates, their ranking
+// (higher logit first, then lower id), top-p and min-p on the distribution at temperature 1, temperature over
+// the survivors and the draw in rank order from u[row], uniform in [0, 1)
+// (crates/nncpu/src/session/sample.rs:121-201).  After the selection and a bitonic sort one thread walks the
+// few candidates with the arithmetic of the reference: 32-bit weights, 64-bit sums.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+sample_chain_kernel(const float* __restrict__ logits, const double* __restrict__ u, int* __restrict__ out, int vocab,
+                    int k, float temperature, float top_p, float min_p) {
+    __shared__ float c_val[1024];
+    __shared__ int c_id[1024];
+    __shared__ unsigned long long key[1024];
+    const int tid = threadIdx.x;
+    select_topk(logits + (size_t)blockIdx.x * vocab, vocab, k, c_val, c_id);
+    // ascending by (descending logit, ascending id); the padding sorts last
+    int n2 = 1;
+    while (n2 < k) n2 <<= 1;
+    if (tid < n2)
+        key[tid] = tid < k ? ((unsigned long long)(~float_order(c_val[tid])) << 32) | (uint32_t)c_id[tid] : ~0ull;
+    __syncthreads();
+    for (int size = 2; size <= n2; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (tid < n2) {
+                const int other = tid ^ stride;
+                if (other > tid) {
+                    const bool up = (tid & size) == 0;
+                    const unsigned long long a = key[tid], b = key[other];
+                    if ((a > b) == up) { key[tid] = b; key[other] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid < k) {
+        const uint32_t image = ~(uint32_t)(key[tid] >> 32);
+        c_val[tid] = __uint_as_float((image & 0x80000000u) ? (image & 0x7fffffffu) : ~image);
+        c_id[tid] = (int)(uint32_t)key[tid];
+    }
+    __syncthreads();
+    if (tid != 0) return;
+    const float top = c_val[0];
+    if (!(top > -INFINITY) || top == INFINITY) {   // nothing finite to draw from
+        out[blockIdx.x] = c_id[0];
+        return;
+    }
+    // weights at temperature 1
+    double total = 0.0;
+    for (int i = 0; i < k; ++i) total += (double)expf(c_val[i] - top);
+    int keep = k;
+    if (top_p > 0.0f && top_p < 1.0f) {
+        double cum = 0.0;
+        for (int i = 0; i < k; ++i) {
+            cum += (double)expf(c_val[i] - top) / total;
+            if (cum >= (double)top_p) { keep = i + 1; break; }
+        }
+    }
+    if (min_p > 0.0f) {
+        const float floor_ = min_p * 1.0f;   // the best candidate's weight is exp(0) = 1
+        int i = 1;
+        while (i < keep && expf(c_val[i] - top) >= floor_) ++i;
+        keep = i;
+    }
+    const double inv_t = 1.0 / (double)temperature;
+    double sum_t = 0.0;
+    for (int i = 0; i < keep; ++i) sum_t += (double)(float)exp((double)(c_val[i] - top) * inv_t);
+    double r = u[blockIdx.x] * sum_t;
+    int chosen = c_id[keep - 1];
+    for (int i = 0; i < keep; ++i) {
+        r -= (double)(float)exp((double)(c_val[i] - top) * inv_t);
+        if (r <= 0.0) { chosen = c_id[i]; break; }
+    }
+    out[blockIdx.x] = chosen;
+}
+
+extern "C" int nncpu_sample_chain(const float* logits, const double* u, int* out, int n_rows, int vocab, int top_k,
+                                  float temperature, float top_p, float min_p, void* stream) {
+    NN_CHECK(n_rows >= 0 && vocab > 0, "sample_chain: %d rows of %d", n_rows, vocab);
+    NN_CHECK(top_k > 0 && top_k <= 1024 && top_k <= vocab, "sample_chain: top-k %d is outside 1..min(1024, %d)", top_k, vocab);
+    NN_CHECK(temperature > 0.0f && temperature < INFINITY, "sample_chain: temperature %g", (double)temperature);
+    NN_CHECK(top_p >= 0.0f && top_p <= 1.0f && min_p >= 0.0f && min_p <= 1.0f, "sample_chain: top-p %g, min-p %g",
+             (double)top_p, (double)min_p);
+    if (n_rows == 0) return 0;
+    sample_chain_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, u, out, vocab, top_k, temperature, top_p, min_p);
+    NN_LAUNCH_OK("sample_chain");
+    return 0;
 }
 
 // Per row: sum over the vocabulary of exp(logit - largest logit), NaN as -inf: the denominator of the

@@ -18,14 +18,15 @@ The loop talks to an engine through ``alloc_slot``, ``free_slot``, ``step``
 and ``max_seq_len`` only, and to a chooser through ``choose(logits, indices)``,
 so its decisions can be tested with scripted stand-ins for both.
 
-Greedy decoding does not wait for the host: when the chooser says its choice
-is the engine's own device-side greedy choice (``greedy_on_device``) and the
-engine offers ``greedy_fetch`` and ``step_again``, the next step is launched
-with the tokens still on the device while the host reads the previous step's
-tokens and takes its decisions one step behind.  A sequence that the host
-then stops has run one step too many, which nobody sees: its slot is freed.
-Steps in which a count limit (context, ``max_tokens``) can end a sequence are
-not run ahead.
+Decoding does not wait for the host where the choice can be made on the
+device: when the chooser says so (``chooses_on_device``; greedy choices are
+even made by the engine's decode graph itself, ``greedy_on_device``) and the
+engine offers ``choice_buffer``, ``fetch_choices`` and ``step_again``, the
+chooser's kernels write the tokens into the engine's buffer, the next step is
+launched on top of them, and the host reads the tokens meanwhile and takes its
+decisions one step behind.  A sequence that the host then stops has run one
+step too many, which nobody sees: its slot is freed.  Steps in which a count
+limit (context, ``max_tokens``) can end a sequence are not run ahead.
 """
 from __future__ import annotations
 
@@ -86,8 +87,8 @@ def generate(engine, chooser, prompts: Sequence[Sequence[int]], params: Generate
 
 def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_ctx, results) -> None:
     live = []  # [index, slot, tokens so far (prompt + generated), result]
-    device_greedy = (getattr(chooser, "greedy_on_device", False) and hasattr(engine, "greedy_fetch")
-                     and hasattr(engine, "step_again"))
+    on_device = ((getattr(chooser, "chooses_on_device", False) or getattr(chooser, "greedy_on_device", False))
+                 and all(hasattr(engine, a) for a in ("choice_buffer", "fetch_choices", "step_again")))
 
     def settle(rows, chosen):
         """Takes one chosen token per sequence of ``rows``; returns the sequences that go on."""
@@ -126,11 +127,14 @@ def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_c
                     r.stop = StopReason.CANCELLED
                 break
             ahead = None
-            fetch = engine.greedy_fetch(len(live)) if device_greedy and prefill is not None else None
-            if fetch is not None:
-                # The step in flight chose its tokens on the device: start their copy to the host and, unless a
-                # count limit may end a sequence with this very token, launch the next step on top of them.
-                event, ids = fetch
+            buffer = engine.choice_buffer(len(live)) if on_device and prefill is not None else None
+            if buffer is not None:
+                # The tokens of the step in flight are chosen on the device (a greedy choice is there already,
+                # made by the step itself): start their copy to the host and, unless a count limit may end a
+                # sequence with this very token, launch the next step on top of them.
+                if not getattr(chooser, "greedy_on_device", False):
+                    chooser.enqueue(logits, [idx for idx, _, _, _ in live], buffer)
+                event, ids = engine.fetch_choices(len(live))
                 if all(len(toks) + 2 <= n_ctx and (params.max_tokens <= 0 or r.n_generated + 2 <= params.max_tokens)
                        for _, _, toks, r in live):
                     ahead = engine.step_again([s for _, s, _, _ in live])
@@ -151,7 +155,9 @@ def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_c
                 # next round starts with a plain step.
                 going_on = {m[0] for m in still}
                 rows = [k for k, m in enumerate(live) if m[0] in going_on]
-                event, ids = engine.greedy_fetch(len(live))
+                if not getattr(chooser, "greedy_on_device", False):
+                    chooser.enqueue(ahead, [m[0] for m in live], engine.choice_buffer(len(live)))
+                event, ids = engine.fetch_choices(len(live))
                 event.synchronize()
                 still = settle(still, [int(ids[k]) for k in rows])
             live = still

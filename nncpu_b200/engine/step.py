@@ -201,13 +201,20 @@ class Engine:
         self.cache.commit(slots, ctx.q_lens)
         return logits
 
-    # -- greedy decoding without a host round trip per step ----------------------
+    # -- decoding without a host round trip per step -----------------------------
 
-    def greedy_fetch(self, n: int):
-        """Starts the copy of the last graph step's greedy choices (one per
-        sequence, made by the graph itself) to pinned host memory.  Returns
-        ``(event, ids)``: after ``event.synchronize()`` ``ids[:n]`` holds them.
-        None if the last step did not run through a graph."""
+    def choice_buffer(self, n: int) -> Optional[torch.Tensor]:
+        """Where the last graph step's choices live on the device: int32 [n],
+        filled by the graph itself with the greedy choice of every sequence; a
+        chooser that draws on the device overwrites it.  None if the last step
+        did not run through a graph."""
+        g = self._last_graph
+        return None if g is None else g.next_ids[:n]
+
+    def fetch_choices(self, n: int):
+        """Starts the copy of the choice buffer to pinned host memory, in
+        stream order.  Returns ``(event, ids)``: after ``event.synchronize()``
+        ``ids[:n]`` holds the tokens.  None if the last step did not run through a graph."""
         g = self._last_graph
         if g is None:
             return None
@@ -215,7 +222,7 @@ class Engine:
 
     def step_again(self, slots: Sequence[int]) -> torch.Tensor:
         """One more decode step for exactly the sequences of the last graph
-        step, each fed its own greedy choice of that step, which never leaves
+        step, each fed its token from the choice buffer, which never leaves
         the device."""
         slots = [int(s) for s in slots]
         g = self._last_graph

@@ -319,6 +319,16 @@ def topk(logits, vals, ids) -> None:
     _call("generic", "nncpu_topk", _ptr(logits), _ptr(vals), _ptr(ids), _i(n), _i(vocab), _i(k), _stream())
 
 
+def sample_chain(logits, u, out, top_k: int, temperature: float, top_p: float, min_p: float) -> None:
+    """The whole chain on the device for 0 < top_k <= 1024: out[r] = the token drawn from row r with the
+    uniform u[r] (float64 in [0, 1)) after top-k, top-p, min-p and temperature, in rank order."""
+    n, vocab = logits.shape
+    assert logits.dtype == torch.float32 and u.dtype == torch.float64 and out.dtype == torch.int32
+    assert u.numel() >= n and out.numel() >= n
+    _call("generic", "nncpu_sample_chain", _ptr(logits), _ptr(u), _ptr(out), _i(n), _i(vocab), _i(top_k),
+          _f(temperature), _f(top_p), _f(min_p), _stream())
+
+
 def row_exp_sum(logits, out) -> None:
     """out[r] (float64) = sum over the row of exp(logit - the row's largest logit), NaN as -inf."""
     n, vocab = logits.shape

@@ -145,7 +145,7 @@ def test_engine_failure_gives_every_slot_back():
 
 class AheadEngine(FakeEngine):
     """A FakeEngine whose decode steps choose their tokens themselves, by the Script's rule, and can be run
-    again on top of those choices (``step_again``) before the host has read them (``greedy_fetch``)."""
+    again on top of those choices (``step_again``) before the host has read them (``fetch_choices``)."""
 
     class _Event:
         def synchronize(self):
@@ -175,7 +175,10 @@ class AheadEngine(FakeEngine):
         self.last = (list(slots), [self.special.get((self.owner[s], n), 100 + n) for s, n in out]) if decode else None
         return out
 
-    def greedy_fetch(self, n):
+    def choice_buffer(self, n):
+        return None if self.last is None else object()
+
+    def fetch_choices(self, n):
         if self.last is None:
             return None
         assert n == len(self.last[0])

@@ -691,6 +691,30 @@ def test_sample_temperature(ops):
         ops.sample_temperature(logits, torch.zeros(4000, dtype=torch.float64, device=DEV), out, 0.0)
 
 
+def test_sample_chain_on_the_device(ops):
+    """The whole chain in one kernel against the plain chain: the same uniform numbers give the same tokens,
+    with ties at the top-k boundary, NaN, flat and peaked rows, every combination of the cuts."""
+    from plain_qwen3 import PlainMt19937_64, sample_chain
+    rs = np.random.RandomState(12)
+    for vocab in (50, 1031, 20011):
+        rows = np.stack([(rs.randn(vocab) * s).astype(np.float32) for s in (8.0, 3.0, 1.0, 0.05, 3.0, 3.0)])
+        rows[4] = np.round(rows[4])                        # ties everywhere
+        rows[5, rs.randint(vocab, size=vocab // 5)] = np.nan
+        dev = torch.tensor(rows).to(DEV)
+        for top_k, temp, top_p, min_p in ((40, 0.7, 0.95, 0.05), (1, 1.0, 1.0, 0.0), (7, 1.3, 1.0, 0.0),
+                                          (40, 0.5, 0.5, 0.0), (40, 1.0, 1.0, 0.3), (min(1024, vocab - 1), 0.9, 0.9, 0.01)):
+            gens = [PlainMt19937_64(77 + r) for r in range(6)]
+            mine = [PlainMt19937_64(77 + r) for r in range(6)]
+            for draw in range(8):
+                u = torch.tensor([g.uniform(1.0) for g in mine], dtype=torch.float64).to(DEV)
+                out = torch.empty(6, dtype=torch.int32, device=DEV)
+                ops.sample_chain(dev, u, out, top_k, temp, top_p, min_p)
+                want = [sample_chain(rows[r], gens[r], temp, top_k, top_p, min_p) for r in range(6)]
+                assert out.tolist() == want, (vocab, top_k, temp, top_p, min_p, draw)
+    with pytest.raises(ExtensionError, match="top-k"):
+        ops.sample_chain(dev, u, out, 0, 1.0, 1.0, 0.0)
+
+
 def test_row_exp_sum(ops):
     rs = np.random.RandomState(4)
     for vocab in (3, 307, 151936):
