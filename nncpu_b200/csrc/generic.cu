@@ -604,9 +604,9 @@ __device__ __forceinline__ uint32_t float_order(float v) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// The selection itself, for a block of 1024 threads: vals and ids (global or shared memory) receive the k
-// candidates of `row` in no particular order.
-__device__ void select_topk(const float* __restrict__ row, int vocab, int k, float* vals, int* ids) {
+// The selection by radix, for a block of 1024 threads: vals and ids (global or shared memory) receive the k
+// candidates of `row` in no particular order.  Works for every row and every k.
+__device__ void select_topk_radix(const float* __restrict__ row, int vocab, int k, float* vals, int* ids) {
     __shared__ int hist[256];
     __shared__ uint32_t prefix_s;
     __shared__ int need_s, n_out;
@@ -666,10 +666,106 @@ __device__ void select_topk(const float* __restrict__ row, int vocab, int k, flo
     __syncthreads();
 }
 
+// Ascending bitonic sort of key[0 .. n2) by a block of at least n2 threads; n2 a power of two.
+__device__ void sort_keys(unsigned long long* key, int n2) {
+    const int tid = threadIdx.x;
+    for (int size = 2; size <= n2; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (tid < n2) {
+                const int other = tid ^ stride;
+                if (other > tid) {
+                    const bool up = (tid & size) == 0;
+                    const unsigned long long a = key[tid], b = key[other];
+                    if ((a > b) == up) { key[tid] = b; key[other] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// (descending logit, ascending id) as one ascending 64-bit key, and back.
+__device__ __forceinline__ unsigned long long rank_key(float v, int id) {
+    return ((unsigned long long)(~float_order(v)) << 32) | (uint32_t)id;
+}
+__device__ __forceinline__ float key_value(unsigned long long key) {
+    const uint32_t image = ~(uint32_t)(key >> 32);
+    return __uint_as_float((image & 0x80000000u) ? (image & 0x7fffffffu) : ~image);
+}
+
+// The quick way to the k candidates, which serves the rows a language model produces: the candidates lie within
+// 16 of the row's largest logit.  One pass finds the largest, one counts the logits of that range in 1024 bins
+// (few logits share a bin there, so the counters do not collide), one gathers everything down to the bin that
+// holds the k-th, and a sort of those few puts the k best first.  `key` is scratch for 1024 keys.  Returns
+// false, having written nothing, when the range holds fewer than k logits or the gathered ones do not fit:
+// then the radix selection does the job.  On success vals and ids are in rank order.
+__device__ bool select_topk_near_max(const float* __restrict__ row, int vocab, int k, float* vals, int* ids,
+                                     unsigned long long* key) {
+    constexpr int kBins = 1024;
+    constexpr float kRange = 16.0f, kPerUnit = kBins / kRange;
+    __shared__ int fine[kBins];
+    __shared__ float red[33];
+    __shared__ int cut_bin, n_in, n_got;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += nt) {
+        const float v = row[i];
+        if (v == v) mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, red);
+    if (!(mx > -INFINITY) || mx == INFINITY) return false;
+    for (int i = tid; i < kBins; i += nt) fine[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < vocab; i += nt) {
+        const float d = mx - row[i];
+        if (d < kRange) atomicAdd(&fine[(int)(d * kPerUnit)], 1);   // false for NaN
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0, b = 0;
+        for (; b < kBins; ++b) {
+            run += fine[b];
+            if (run >= k) break;
+        }
+        cut_bin = b;
+        n_in = run;
+        n_got = 0;
+    }
+    __syncthreads();
+    const int cut = cut_bin, n = n_in;
+    if (cut >= kBins || n > 1024) return false;
+    for (int i = tid; i < vocab; i += nt) {
+        const float v = row[i];
+        const float d = mx - v;
+        if (d < kRange && (int)(d * kPerUnit) <= cut) key[atomicAdd(&n_got, 1)] = rank_key(v, i);
+    }
+    int n2 = 1;
+    while (n2 < n) n2 <<= 1;
+    __syncthreads();
+    for (int i = n + tid; i < n2; i += nt) key[i] = ~0ull;
+    __syncthreads();
+    sort_keys(key, n2);
+    if (tid < k) {
+        vals[tid] = key_value(key[tid]);
+        ids[tid] = (int)(uint32_t)key[tid];
+    }
+    __syncthreads();
+    return true;
+}
+
+// The k candidates of `row` in vals and ids; `*sorted` tells whether they came out in rank order.
+__device__ void select_topk(const float* __restrict__ row, int vocab, int k, float* vals, int* ids,
+                            unsigned long long* key, bool* sorted) {
+    *sorted = select_topk_near_max(row, vocab, k, vals, ids, key);
+    if (!*sorted) select_topk_radix(row, vocab, k, vals, ids);
+}
+
 __global__ void __launch_bounds__(1024)
 topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int* __restrict__ out_ids, int vocab, int k) {
+    __shared__ unsigned long long key[1024];
+    bool sorted;
     select_topk(logits + (size_t)blockIdx.x * vocab, vocab, k, out_vals + (size_t)blockIdx.x * k,
-                out_ids + (size_t)blockIdx.x * k);
+                out_ids + (size_t)blockIdx.x * k, key, &sorted);
 }
 
 // ---------------------------------------------------------------------------
@@ -686,32 +782,21 @@ sample_chain_kernel(const float* __restrict__ logits, const double* __restrict__
     __shared__ int c_id[1024];
     __shared__ unsigned long long key[1024];
     const int tid = threadIdx.x;
-    select_topk(logits + (size_t)blockIdx.x * vocab, vocab, k, c_val, c_id);
-    // ascending by (descending logit, ascending id); the padding sorts last
-    int n2 = 1;
-    while (n2 < k) n2 <<= 1;
-    if (tid < n2)
-        key[tid] = tid < k ? ((unsigned long long)(~float_order(c_val[tid])) << 32) | (uint32_t)c_id[tid] : ~0ull;
-    __syncthreads();
-    for (int size = 2; size <= n2; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            if (tid < n2) {
-                const int other = tid ^ stride;
-                if (other > tid) {
-                    const bool up = (tid & size) == 0;
-                    const unsigned long long a = key[tid], b = key[other];
-                    if ((a > b) == up) { key[tid] = b; key[other] = a; }
-                }
-            }
-            __syncthreads();
+    bool sorted;
+    select_topk(logits + (size_t)blockIdx.x * vocab, vocab, k, c_val, c_id, key, &sorted);
+    if (!sorted) {
+        // ascending by (descending logit, ascending id); the padding sorts last
+        int n2 = 1;
+        while (n2 < k) n2 <<= 1;
+        if (tid < n2) key[tid] = tid < k ? rank_key(c_val[tid], c_id[tid]) : ~0ull;
+        __syncthreads();
+        sort_keys(key, n2);
+        if (tid < k) {
+            c_val[tid] = key_value(key[tid]);
+            c_id[tid] = (int)(uint32_t)key[tid];
         }
+        __syncthreads();
     }
-    if (tid < k) {
-        const uint32_t image = ~(uint32_t)(key[tid] >> 32);
-        c_val[tid] = __uint_as_float((image & 0x80000000u) ? (image & 0x7fffffffu) : ~image);
-        c_id[tid] = (int)(uint32_t)key[tid];
-    }
-    __syncthreads();
     if (tid != 0) return;
     const float top = c_val[0];
     if (!(top > -INFINITY) || top == INFINITY) {   // nothing finite to draw from
