@@ -106,7 +106,7 @@ class Attention(Mixer):
         s = self.spec
         return (not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
                 and self.w_qkv.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
-                and (self.position is None or self.position.half * 2 == s.head_dim)
+                and (self.position is None or (self.position.tables_by_pair and self.position.half * 2 == s.head_dim))
                 and ops.linear_tc_qkv_supported(x, s.n_heads, s.n_kv_heads, s.head_dim))
 
     def _attend(self, ctx, q, cache, attn):

@@ -55,6 +55,14 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """``tables(ctx)`` gives float32 [n_tokens, half, 2]: for every token of the
+    step the (cos, sin) that rotate the pairs (i, i + half) of a head's first
+    2 * half dimensions.  An encoding that sets ``tables_by_pair`` also takes
+    ``tables(ctx, by_pair=True)`` and gives the same values as [half, n_tokens, 2],
+    which the fused q/k/v epilogue of long prompts reads; without it the
+    unfused kernels are used."""
+    tables_by_pair = False
+
     def tables(self, ctx):
         raise NotImplementedError
 

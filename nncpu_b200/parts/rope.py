@@ -17,6 +17,8 @@ from .base import PositionEncoding, register_position
 
 @register_position("rope_neox")
 class RopeNeox(PositionEncoding):
+    tables_by_pair = True
+
     def __init__(self, spec):
         if spec.rotary_dim % 2 or spec.rotary_dim <= 0:
             raise BadFormat(f"rotary size {spec.rotary_dim} must be even and positive")
