@@ -26,7 +26,7 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kRows = 16;     // weight rows per block
-constexpr int kUnroll = 8;    // 32-wide k groups in flight per warp
+constexpr int kUnroll = 8;    // 32-wide k groups in flight per warp with up to 8 tokens; 6 with up to 16 (registers)
 
 static_assert(kRows * 16 <= kWarps * 32, "one output element per thread with 16 tokens");
 
@@ -52,6 +52,7 @@ template <int NT, int kEpi>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, const void* __restrict__ bias,
               int bias_dt, void* __restrict__ out, int out_dt, int M, int N, int K, int lda, int ldc, int accumulate) {
+    constexpr int kU = NT == 1 ? kUnroll : 6;
     __shared__ float part[kWarps][kRows][NT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = lane & 3, r = lane >> 2;
@@ -83,10 +84,10 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
     const int k_full = K / 32;                        // groups that lie wholly inside K
     const int g_fast_end = min(g_end, k_full);
     int g0 = g_begin;
-    for (; g0 + kUnroll <= g_fast_end; g0 += kUnroll) {
-        uint4 a_lo[kUnroll], a_hi[kUnroll], b0[kUnroll], b1[kUnroll];
+    for (; g0 + kU <= g_fast_end; g0 += kU) {
+        uint4 a_lo[kU], a_hi[kU], b0[kU], b1[kU];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
+        for (int u = 0; u < kU; ++u) {
             const int k = (g0 + u) * 32 + c * 8;
             a_lo[u] = ldg16_stream(w_lo + k);
             a_hi[u] = ldg16_stream(w_hi + k);
@@ -94,7 +95,7 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
             if (NT > 1) b1[u] = *reinterpret_cast<const uint4*>(x1 + k);
         }
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
+        for (int u = 0; u < kU; ++u) {
             mma_bf16(acc[0], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b0[u].x, b0[u].y);
             mma_bf16(acc[0], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b0[u].z, b0[u].w);
             if (NT > 1) {
