@@ -221,3 +221,41 @@ def test_random_generate_calls_on_one_session(tmp_path, seed):
             assert (r.tokens, r.stop) == (want, why), (seed, call, i)
         session.engine.cache.check()
         assert session.engine.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_random_sampled_generate_calls_on_one_session(tmp_path, seed):
+    """The same with sampling: the chain runs on the device and generation one step ahead of the host; tokens,
+    stop reasons and the numbers each sequence draws are the plain loop's with the plain chain."""
+    from test_gpu_random_configs import random_config
+    from tiny import make_folder
+    rs = np.random.RandomState(9000 + seed)
+    folder = make_folder(tmp_path / "m", "A", seed=seed, store_dtype=torch.float32, **random_config(rs))
+    plain = PlainQwen3(folder)
+    n_ctx, session_seed = int(rs.choice([64, 128, 200])), int(rs.randint(1, 1000))
+    session = Session(Model.load(folder, dtype="float32"),
+                      SessionParams(n_ctx=n_ctx, seed=session_seed, max_batch=int(rs.choice([1, 2, 3, 4]))))
+    for call in range(2):
+        prompts = [rs.randint(0, plain.cfg.vocab, size=int(rs.choice([1, 3, 9, 30, 50]))).tolist()
+                   for _ in range(int(rs.randint(1, 6)))]
+        max_tokens = int(rs.choice([1, 3, 8, 20]))
+        sp = SamplerParams(float(rs.choice([0.6, 1.0, 1.5])), int(rs.choice([1, 5, 40])), float(rs.choice([1.0, 0.9])),
+                           float(rs.choice([0.0, 0.05])))
+        stops = [int(x) for x in rs.randint(0, plain.cfg.vocab, size=plain.cfg.vocab // 6)] if rs.rand() < 0.6 else []
+        res = session.generate(prompts, GenerateParams(max_tokens, sp), stop_token_ids=stops)
+        for i, (p, r) in enumerate(zip(prompts, res)):
+            rng = PlainMt19937_64(session_seed + 1000003 * call + i)   # a generator per call and sequence
+            toks, out, why = list(p), [], None
+            while why is None:
+                t = sample_chain(plain.logits(toks)[-1], rng, sp.temperature, sp.top_k, sp.top_p, sp.min_p)
+                toks.append(t)
+                if t in stops:
+                    why = StopReason.END_OF_TURN
+                else:
+                    out.append(t)
+                    if len(toks) >= n_ctx:
+                        why = StopReason.CONTEXT_FULL
+                    elif len(out) >= max_tokens:
+                        why = StopReason.MAX_TOKENS
+            assert (r.tokens, r.stop) == (out, why), (seed, call, i)
+        session.engine.cache.check()
