@@ -5,21 +5,24 @@
 //
 // Operand tiles come to shared memory by TMA (128-byte swizzle); one elected
 // thread issues tcgen05.mma with the accumulator in tensor memory; four warps
-// read the accumulator back with tcgen05.ld for the epilogue.  The kernel is
-// persistent: each block walks a list of work items (output tile x slice of K)
-// and keeps two accumulators in tensor memory, so the epilogue of one item
-// runs under the matrix instructions of the next.
+// read the accumulator back with tcgen05.ld for the epilogue.  The kernels are
+// persistent: each block walks a list of work items and keeps two accumulators
+// in tensor memory, so the epilogue of one item runs under the matrix
+// instructions of the next.
 //
-// One kernel serves prefill and decode.  The tensor-core M operand is always a
-// 128-row tile of "A" and the N operand a BN-row tile of "B":
-//   * many tokens:  A = activations, B = weights;
-//   * few tokens:   A = weights, B = activations, and the epilogue stores the
-//     tile transposed: every weight byte is read once and no tensor-core row
-//     is spent on padding.  With few tokens there are few output tiles, so K is
-//     cut into slices that run on different SMs; each slice writes its partial
-//     tile to scratch memory and takes a ticket, and the block that takes the
-//     last ticket of a tile adds the slices in slice order, so the sum does not
-//     depend on which block came last.  No block waits for another.
+// The tensor-core M operand is always a 128-row tile of "A" and the N operand a
+// BN-row tile of "B":
+//   * many tokens:  A = activations, B = weights; from 512 tokens on two SMs
+//     share a 256 x 256 tile (gemm_pair_kernel);
+//   * few tokens (up to 256):  A = weights, B = activations, and the epilogue
+//     stores the tile transposed: every weight byte is read once and no
+//     tensor-core row is spent on padding.  There are few output tiles then, so
+//     K is cut: either the k-blocks of all tiles are dealt out evenly to the
+//     blocks and a second kernel adds the parts of split tiles
+//     (gemm_streamk_kernel), or a thread-block cluster shares a tile and adds
+//     its slices through distributed shared memory (gemm_cluster_kernel).
+//     Both add in a fixed order: the sum does not depend on timing, and no
+//     block waits for another outside a cluster barrier.
 // The reference computes the same products with its own BF16 row kernels
 // (crates/nncpu/src/kernels/mod.rs:454-485, crates/nncpu/src/kernels/scalar.rs:555-567);
 // accumulation is 32-bit here as there.
@@ -46,8 +49,6 @@ constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA and tensor memory, wa
 enum GemmStatus : int { kOk = 0, kTimeoutEmpty = 101, kTimeoutFull = 102, kTimeoutAccumFull = 103,
                         kTimeoutAccumEmpty = 104 };
 enum Epilogue : int { kPlain = 0, kSwiglu = 1, kQkv = 2 };
-
-__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
 
@@ -78,8 +79,7 @@ struct GemmParams {
     int accumulate;  // add to what `out` holds
     int swap;        // 0: A rows are tokens; 1: A rows are output features
     int vec;         // rows of `out` may be written 16 bytes at a time
-    float* scratch;  // partial tiles of the K slices: [tile][slice][BN][128] floats
-    int* tickets;    // one counter per output tile, zero between launches
+    float* scratch;  // partial tiles of products that deal k-blocks out evenly: two slots of [BN][128] floats per block
     int* status;
     QkvParams qkv;     // epilogue kQkv only
 };
@@ -210,12 +210,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* acc_full = empty + kStages;   // [2]
     uint64_t* acc_empty = acc_full + 2;     // [2]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
-    volatile int* last_flag = (volatile int*)(tmem_slot + 1);
-    volatile int* fail_flag = last_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = p.tiles_a * p.tiles_b;
-    const int n_items = n_tiles * p.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -226,7 +223,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(&acc_full[b], 1);
             mbar_init(&acc_empty[b], 4);
         }
-        *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -241,18 +237,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    // Work item w: output tile (w % tiles_a, (w / tiles_a) % tiles_b), K slice w / n_tiles.
-    // Slice s covers the k-blocks [s * kb_total / splits, (s + 1) * kb_total / splits).
+    // Work item w: output tile (w % tiles_a, w / tiles_a), all of K.
     if (warp == 0) {
         if (lane == 0) {
             int kb_run = 0, issued = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-                const int tile = w % n_tiles, split = w / n_tiles;
-                const int m0 = (tile % p.tiles_a) * kBlockM, n0 = (tile / p.tiles_a) * BN;
-                const int kb0 = (int)((long long)split * p.kb_total / p.splits);
-                const int kb1 = (int)((long long)(split + 1) * p.kb_total / p.splits);
-                for (int kb = kb0; kb < kb1; ++kb, ++kb_run) {
+            for (int w = blockIdx.x; w < n_tiles && ok; w += gridDim.x) {
+                const int m0 = (w % p.tiles_a) * kBlockM, n0 = (w / p.tiles_a) * BN;
+                for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
                     const int s = kb_run % kStages;
                     if (!mbar_wait(&empty[s], ((kb_run / kStages) & 1) ^ 1)) {
                         atomicExch(p.status, kTimeoutEmpty);
@@ -275,10 +267,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             constexpr uint32_t idesc = instr_desc_bf16(kBlockM, BN);
             int kb_run = 0, it = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++it) {
-                const int split = w / n_tiles;
-                const int kb0 = (int)((long long)split * p.kb_total / p.splits);
-                const int kb1 = (int)((long long)(split + 1) * p.kb_total / p.splits);
+            for (int w = blockIdx.x; w < n_tiles && ok; w += gridDim.x, ++it) {
                 const int buf = it & 1;
                 if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1)) {
                     atomicExch(p.status, kTimeoutAccumEmpty);
@@ -286,7 +275,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kAccCols);
-                for (int kb = kb0; kb < kb1; ++kb, ++kb_run) {
+                for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
                     const int s = kb_run % kStages;
                     if (!mbar_wait(&full[s], (kb_run / kStages) & 1)) {
                         atomicExch(p.status, kTimeoutFull);
@@ -300,7 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     for (int k = 0; k < kBlockK / kUmmaK; ++k) {
                         const uint64_t a_desc = smem_desc_sw128(a_addr + k * kUmmaK * 2);
                         const uint64_t b_desc = smem_desc_sw128(b_addr + k * kUmmaK * 2);
-                        umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[s]);
                 }
@@ -311,91 +300,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // Epilogue: warp w may read the tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
-        const int ep_tid = threadIdx.x - 64;
         int it = 0;
-        for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++it) {
-            const int tile = w % n_tiles, split = w / n_tiles;
-            const int m0 = (tile % p.tiles_a) * kBlockM, n0 = (tile / p.tiles_a) * BN;
+        for (int w = blockIdx.x; w < n_tiles; w += gridDim.x, ++it) {
+            const int m0 = (w % p.tiles_a) * kBlockM, n0 = (w / p.tiles_a) * BN;
             const int a_row = m0 + row_in_tile;
             const int buf = it & 1;
-            const bool ok = mbar_wait(&acc_full[buf], (it >> 1) & 1);
-            if (!ok && lane == 0) {
-                atomicExch(p.status, kTimeoutAccumFull);
-                *fail_flag = 1;
+            if (!mbar_wait(&acc_full[buf], (it >> 1) & 1)) {
+                if (lane == 0) atomicExch(p.status, kTimeoutAccumFull);
+                break;
             }
             __syncwarp();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kAccCols);
-            if (p.splits == 1) {
-                if (!ok) break;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + (uint32_t)c0, v);
-                    store16<kEpi>(p, a_row, n0 + c0, v);
-                }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            } else {
-                // this slice's partial tile, column by column so that a warp writes 128 contiguous bytes
-                float* mine = p.scratch + ((size_t)tile * p.splits + split) * (BN * kBlockM);
-                if (ok) {
-#pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
-                        float v[16];
-                        tmem_ld16(taddr + (uint32_t)c0, v);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) mine[(c0 + j) * kBlockM + row_in_tile] = v[j];
-                    }
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                }
-                __threadfence();
-                epilogue_bar();  // the four epilogue warps pass every barrier together, also after a failed wait
-                if (ep_tid == 0) {
-                    int last = 0;
-                    if (!*fail_flag) {
-                        const int ticket = atomicAdd(&p.tickets[tile], 1);
-                        last = ticket == p.splits - 1;
-                        if (last) p.tickets[tile] = 0;  // ready for the next launch
-                    }
-                    *last_flag = last;
-                }
-                epilogue_bar();
-                if (*last_flag) {
-                    __threadfence();
-                    const float* all = p.scratch + (size_t)tile * p.splits * (BN * kBlockM);
-#pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
-                        float v[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                        // slices are added in slice order; two slices' loads are in flight at a time
-                        int s = 0;
-                        for (; s + 2 <= p.splits; s += 2) {
-                            const float* src = all + (size_t)s * (BN * kBlockM) + c0 * kBlockM + row_in_tile;
-                            float x0[16], x1[16];
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                x0[j] = __ldcg(src + j * kBlockM);
-                                x1[j] = __ldcg(src + BN * kBlockM + j * kBlockM);
-                            }
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] = (v[j] + x0[j]) + x1[j];
-                        }
-                        if (s < p.splits) {
-                            const float* src = all + (size_t)s * (BN * kBlockM) + c0 * kBlockM + row_in_tile;
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + j * kBlockM);
-                        }
-                        store16<kEpi>(p, a_row, n0 + c0, v);
-                    }
-                }
-                epilogue_bar();  // the flags are read before the next item overwrites them
-                if (*fail_flag) break;
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr + (uint32_t)c0, v);
+                store16<kEpi>(p, a_row, n0 + c0, v);
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -415,7 +340,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // of tiles; a tile whose k-blocks fall to several blocks is put together from
 // their partial tiles: each block writes its own to scratch memory, and a
 // second, wide kernel adds a tile's parts in block order (the order of k) and
-// runs the epilogue.  No block waits for another, no tickets, and the sum does
+// runs the epilogue.  No block waits for another, and the sum does
 // not depend on timing.  Used for 17 to 256 tokens (weights are the 128-row
 // operand), where tiles are few and K is long.
 // ---------------------------------------------------------------------------
@@ -655,7 +580,7 @@ gemm_streamk_fixup_kernel(const GemmParams p, int blocks) {
 // copies the partial tile to its shared memory, and after a cluster barrier
 // every block adds up one share of the tile's columns, reading the other
 // blocks' partial tiles through distributed shared memory in rank order.  No
-// global scratch, no tickets, and the sum does not depend on timing.
+// global scratch, and the sum does not depend on timing.
 // Used when A rows are output features (few tokens); one tile per cluster.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -1181,7 +1106,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int bloc
         NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    const int n_items = p.tiles_a * p.tiles_b * p.splits;
+    const int n_items = p.tiles_a * p.tiles_b;
     const int grid = n_items < blocks_per_sm * sm_count() ? n_items : blocks_per_sm * sm_count();
     gemm_bf16_kernel<BN, kStages, kEpi><<<grid, kThreads, smem, stream>>>(ma, mb, p);
     NN_LAUNCH_OK("gemm_bf16");
@@ -1217,6 +1142,7 @@ int launch_streamk(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, 
 template <int kEpi>
 int dispatch_streamk(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
     switch (bn) {
+        case 16: return launch_streamk<16, 10, kEpi>(ma, mb, p, stream);
         case 32: return launch_streamk<32, 10, kEpi>(ma, mb, p, stream);
         case 64: return launch_streamk<64, 8, kEpi>(ma, mb, p, stream);
         case 128: return launch_streamk<128, 6, kEpi>(ma, mb, p, stream);
@@ -1311,10 +1237,8 @@ extern "C" int nncpu_linear_tc_supported(int M, int N, int K, int lda) {
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0;
 }
 
-// Floats of scratch and number of tickets a workspace must hold for any product
-// this library launches with at most `max_n` output features.
+// Floats of scratch a workspace must hold for any product this library launches.
 extern "C" long nncpu_linear_tc_scratch_floats() { return 10l << 20; }  // 40 MiB: two partial tiles of 256 x 128 per SM
-extern "C" int nncpu_linear_tc_tickets() { return 8192; }
 
 // The q/k/v projection of a prompt with its epilogue fused: X[M, K] . W[(n_heads + 2 n_kv) * 128, K]^T, then per
 // head the RMS norm (q and k, if their weights are given), the rotation (if cos_sin is given) and the stores:
@@ -1362,9 +1286,8 @@ extern "C" int nncpu_linear_tc_qkv(const void* X, const void* W, int M, int K, i
 // C[M, N] (+)= X[M, K] . W[N, K]^T + bias, or with epilogue 1: C[M, N/2] = silu(gate) * up for W rows
 // interleaved in blocks of 8 (8 gate rows, the 8 up rows of the same outputs, ...).  X and W are
 // bfloat16; C is float or bfloat16 with row stride ldc.  `scratch` (nncpu_linear_tc_scratch_floats
-// floats) and `tickets` (nncpu_linear_tc_tickets ints, zero before the first launch) serve the
-// products that cut K into slices; launches that share them must not overlap on the GPU.  `status`
-// is a device word that a kernel sets when one of its bounded waits ran out.
+// floats) serves the products that deal their k-blocks out evenly; launches that share it must not
+// overlap on the GPU.  `status` is a device word that a kernel sets when one of its bounded waits ran out.
 // 1: products of 512 or more tokens run on pairs of SMs (256 x 256 tiles); 0: one SM per 128 x 256 tile.
 static int pair_mode = 1;
 extern "C" void nncpu_linear_tc_set_pair_mode(int on) { pair_mode = on; }
@@ -1375,7 +1298,7 @@ extern "C" void nncpu_linear_tc_set_streamk_mode(int on) { streamk_mode = on; }
 
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
                                int N, int K, int lda, int ldc, int accumulate, int epilogue, float* scratch,
-                               int* tickets, int* status, void* stream_) {
+                               int* status, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(nncpu_linear_tc_supported(M, N, K, lda),
              "gemm: M %d, N %d, K %d, lda %d: K and lda must be multiples of 8 for the tensor-core path", M, N, K, lda);
@@ -1390,7 +1313,7 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
     p.K = K;
     p.kb_total = (K + kBlockK - 1) / kBlockK;
     p.out = C; p.bias = bias; p.out_dt = c_dt; p.bias_dt = bias_dt; p.ldc = ldc; p.accumulate = accumulate;
-    p.scratch = scratch; p.tickets = tickets; p.status = status;
+    p.scratch = scratch; p.status = status;
     const int esize = c_dt == DT_F32 ? 4 : 2;
     p.vec = ((uintptr_t)C % 16 == 0) && ((size_t)ldc * esize % 16 == 0);
     CUtensorMap ma, mb;
@@ -1420,25 +1343,13 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
     }
     p.tiles_a = (p.rows_a + kBlockM - 1) / kBlockM;
     p.tiles_b = (p.rows_b + bn - 1) / bn;
-    // Cut K into slices when there are too few tiles to occupy the GPU: aim at about two blocks per SM,
-    // keep at least 4 k-blocks per slice, and stay inside the workspace.
     const int n_tiles = p.tiles_a * p.tiles_b;
-    int splits = 1;
-    if (bn <= 16 && scratch != nullptr && tickets != nullptr && n_tiles <= nncpu_linear_tc_tickets()) {
-        const int want = (2 * sm_count() + n_tiles - 1) / n_tiles;
-        splits = want < 1 ? 1 : want;
-        if (splits > p.kb_total / 4) splits = p.kb_total / 4;
-        const int cap = bn <= 16 ? 16 : bn <= 32 ? 6 : 4;   // wider partial tiles cost more to write and add
-        if (splits > cap) splits = cap;
-        const long per_tile = (long)bn * kBlockM;
-        while (splits > 1 && (long)n_tiles * splits * per_tile > nncpu_linear_tc_scratch_floats()) --splits;
-        if (splits < 1) splits = 1;
-    }
-    p.splits = splits;
-    // 65 to 256 tokens: the work is cut evenly over the SMs; fewer tokens: a cluster per output tile (measured:
+    p.splits = 1;
+    // Up to 16 tokens (the few-token kernel of linear_skinny.cu is the product path for those; this serves direct
+    // calls) and 65 to 256 tokens: the work is cut evenly over the SMs; 17 to 64: a cluster per output tile (measured:
     // at 96 tokens 139 us against 220 us for the four products of a Qwen3-8B layer, at 64 tokens 123 against 117)
     // The same for 257 and more tokens that do not fill the SMs with 128 x 256 tiles at least twice.
-    const bool even_swap = p.swap && bn >= (streamk_mode == 2 ? 32 : 128);
+    const bool even_swap = p.swap && (bn <= 16 || bn >= (streamk_mode == 2 ? 32 : 128));
     const bool even_plain = !p.swap && n_tiles < 2 * sm_count();
     if ((even_swap || even_plain) && streamk_mode && scratch != nullptr &&
         2l * sm_count() * bn * kBlockM <= nncpu_linear_tc_scratch_floats()) {

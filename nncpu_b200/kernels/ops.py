@@ -112,17 +112,16 @@ def linear_tc_supported(m: int, n: int, k: int) -> bool:
 
 
 class GemmWorkspace:
-    """Device memory the tensor-core product needs besides its operands:
-    scratch for the partial tiles of products that cut K into slices, one
-    ticket counter per output tile, and the status word that a kernel sets when
-    a bounded wait ran out.  Launches that share a workspace must not overlap
-    on the GPU (one stream)."""
+    """Device memory the tensor-core kernels need besides their operands:
+    scratch for the partial tiles of products that deal their k-blocks out
+    evenly, and the status word that a kernel sets when a bounded wait ran
+    out.  Launches that share a workspace must not overlap on the GPU (one
+    stream)."""
 
     def __init__(self, device):
         lib = library.load("gemm_sm100")
         lib.nncpu_linear_tc_scratch_floats.restype = ctypes.c_long
         self.scratch = torch.empty(lib.nncpu_linear_tc_scratch_floats(), dtype=torch.float32, device=device)
-        self.tickets = torch.zeros(lib.nncpu_linear_tc_tickets(), dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
 
@@ -145,7 +144,7 @@ def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = Fals
     assert w.shape[1] == k and out.shape == (m, n // 2 if epilogue == "swiglu" else n)
     _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
           _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
-          _ptr(workspace.scratch), _ptr(workspace.tickets), _ptr(workspace.status), _stream())
+          _ptr(workspace.scratch), _ptr(workspace.status), _stream())
 
 
 def linear_tc_qkv_supported(x, n_heads: int, n_kv: int, head_dim: int) -> bool:

@@ -53,5 +53,4 @@ class Runtime:
         code = int(self._workspace.status.item())
         if code:
             self._workspace.status.zero_()
-            self._workspace.tickets.zero_()
             raise ExtensionError(f"a kernel gave up waiting (status {code}); the step's results are not valid")

@@ -100,7 +100,7 @@ def test_linear_tensor_core(ops, m, n, k):
     accb = torch.full((m, n), 0.5, dtype=torch.bfloat16, device=DEV)
     ops.linear_tc(x, w, None, accb, status, accumulate=True)
     check(accb, want + 0.5, 8e-3, "tensor-core linear, accumulate in bfloat16")
-    assert int(status.status.item()) == 0 and int(status.tickets.abs().sum()) == 0
+    assert int(status.status.item()) == 0
 
 
 @pytest.mark.parametrize("m,inter,k", [(1, 8, 64), (7, 136, 80), (64, 12288, 512), (100, 1000, 264), (300, 320, 128),
