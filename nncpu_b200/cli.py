@@ -130,7 +130,7 @@ usage: {argv0} -m DIR --tokens "ID ID ..."   continue the token ids and exit
        {argv0} -m DIR -p TEXT                answer one message and exit (needs tokenizer.json in DIR)
 
 model:
-  -m, --model DIR          a folder with config.json and model.safetensors
+  -m, --model DIR          a folder with config.json and model.safetensors (or its index and files)
   --bf16                   run in bfloat16 (default)
   --fp32                   run everything in true 32-bit (slow; shows what bfloat16 hides)
   --dtype NAME             bfloat16 or float32
@@ -237,19 +237,23 @@ def run_gen(o: Options, out=sys.stdout) -> int:
 def run_info(o: Options, out=sys.stdout) -> int:
     from .config import load_config
     from .engine.model import parameter_list
-    from .weights import SafetensorsFile, check_tensors
+    from .weights import check_tensors, open_checkpoint
     cfg = load_config(o.args[0])
     params = parameter_list(cfg.model_spec())
-    f = SafetensorsFile(Path(o.args[0]) / "model.safetensors")
-    check_tensors({n: f.shape(n) for n in f.names()}, params, str(f.path))
+    files, where, label = open_checkpoint(o.args[0])
+    try:
+        check_tensors({n: files[name].shape(n) for n, name in where.items()}, params, label)
+    finally:
+        for f in files.values():
+            f.close()
     n = 0
     for p in params:
-        if p.name in f.entries:
+        if p.name in where:
             c = 1
             for s in p.shape:
                 c *= s
             n += c
-    out.write(json.dumps({"config": cfg.to_dict(), "tensors": len(f.entries), "parameters": n}, indent=2) + "\n")
+    out.write(json.dumps({"config": cfg.to_dict(), "tensors": len(where), "parameters": n}, indent=2) + "\n")
     return 0
 
 

@@ -83,8 +83,9 @@ class Model:
     @classmethod
     def load(cls, folder, dtype="bfloat16", device="cuda:0", progress=None) -> "Model":
         """Reads ``folder/config.json``, picks the architecture's configuration
-        class from the registry, checks ``folder/model.safetensors`` against
-        what the parts ask for, and moves the weights to ``device``."""
+        class from the registry, checks the folder's safetensors file (or the
+        files of its index) against what the parts ask for, and moves the
+        weights to ``device``."""
         config = load_config(folder)
         dt = resolve_dtype(dtype)
         rt = Runtime(device, dt)

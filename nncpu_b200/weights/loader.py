@@ -12,9 +12,14 @@ Element types: with ``dtype=torch.bfloat16`` a tensor stored as BF16 stays
 BF16, one stored in 32-bit floats stays in 32-bit floats, F16 becomes BF16,
 and integer tables become int32.  With ``dtype=torch.float32`` every floating
 tensor is widened to float32 (exact for BF16 and F16).
+
+A folder holds either ``model.safetensors`` or, for a checkpoint cut into
+several files, ``model.safetensors.index.json`` whose ``weight_map`` names the
+file of every tensor; the files are checked as one set of tensors.
 """
 from __future__ import annotations
 
+import json
 from pathlib import Path
 from typing import Dict, Iterable, Optional
 
@@ -56,18 +61,58 @@ def convert(t: torch.Tensor, st_dtype: str, dtype: torch.dtype) -> torch.Tensor:
     return t.to(torch.int32)
 
 
+INDEX_NAME = "model.safetensors.index.json"
+
+
+def open_checkpoint(folder):
+    """The files of the checkpoint in ``folder`` and, for every tensor, the
+    file that holds it: ({file name: SafetensorsFile}, {tensor: file name},
+    what to call the checkpoint in messages)."""
+    folder = Path(folder)
+    single, index = folder / "model.safetensors", folder / INDEX_NAME
+    if single.exists() or not index.exists():
+        f = SafetensorsFile(single)          # a missing file is reported by name
+        return {single.name: f}, {n: single.name for n in f.names()}, str(single)
+    try:
+        weight_map = json.loads(index.read_text())["weight_map"]
+        if not isinstance(weight_map, dict) or not all(isinstance(v, str) for v in weight_map.values()):
+            raise TypeError
+    except (json.JSONDecodeError, UnicodeDecodeError, KeyError, TypeError):
+        raise BadFormat(f"{index}: no weight_map of tensor names to file names") from None
+    files: Dict[str, SafetensorsFile] = {}
+    try:
+        for name in sorted(set(weight_map.values())):
+            if Path(name).name != name:
+                raise BadFormat(f"{index}: file name {name!r} points outside the folder")
+            files[name] = SafetensorsFile(folder / name)
+        absent = sorted(t for t, name in weight_map.items() if t not in files[name].entries)
+        if absent:
+            raise BadFormat(f"{index} names tensors that their files do not hold: "
+                            + ", ".join(f"{t} ({weight_map[t]})" for t in absent))
+        # a tensor that a file holds but the index does not name is still part of the checkpoint
+        where = dict(weight_map)
+        for name, f in files.items():
+            for t in f.names():
+                where.setdefault(t, name)
+    except Exception:
+        for f in files.values():
+            f.close()
+        raise
+    return files, where, f"{index} ({len(files)} files)"
+
+
 def load_tensors(folder, params: Iterable[ParamSpec], dtype: torch.dtype, device,
                  progress=None) -> Dict[str, torch.Tensor]:
-    """Checks ``folder/model.safetensors`` against ``params`` and returns the
+    """Checks the checkpoint in ``folder`` against ``params`` and returns the
     tensors on ``device``.  ``progress(done, total)`` may return False to stop."""
     params = list(params)
-    path = Path(folder) / "model.safetensors"
-    f = SafetensorsFile(path)
+    files, where, label = open_checkpoint(folder)
     try:
-        check_tensors({n: f.shape(n) for n in f.names()}, params, str(path))
+        check_tensors({n: files[name].shape(n) for n, name in where.items()}, params, label)
         out: Dict[str, torch.Tensor] = {}
-        present = [p for p in params if p.name in f.entries]
+        present = [p for p in params if p.name in where]
         for i, p in enumerate(present):
+            f = files[where[p.name]]
             t = convert(f.tensor(p.name), f.dtype(p.name), dtype)
             out[p.name] = t.to(device, copy=True) if torch.device(device).type == "cpu" else t.to(device)
             if progress is not None and progress(i + 1, len(present)) is False:
@@ -75,4 +120,5 @@ def load_tensors(folder, params: Iterable[ParamSpec], dtype: torch.dtype, device
                 raise Cancelled("loading was cancelled")
         return out
     finally:
-        f.close()
+        for f in files.values():
+            f.close()

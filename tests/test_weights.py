@@ -150,3 +150,53 @@ def test_load_can_be_cancelled(tmp_path):
         load_tensors(folder, parameter_list(tiny_config("A").model_spec()), torch.float32, "cpu",
                      progress=lambda done, total: seen.append((done, total)) or len(seen) < 3)
     assert len(seen) == 3
+
+
+def _split_folder(tmp_path, name):
+    """A written model folder cut into two files with an index, the way large checkpoints are published."""
+    cfg = tiny_config(name)
+    folder = write_model_folder(tmp_path / name, cfg, seed=2)
+    params = parameter_list(cfg.model_spec())
+    whole = load_tensors(folder, params, torch.bfloat16, "cpu")
+    f = SafetensorsFile(folder / "model.safetensors")
+    stored = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    (folder / "model.safetensors").unlink()
+    names = sorted(stored)
+    parts = {"model-00001-of-00002.safetensors": names[::2], "model-00002-of-00002.safetensors": names[1::2]}
+    for file_name, members in parts.items():
+        write_safetensors(folder / file_name, {n: stored[n] for n in members})
+    index = {"metadata": {}, "weight_map": {n: file_name for file_name, members in parts.items() for n in members}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    return folder, params, whole, index
+
+
+def test_checkpoint_in_several_files_loads_like_one(tmp_path):
+    folder, params, whole, _ = _split_folder(tmp_path, "B")
+    t = load_tensors(folder, params, torch.bfloat16, "cpu")
+    assert set(t) == set(whole) and all(torch.equal(t[n], whole[n]) for n in whole)
+
+
+def test_checkpoint_in_several_files_reports_everything_at_once(tmp_path):
+    folder, params, _, index = _split_folder(tmp_path, "A")
+    # one error over the union of the files: a tensor of another model's shape set
+    with pytest.raises(BadFormat) as e:
+        load_tensors(folder, parameter_list(tiny_config("B").model_spec()), torch.float32, "cpu")
+    assert "index.json" in str(e.value) and "wrong shape" in str(e.value)
+    # the index names a tensor that its file does not hold
+    broken = dict(index, weight_map=dict(index["weight_map"], **{"model.ghost.weight": "model-00001-of-00002.safetensors"}))
+    (folder / "model.safetensors.index.json").write_text(json.dumps(broken))
+    with pytest.raises(BadFormat, match="model.ghost.weight"):
+        load_tensors(folder, params, torch.float32, "cpu")
+    # a file of the index is missing
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    (folder / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(BadFormat, match="model-00002-of-00002.safetensors does not exist"):
+        load_tensors(folder, params, torch.float32, "cpu")
+    # an index without a weight_map, or one that leaves the folder
+    (folder / "model.safetensors.index.json").write_text("{}")
+    with pytest.raises(BadFormat, match="weight_map"):
+        load_tensors(folder, params, torch.float32, "cpu")
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "../x.safetensors"}}))
+    with pytest.raises(BadFormat, match="outside the folder"):
+        load_tensors(folder, params, torch.float32, "cpu")
