@@ -305,7 +305,12 @@ def argmax(logits, out) -> None:
     """out[r] = the first largest of logits[r]; logits float32 [n, vocab], out int32 [n]."""
     n, vocab = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() >= n
-    _call("generic", "nncpu_argmax", _ptr(logits), _ptr(out), _i(n), _i(vocab), _stream())
+    lib = library.load("generic")
+    lib.nncpu_argmax_scratch_bytes.restype = ctypes.c_long
+    need = lib.nncpu_argmax_scratch_bytes(_i(n), _i(vocab))      # long rows are searched in chunks
+    scratch = torch.empty(need, dtype=torch.uint8, device=logits.device) if need else None
+    _call("generic", "nncpu_argmax", _ptr(logits), _ptr(out), _i(n), _i(vocab), _ptr(scratch), ctypes.c_long(need),
+          _stream())
 
 
 def topk(logits, vals, ids) -> None:

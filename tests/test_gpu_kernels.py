@@ -626,13 +626,14 @@ def test_gather_rows(ops):
 
 
 def test_argmax_first_largest(ops):
-    for vocab in (1, 31, 307, 151936):
+    for vocab in (1, 31, 307, 8191, 8192, 10007, 151936):      # from 8192 on the row is searched in chunks
         logits = torch.randn(5, vocab)
         if vocab > 30:
             logits[1, 17] = logits[1, 5] = 50.0          # a tie: the lower id
             logits[2, :] = float("nan")
             logits[2, 9] = -3.0                          # NaN never wins
             logits[3, vocab - 1] = 60.0
+            logits[4, :] = float("-inf")                  # nothing to choose from: the first id
         out = torch.empty(5, dtype=torch.int32, device=DEV)
         ops.argmax(logits.to(DEV), out)
         want = [P.argmax_first(np.where(np.isnan(r), -np.inf, r)) for r in logits.numpy()]
