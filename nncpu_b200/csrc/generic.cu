@@ -844,6 +844,126 @@ topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int*
 }
 
 // ---------------------------------------------------------------------------
+// The same candidates for long rows, found by the whole GPU instead of one block per row: a block per
+// (chunk, row) for each of the three passes of the quick way (largest logit; counts in 1024 bins within 16 of
+// it; gather down to the bin of the k-th), a small kernel between the last two that finds that bin, and the
+// chain's kernel then sorts what was gathered.  Per row the scratch holds: the chunks' largest logits, the
+// bins, three numbers (the cut bin or -1, how many logits lie down to it, how many were gathered) and 1024 keys.
+// ---------------------------------------------------------------------------
+constexpr int kPickChunks = 32;
+constexpr int kPickBins = 1024;
+constexpr float kPickRange = 16.0f, kPickPerUnit = kPickBins / kPickRange;
+
+struct PickScratch {
+    float chunk_max[kPickChunks];
+    int bins[kPickBins];
+    int cut, n_in, n_got, pad;
+    unsigned long long key[1024];
+};
+
+__device__ __forceinline__ void chunk_span(int vocab, int& begin, int& end) {
+    const int len = (vocab + kPickChunks - 1) / kPickChunks;
+    begin = blockIdx.x * len;
+    end = min(vocab, begin + len);
+}
+
+__global__ void __launch_bounds__(256)
+pick_max_kernel(const float* __restrict__ logits, PickScratch* __restrict__ scratch, int vocab) {
+    __shared__ float red[33];
+    PickScratch& sc = scratch[blockIdx.y];
+    int begin, end;
+    chunk_span(vocab, begin, end);
+    const float* row = logits + (size_t)blockIdx.y * vocab;
+    float mx = -INFINITY;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        if (v == v) mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, red);
+    if (threadIdx.x == 0) sc.chunk_max[blockIdx.x] = mx;
+    // this block's share of the row's bins and numbers starts at zero
+    for (int i = threadIdx.x; i < kPickBins / kPickChunks; i += blockDim.x) sc.bins[blockIdx.x * (kPickBins / kPickChunks) + i] = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) sc.cut = sc.n_in = sc.n_got = 0;
+}
+
+__device__ __forceinline__ float row_max_of_chunks(const PickScratch& sc) {
+    float mx = -INFINITY;
+#pragma unroll 8
+    for (int c = 0; c < kPickChunks; ++c) mx = fmaxf(mx, sc.chunk_max[c]);
+    return mx;
+}
+
+__global__ void __launch_bounds__(256)
+pick_count_kernel(const float* __restrict__ logits, PickScratch* __restrict__ scratch, int vocab) {
+    __shared__ int fine[kPickBins];
+    PickScratch& sc = scratch[blockIdx.y];
+    const float mx = row_max_of_chunks(sc);
+    if (!(mx > -INFINITY) || mx == INFINITY) return;
+    int begin, end;
+    chunk_span(vocab, begin, end);
+    const float* row = logits + (size_t)blockIdx.y * vocab;
+    for (int i = threadIdx.x; i < kPickBins; i += blockDim.x) fine[i] = 0;
+    __syncthreads();
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float d = mx - row[i];
+        if (d < kPickRange) atomicAdd(&fine[(int)(d * kPickPerUnit)], 1);   // false for NaN
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kPickBins; i += blockDim.x)
+        if (fine[i]) atomicAdd(&sc.bins[i], fine[i]);
+}
+
+// One block of 1024 threads per row: the bin that holds the k-th logit from the top, by a prefix sum over the bins.
+__global__ void __launch_bounds__(kPickBins)
+pick_cut_kernel(PickScratch* __restrict__ scratch, int k) {
+    __shared__ int warp_total[32];
+    PickScratch& sc = scratch[blockIdx.x];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int mine = sc.bins[tid];
+    int run = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, run, o);
+        if (lane >= o) run += t;
+    }
+    if (lane == 31) warp_total[warp] = run;
+    __syncthreads();
+    if (warp == 0) {
+        int t = warp_total[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, t, o);
+            if (lane >= o) t += v;
+        }
+        warp_total[lane] = t;
+    }
+    __syncthreads();
+    run += warp > 0 ? warp_total[warp - 1] : 0;     // logits in bins 0 .. tid
+    // the first bin whose running count reaches k; none, or too many to gather: -1 (the chain's kernel selects by radix)
+    if (run >= k && run - mine < k) {
+        sc.cut = run <= 1024 ? tid : -1;
+        sc.n_in = run;
+    }
+    if (tid == kPickBins - 1 && run < k) sc.cut = -1;
+}
+
+__global__ void __launch_bounds__(256)
+pick_gather_kernel(const float* __restrict__ logits, PickScratch* __restrict__ scratch, int vocab) {
+    PickScratch& sc = scratch[blockIdx.y];
+    const int cut = sc.cut;
+    const float mx = row_max_of_chunks(sc);
+    if (cut < 0 || !(mx > -INFINITY) || mx == INFINITY) return;
+    int begin, end;
+    chunk_span(vocab, begin, end);
+    const float* row = logits + (size_t)blockIdx.y * vocab;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        const float d = mx - v;
+        if (d < kPickRange && (int)(d * kPickPerUnit) <= cut) sc.key[atomicAdd(&sc.n_got, 1)] = rank_key(v, i);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // The whole sampling chain of one row on the device, for 0 < top-k <= 1024: the k candidates, their ranking
 // (higher logit first, then lower id), top-p and min-p on the distribution at temperature 1, temperature over
 // the survivors and the draw in rank order from u[row], uniform in [0, 1)
@@ -852,13 +972,30 @@ topk_kernel(const float* __restrict__ logits, float* __restrict__ out_vals, int*
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 sample_chain_kernel(const float* __restrict__ logits, const double* __restrict__ u, int* __restrict__ out, int vocab,
-                    int k, float temperature, float top_p, float min_p) {
+                    int k, float temperature, float top_p, float min_p, const PickScratch* __restrict__ picked) {
     __shared__ float c_val[1024];
     __shared__ int c_id[1024];
     __shared__ unsigned long long key[1024];
     const int tid = threadIdx.x;
     bool sorted;
-    select_topk(logits + (size_t)blockIdx.x * vocab, vocab, k, c_val, c_id, key, &sorted);
+    if (picked != nullptr && picked[blockIdx.x].cut >= 0) {
+        // the candidates were gathered by the kernels before this one: sort them, the k best come first
+        const PickScratch& sc = picked[blockIdx.x];
+        const int n = sc.n_in;
+        int n2 = 1;
+        while (n2 < n) n2 <<= 1;
+        if (tid < n2) key[tid] = tid < n ? sc.key[tid] : ~0ull;
+        __syncthreads();
+        sort_keys(key, n2);
+        if (tid < k) {
+            c_val[tid] = key_value(key[tid]);
+            c_id[tid] = (int)(uint32_t)key[tid];
+        }
+        __syncthreads();
+        sorted = true;
+    } else {
+        select_topk(logits + (size_t)blockIdx.x * vocab, vocab, k, c_val, c_id, key, &sorted);
+    }
     if (!sorted) {
         // ascending by (descending logit, ascending id); the padding sorts last
         int n2 = 1;
@@ -907,15 +1044,37 @@ sample_chain_kernel(const float* __restrict__ logits, const double* __restrict__
     out[blockIdx.x] = chosen;
 }
 
+// Bytes of scratch with which nncpu_sample_chain finds the candidates of long rows by the whole GPU (0: rows
+// are short, one block per row does it all).
+extern "C" long nncpu_sample_chain_scratch_bytes(int n_rows, int vocab) {
+    return vocab >= 8192 ? (long)n_rows * (long)sizeof(PickScratch) : 0;
+}
+
 extern "C" int nncpu_sample_chain(const float* logits, const double* u, int* out, int n_rows, int vocab, int top_k,
-                                  float temperature, float top_p, float min_p, void* stream) {
+                                  float temperature, float top_p, float min_p, void* scratch, long scratch_bytes,
+                                  void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(n_rows >= 0 && vocab > 0, "sample_chain: %d rows of %d", n_rows, vocab);
     NN_CHECK(top_k > 0 && top_k <= 1024 && top_k <= vocab, "sample_chain: top-k %d is outside 1..min(1024, %d)", top_k, vocab);
     NN_CHECK(temperature > 0.0f && temperature < INFINITY, "sample_chain: temperature %g", (double)temperature);
     NN_CHECK(top_p >= 0.0f && top_p <= 1.0f && min_p >= 0.0f && min_p <= 1.0f, "sample_chain: top-p %g, min-p %g",
              (double)top_p, (double)min_p);
     if (n_rows == 0) return 0;
-    sample_chain_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, u, out, vocab, top_k, temperature, top_p, min_p);
+    PickScratch* picked = nullptr;
+    const long need = nncpu_sample_chain_scratch_bytes(n_rows, vocab);
+    if (need > 0 && scratch != nullptr && scratch_bytes >= need && ((uintptr_t)scratch % 8) == 0) {
+        picked = (PickScratch*)scratch;
+        const dim3 grid(kPickChunks, n_rows);
+        pick_max_kernel<<<grid, 256, 0, stream>>>(logits, picked, vocab);
+        NN_LAUNCH_OK("sample_chain (largest)");
+        pick_count_kernel<<<grid, 256, 0, stream>>>(logits, picked, vocab);
+        NN_LAUNCH_OK("sample_chain (count)");
+        pick_cut_kernel<<<n_rows, kPickBins, 0, stream>>>(picked, top_k);
+        NN_LAUNCH_OK("sample_chain (cut)");
+        pick_gather_kernel<<<grid, 256, 0, stream>>>(logits, picked, vocab);
+        NN_LAUNCH_OK("sample_chain (gather)");
+    }
+    sample_chain_kernel<<<n_rows, 1024, 0, stream>>>(logits, u, out, vocab, top_k, temperature, top_p, min_p, picked);
     NN_LAUNCH_OK("sample_chain");
     return 0;
 }

@@ -329,8 +329,12 @@ def sample_chain(logits, u, out, top_k: int, temperature: float, top_p: float, m
     n, vocab = logits.shape
     assert logits.dtype == torch.float32 and u.dtype == torch.float64 and out.dtype == torch.int32
     assert u.numel() >= n and out.numel() >= n
+    lib = library.load("generic")
+    lib.nncpu_sample_chain_scratch_bytes.restype = ctypes.c_long
+    need = lib.nncpu_sample_chain_scratch_bytes(_i(n), _i(vocab))   # long rows: candidates found by the whole GPU
+    scratch = torch.empty(need, dtype=torch.uint8, device=logits.device) if need else None
     _call("generic", "nncpu_sample_chain", _ptr(logits), _ptr(u), _ptr(out), _i(n), _i(vocab), _i(top_k),
-          _f(temperature), _f(top_p), _f(min_p), _stream())
+          _f(temperature), _f(top_p), _f(min_p), _ptr(scratch), ctypes.c_long(need), _stream())
 
 
 def row_exp_sum(logits, out) -> None:
