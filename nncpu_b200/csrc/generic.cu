@@ -1194,12 +1194,131 @@ __global__ void sample_kernel(const float* __restrict__ logits, const double* __
     }
 }
 
+// The same draw for long rows in three kernels: the chunks' largest logits (pick_max_kernel), the chunks' sums
+// of weights, and a block per row that finds the chunk in which the running sum reaches r and walks that chunk
+// alone.  Per row the scratch is a PickScratch; the chunk sums lie where its keys would.
+__global__ void __launch_bounds__(256)
+sample_chunk_sum_kernel(const float* __restrict__ logits, PickScratch* __restrict__ scratch, int vocab, float inv_temp) {
+    __shared__ double red[8];
+    PickScratch& sc = scratch[blockIdx.y];
+    const float mx = row_max_of_chunks(sc);
+    int begin, end;
+    chunk_span(vocab, begin, end);
+    const float* row = logits + (size_t)blockIdx.y * vocab;
+    double s = 0.0;
+    if (mx > -INFINITY && mx != INFINITY) {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+            const float v = row[i];
+            if (v == v) s += exp((double)(v - mx) * (double)inv_temp);
+        }
+    }
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+        reinterpret_cast<double*>(sc.key)[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+sample_chunk_draw_kernel(const float* __restrict__ logits, const double* __restrict__ u, int* __restrict__ out,
+                         const PickScratch* __restrict__ scratch, int vocab, float inv_temp) {
+    __shared__ double part[256];
+    const PickScratch& sc = scratch[blockIdx.x];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const float mx = row_max_of_chunks(sc);
+    if (!(mx > -INFINITY) || mx == INFINITY) {  // nothing finite to draw from: the first largest
+        if (tid == 0) {
+            int best = 0;
+            for (int i = 1; i < vocab; ++i) if (row[i] > row[best] || (row[best] != row[best] && row[i] == row[i])) best = i;
+            out[blockIdx.x] = best;
+        }
+        return;
+    }
+    // the chunk in which the running sum, in id order, reaches r; the last chunk with weight if rounding ran past the end
+    const double* chunk_sum = reinterpret_cast<const double*>(sc.key);
+    double total = 0.0;
+    for (int c = 0; c < kPickChunks; ++c) total += chunk_sum[c];
+    double r = u[blockIdx.x] * total;
+    int chunk = -1, last_chunk = -1;
+    for (int c = 0; c < kPickChunks; ++c) {
+        if (chunk_sum[c] > 0.0) last_chunk = c;
+        if (r - chunk_sum[c] <= 0.0 && chunk_sum[c] > 0.0) { chunk = c; break; }
+        r -= chunk_sum[c];
+    }
+    if (chunk < 0) {      // past the end: the last id with weight
+        chunk = last_chunk;
+        r = INFINITY;
+    }
+    if (chunk < 0) {      // no weight anywhere (cannot be: the largest logit has weight 1)
+        if (tid == 0) out[blockIdx.x] = 0;
+        return;
+    }
+    const int len = (vocab + kPickChunks - 1) / kPickChunks;
+    const int begin = chunk * len, end = min(vocab, begin + len);
+    // thread `tid` owns the contiguous ids [lo, hi) of the chunk
+    const int per = (end - begin + nt - 1) / nt;
+    const int lo = min(end, begin + tid * per), hi = min(end, lo + per);
+    double s = 0.0;
+    for (int i = lo; i < hi; ++i) {
+        const float v = row[i];
+        if (v == v) s += exp((double)(v - mx) * (double)inv_temp);
+    }
+    part[tid] = s;
+    __syncthreads();
+    if (tid != 0) return;
+    int owner = -1, last_owner = -1;
+    for (int i = 0; i < nt; ++i) {
+        if (part[i] > 0.0) last_owner = i;
+        if (r - part[i] <= 0.0 && part[i] > 0.0) { owner = i; break; }
+        r -= part[i];
+    }
+    if (owner < 0) {
+        owner = last_owner;
+        r = INFINITY;
+    }
+    int pick = -1, last = -1;
+    if (owner >= 0) {
+        const int olo = min(end, begin + owner * per), ohi = min(end, olo + per);
+        for (int i = olo; i < ohi; ++i) {
+            const float v = row[i];
+            if (!(v == v)) continue;
+            const double w = exp((double)(v - mx) * (double)inv_temp);
+            if (w > 0.0) last = i;
+            r -= w;
+            if (r <= 0.0 && w > 0.0) { pick = i; break; }
+        }
+    }
+    if (pick < 0) pick = last;
+    out[blockIdx.x] = pick < 0 ? 0 : pick;
+}
+
+extern "C" long nncpu_sample_temperature_scratch_bytes(int n_rows, int vocab) {
+    return vocab >= 8192 ? (long)n_rows * (long)sizeof(PickScratch) : 0;
+}
+
 extern "C" int nncpu_sample_temperature(const float* logits, const double* u, int* out, int n_rows, int vocab,
-                                        float temperature, void* stream) {
+                                        float temperature, void* scratch, long scratch_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(n_rows >= 0 && vocab > 0, "sample: %d rows of %d", n_rows, vocab);
     NN_CHECK(temperature > 0.0f && isfinite(temperature), "sample: temperature %g must be positive", temperature);
     if (n_rows == 0) return 0;
-    sample_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, u, out, vocab, 1.0f / temperature);
+    const long need = nncpu_sample_temperature_scratch_bytes(n_rows, vocab);
+    if (need > 0 && scratch != nullptr && scratch_bytes >= need && ((uintptr_t)scratch % 8) == 0) {
+        PickScratch* sc = (PickScratch*)scratch;
+        const dim3 grid(kPickChunks, n_rows);
+        pick_max_kernel<<<grid, 256, 0, stream>>>(logits, sc, vocab);
+        NN_LAUNCH_OK("sample (largest)");
+        sample_chunk_sum_kernel<<<grid, 256, 0, stream>>>(logits, sc, vocab, 1.0f / temperature);
+        NN_LAUNCH_OK("sample (sums)");
+        sample_chunk_draw_kernel<<<n_rows, 256, 0, stream>>>(logits, u, out, sc, vocab, 1.0f / temperature);
+        NN_LAUNCH_OK("sample (draw)");
+        return 0;
+    }
+    sample_kernel<<<n_rows, 1024, 0, stream>>>(logits, u, out, vocab, 1.0f / temperature);
     NN_LAUNCH_OK("sample");
     return 0;
 }

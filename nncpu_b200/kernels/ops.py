@@ -349,5 +349,9 @@ def sample_temperature(logits, uniforms, out, temperature: float) -> None:
     order; uniforms float64 [n] in [0, 1)."""
     n, vocab = logits.shape
     assert logits.dtype == torch.float32 and uniforms.dtype == torch.float64 and out.dtype == torch.int32
+    lib = library.load("generic")
+    lib.nncpu_sample_temperature_scratch_bytes.restype = ctypes.c_long
+    need = lib.nncpu_sample_temperature_scratch_bytes(_i(n), _i(vocab))   # long rows are summed in chunks
+    scratch = torch.empty(need, dtype=torch.uint8, device=logits.device) if need else None
     _call("generic", "nncpu_sample_temperature", _ptr(logits), _ptr(uniforms), _ptr(out), _i(n), _i(vocab),
-          _f(temperature), _stream())
+          _f(temperature), _ptr(scratch), ctypes.c_long(need), _stream())

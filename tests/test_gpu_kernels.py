@@ -670,9 +670,14 @@ def plain_temperature_draw(row, u, temperature):
 
 def test_sample_temperature(ops):
     rs = np.random.RandomState(0)
-    for vocab, temp in ((5, 1.0), (307, 0.8), (5000, 1.5), (151936, 0.7)):
-        logits = (rs.randn(6, vocab) * 2).astype(np.float32)
+    for vocab, temp in ((5, 1.0), (307, 0.8), (5000, 1.5), (8192, 0.5), (20011, 1.2), (151936, 0.7)):
+        logits = (rs.randn(6, vocab) * 2).astype(np.float32)     # from 8192 on the row is summed in chunks
         logits[1, 3 % vocab] = np.nan
+        if vocab > 5000:
+            logits[2, :vocab // 2] = -np.inf                     # whole chunks without weight
+            logits[3, vocab // 3:] = np.nan
+            logits[4, :] = -np.inf
+            logits[4, vocab - 7] = 0.5                           # one id to draw
         u = rs.rand(6)
         u[0], u[5] = 0.0, 1.0 - 1e-16
         out = torch.empty(6, dtype=torch.int32, device=DEV)
