@@ -9,6 +9,7 @@ loop, sampling, and hand-written sm_100a kernels underneath.
 from .errors import (BadFormat, Cancelled, ContextFull, ExtensionError, InvalidArgument, NncpuError, OutOfMemory,
                      UnsupportedModel)
 from .engine import Engine, Model
+from .perf import perf_enable, perf_report, perf_reset, perf_totals
 from .sampling import GenerateParams, GenerateResult, SamplerParams, StopReason
 from .session import CancelHandle, Piece, Session, SessionParams
 
@@ -16,4 +17,5 @@ __version__ = "0.1.0"
 
 __all__ = ["BadFormat", "Cancelled", "ContextFull", "ExtensionError", "InvalidArgument", "NncpuError",
            "OutOfMemory", "UnsupportedModel", "Engine", "Model", "GenerateParams", "GenerateResult", "SamplerParams",
-           "StopReason", "CancelHandle", "Piece", "Session", "SessionParams", "__version__"]
+           "StopReason", "CancelHandle", "Piece", "Session", "SessionParams", "perf_enable", "perf_report", "perf_reset",
+           "perf_totals", "__version__"]

@@ -10,8 +10,10 @@ pages, and fixed-size state per sequence.
   every key and a group that needs only a window of them do not share a
   shape or a lifetime: a windowed group gives pages back as soon as no later
   query can see them.  An entry that reads another entry's cache owns nothing.
-* **State** is a tensor ``[n_slots, *shape]`` per entry that asks for one; a
-  sequence that starts (length 0) starts with zeros.
+* **State** is a tensor ``[n_slots + 1, *shape]`` per entry that asks for one; a
+  sequence that starts (length 0) starts with zeros.  The last row belongs to
+  no sequence: the padding rows of a captured decode step carry slot -1, which
+  indexes it, so a part may read and write "its" state for them unconditionally.
 
 The reference keeps one sequence per cache (crates/nncpu/src/model/kv.rs:133-180):
 per-layer buffers, ring buffers for sliding layers
@@ -27,7 +29,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..errors import ContextFull, InvalidArgument
+from ..errors import ContextFull, InvalidArgument, translating_oom
 from .slots import IndexPool
 
 PAGE = 64  # tokens per page; also the unit in which a request's tokens are counted
@@ -134,18 +136,23 @@ class Cache:
                                           "which is not an earlier entry with keys and values of its own")
             elif kv is not None:
                 by_request.setdefault(kv, []).append(i)
+        esize = torch.empty((), dtype=dtype).element_size()
+        need = sum(2 * len(e) * self.n_pages * kv.n_kv_heads * PAGE * kv.head_dim * esize for kv, e in by_request.items())
         for kv, entries in by_request.items():
             g = len(self.groups)
-            self.groups.append(KVGroup(kv, entries, self.n_pages, dtype, self.device))
+            with translating_oom(f"a cache of {self.max_tokens} tokens ({need / 2 ** 30:.2f} GiB of keys and values "
+                                 f"for {sum(len(e) for e in by_request.values())} layer runs)"):
+                self.groups.append(KVGroup(kv, entries, self.n_pages, dtype, self.device))
             for k, e in enumerate(entries):
                 self._entry_group[e] = (g, k)
                 self._owns[e] = True
         for i, j in enumerate(cache_of):
             if j is not None:
                 self._entry_group[i] = self._entry_group[j]
-        self.states: List[Optional[torch.Tensor]] = [
-            None if st is None else torch.zeros((self.n_slots, *st.shape), dtype=st.dtype, device=self.device)
-            for _, st in requests]
+        with translating_oom(f"per-sequence state for {self.n_slots} sequence slots"):
+            self.states: List[Optional[torch.Tensor]] = [
+                None if st is None else torch.zeros((self.n_slots + 1, *st.shape), dtype=st.dtype, device=self.device)
+                for _, st in requests]
 
     # -- slots ---------------------------------------------------------------
 
@@ -208,11 +215,24 @@ class Cache:
         for g in self.groups:
             for s, n in zip(slots, n_new):
                 g.grow(s, self.lengths[s] + n)
-        starting = [s for s in slots if self.lengths[s] == 0]
-        if starting:
-            for st in self.states:
-                if st is not None:
-                    st[torch.tensor(starting, device=st.device)] = 0
+        for st in self.states:
+            if st is not None:
+                for s in slots:
+                    if self.lengths[s] == 0:
+                        st[s].zero_()       # a fill kernel in stream order: no host tensor, no wait
+
+    def rollback(self, slots: Sequence[int]) -> None:
+        """Undoes a ``prepare`` whose step did not happen: the pages taken beyond what each sequence's length
+        needs go back to their pools."""
+        for g in self.groups:
+            for s in slots:
+                table = g.tables.get(s)
+                while table is not None and len(table) > pages_for(self.lengths[s]):
+                    p = table.pop()
+                    if p >= 0:
+                        g.pool.give_back(p)
+                if table is not None and not table:
+                    del g.tables[s]
 
     def commit(self, slots: Sequence[int], n_new: Sequence[int]) -> None:
         """The step's launches are enqueued: lengths advance, and windowed

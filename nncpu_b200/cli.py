@@ -4,7 +4,8 @@ its token-level harness (crates/nncpu-cli/src/devtools.rs:70-90,632-705) as
 ``--gen``.
 
     nncpu-b200 -m DIR --tokens "1 2 3" -n 32            generate from token ids
-    nncpu-b200 -m DIR -p TEXT                           generate from text (needs tokenizer.json)
+    nncpu-b200 -m DIR -p TEXT                           answer one message (needs tokenizer.json), streamed
+    nncpu-b200 chat -m DIR                              chat: a message per line, /reset /exit /help
     nncpu-b200 --gen DIR "ID ID ..." [N] [CTX]          greedy token-level run with timings
     nncpu-b200 --info DIR                               what the folder holds
     nncpu-b200 --random-weights CONFIG.json SEED OUT    write a model folder with random weights
@@ -12,6 +13,8 @@ its token-level harness (crates/nncpu-cli/src/devtools.rs:70-90,632-705) as
 from __future__ import annotations
 
 import json
+import os
+import signal
 import sys
 import time
 from dataclasses import dataclass, field
@@ -29,6 +32,7 @@ MODES = {"--help": (0, 0), "-h": (0, 0), "--version": (0, 0), "--gen": (2, 4), "
 VALUE_OPTIONS = {
     "-m": "model", "--model": "model",
     "-p": "prompt", "--prompt": "prompt",
+    "-sys": "system_prompt", "--system": "system_prompt",
     "--tokens": "tokens",
     "-n": "n_predict", "--n_predict": "n_predict", "--n-predict": "n_predict",
     "-c": "n_ctx", "--ctx-size": "n_ctx", "--ctx_size": "n_ctx",
@@ -50,6 +54,7 @@ class Options:
     args: List[str] = field(default_factory=list)
     model: str = ""
     prompt: str = ""
+    system_prompt: str = ""     # -sys: instructions for the model, given before the first message
     tokens: str = ""
     n_predict: int = 0          # -n: most tokens per reply; 0 = until a stop token or a full context
     n_ctx: int = 0              # -c: 0 = min(4096, the model's position range)
@@ -81,7 +86,9 @@ def parse_options(argv: List[str]) -> Options:
     i = 0
     while i < len(argv):
         a = argv[i]
-        if a in MODES:
+        if a == "chat" and i == 0:
+            o.mode = "chat"
+        elif a in MODES:
             lo, hi = MODES[a]
             o.mode = {"-h": "--help"}.get(a, a).lstrip("-")
             rest = []
@@ -128,6 +135,7 @@ def usage(argv0: str = "nncpu-b200") -> str:
 
 usage: {argv0} -m DIR --tokens "ID ID ..."   continue the token ids and exit
        {argv0} -m DIR -p TEXT                answer one message and exit (needs tokenizer.json in DIR)
+       {argv0} chat -m DIR                   chat: type a message per line (needs tokenizer.json in DIR)
 
 model:
   -m, --model DIR          a folder with config.json and model.safetensors (or its index and files)
@@ -138,7 +146,8 @@ model:
   --kv-f32                 keep the K/V cache in F32 (default: the run's element type)
 
 generation:
-  -p, --prompt TEXT        answer TEXT and exit; the reply goes to stdout
+  -p, --prompt TEXT        answer TEXT and exit; the reply goes to stdout as it is written
+  -sys, --system TEXT      instructions for the model, given before the first message
   --tokens "ID ID ..."     continue these token ids; the new ids go to stdout
   -n, --n_predict N        most tokens per reply (default: until the reply ends)
   -b, --batch N            generate N copies of the prompt together (default 1)
@@ -147,7 +156,7 @@ generation:
   --top-p X                ...that make up probability X (default 0.95)
   --min-p X                ...each at least X times the likeliest (default 0.05)
   -s, --seed N             random seed, for repeatable replies (default: random)
-  --perf                   print timings after the reply
+  --perf                   print a table of the time per phase after the reply
   -v, --verbose            show what the library is doing
 
 modes (each runs instead of generation):
@@ -167,55 +176,193 @@ def _token_list(text: str) -> List[int]:
         raise InvalidArgument(f"token ids must be integers: {text!r}") from None
 
 
-def _load_tokenizer(folder: str):
-    path = Path(folder) / "tokenizer.json"
-    if not path.exists():
-        raise InvalidArgument(f"-p needs {path}; pass token ids with --tokens instead")
-    try:
-        from tokenizers import Tokenizer
-    except ImportError:
-        raise InvalidArgument("-p needs the 'tokenizers' package; pass token ids with --tokens instead") from None
-    return Tokenizer.from_file(str(path))
+def _peaks() -> Optional[dict]:
+    """The device's measured peaks for the profiler's last column: the JSON file that $NNCPU_B200_PEAKS names,
+    or MEASURED_PEAKS.json in the working directory ({"hbm_gbs": ..., "bf16_tflops": ...})."""
+    for cand in (os.environ.get("NNCPU_B200_PEAKS"), "MEASURED_PEAKS.json"):
+        if cand and Path(cand).exists():
+            try:
+                d = json.loads(Path(cand).read_text())
+                return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}
+            except (ValueError, KeyError, TypeError):
+                return None
+    return None
+
+
+def _perf_begin(o: Options) -> None:
+    if o.perf:
+        from . import perf_enable, perf_reset
+        perf_enable(True)
+        perf_reset()
+
+
+def _perf_end(o: Options, title: str, n_tokens: int, err) -> None:
+    """The phase table after a reply (crates/nncpu-cli/src/chat.rs:232-235)."""
+    if o.perf:
+        from . import perf_report, perf_reset
+        err.write(perf_report(title, n_tokens, _peaks()))
+        perf_reset()
+
+
+def _stats_line(res, verbose: bool, n_predict: int) -> str:
+    """The line after a reply: tokens, speed, and why it stopped if that was not the model's own choice
+    (crates/nncpu-cli/src/chat.rs:170-231)."""
+    from .sampling import StopReason
+    note = {StopReason.MAX_TOKENS: f", cut at -n {n_predict}", StopReason.CANCELLED: ", stopped",
+            StopReason.CONTEXT_FULL: ", context full: the next message starts afresh"}.get(res.stop, "")
+    tps = res.n_generated / res.decode if res.decode > 0 else 0.0
+    if verbose:
+        return f"[{res.n_generated} tokens, {tps:.1f} tok/s; prompt {res.n_prompt} tokens in {res.prefill:.2f} s{note}]"
+    return f"[{res.n_generated} tokens, {tps:.1f} tok/s{note}]"
 
 
 def run_generate(o: Options, out=sys.stdout, err=sys.stderr) -> int:
     from . import Model, Session, SessionParams
+    from .text import load_tokenizer
     if not o.model:
         raise InvalidArgument("no model: pass -m DIR")
     if bool(o.prompt) == bool(o.tokens):
         raise InvalidArgument("pass exactly one of -p TEXT and --tokens \"ID ID ...\"")
-    tok = _load_tokenizer(o.model) if o.prompt else None
-    if tok is not None:
-        # one ChatML turn (crates/nncpu/src/session/chat.rs:340-383)
-        text = f"<|im_start|>user\n{o.prompt}<|im_end|>\n<|im_start|>assistant\n"
-        ids = tok.encode(text, add_special_tokens=False).ids
-    else:
-        ids = _token_list(o.tokens)
+    tok = load_tokenizer(o.model) if o.prompt else None
     t0 = time.perf_counter()
     model = Model.load(o.model, dtype=o.dtype)
     if o.verbose:
         print(f"loaded {model.info()} in {time.perf_counter() - t0:.2f} s", file=err)
-    session = Session(model, SessionParams(n_ctx=o.n_ctx, seed=o.seed, kv_f32=o.kv_f32, max_batch=o.batch))
-    pieces = []
-
-    def on_piece(p):
-        if p.index == 0:
-            if tok is None:
-                out.write(f"{p.token} ")
-            else:
-                pieces.append(p.token)
-            out.flush()
-        return True
-    res = session.generate([ids] * o.batch, GenerateParams(o.n_predict, o.sampler()), on_piece)
+    session = Session(model, SessionParams(n_ctx=o.n_ctx, seed=o.seed, kv_f32=o.kv_f32, max_batch=o.batch,
+                                           system_prompt=o.system_prompt), tokenizer=tok)
+    _perf_begin(o)
+    params = GenerateParams(o.n_predict, o.sampler())
     if tok is not None:
-        out.write(tok.decode(pieces))
+        # one chat turn on the session's own sequence, streamed in whole characters
+        def on_text(p):
+            out.write(p.text)
+            out.flush()
+            return True
+        r = session.chat(o.prompt, params, on_text)
+        res = [r]
+    else:
+        def on_piece(p):
+            if p.index == 0:
+                out.write(f"{p.token} ")
+                out.flush()
+            return True
+        res = session.generate([_token_list(o.tokens)] * o.batch, params, on_piece)
     out.write("\n")
+    out.flush()
     if o.perf or o.verbose:
         r = res[0]
         n = sum(x.n_generated for x in res)
         print(f"{r.n_prompt} prompt tokens in {r.prefill:.3f} s ({len(res) * r.n_prompt / max(r.prefill, 1e-9):.1f} tok/s), "
               f"{n} tokens in {r.decode:.3f} s ({n / max(r.decode, 1e-9):.1f} tok/s), stop: {r.stop.value}", file=err)
+    _perf_end(o, "reply", sum(x.n_prompt + x.n_generated for x in res), err)
     return 0
+
+
+CHAT_HELP = """Commands:
+  /reset            forget the conversation and start a new one
+  /exit             quit (so does the end of the input)
+  /help             this list
+Ctrl-C stops a reply that is being written.
+"""
+
+
+def parse_chat_line(line: str):
+    """What a line typed at the prompt asks for: (kind, text) with kind one of empty, exit, help, reset,
+    unknown, message (crates/nncpu-cli/src/chat.rs:253-293)."""
+    msg = line.strip(" \t\r\n")
+    if msg == "":
+        return "empty", ""
+    if msg in ("/exit", "/quit", "/bye"):
+        return "exit", ""
+    if msg in ("/help", "/?"):
+        return "help", ""
+    if msg in ("/reset", "/clear"):
+        return "reset", ""
+    if msg.startswith("/") and " " not in msg:
+        return "unknown", msg
+    return "message", msg
+
+
+def chat_loop(session, o: Options, lines, out=sys.stdout, err=sys.stderr, interactive: bool = False) -> int:
+    """The chat loop over ``lines`` (an iterable of input lines): commands, one turn per message on the
+    session's own sequence, whose cache stays between turns, a line of figures after every reply, Ctrl-C wired to
+    the session's cancel handle while a reply is written.  A conversation that has filled the context starts
+    afresh and the message is tried again (crates/nncpu-cli/src/chat.rs:138-166,302-484)."""
+    from .errors import ContextFull
+    params = GenerateParams(o.n_predict, o.sampler())
+    cancel = session.cancel_handle()
+
+    def turn(message):
+        def on_text(p):
+            out.write(p.text)
+            out.flush()
+            return True
+        old = None
+        try:
+            old = signal.signal(signal.SIGINT, lambda *_: cancel.cancel())
+        except ValueError:
+            pass                     # not the main thread: no Ctrl-C wiring
+        try:
+            try:
+                return session.chat(message, params, on_text)
+            except ContextFull:
+                if session.n_past() == 0 and not session.tokens():
+                    raise
+                print(f"(the conversation filled the {session.n_ctx}-token context, so it starts afresh)", file=err)
+                session.reset()
+                return session.chat(message, params, on_text)
+        finally:
+            if old is not None:
+                signal.signal(signal.SIGINT, old)
+
+    print("Type a message and press Enter. /help lists commands; Ctrl-C stops a reply.", file=err)
+    while True:
+        if interactive:
+            err.write("\n> ")
+            err.flush()
+        try:
+            line = next(lines)
+        except StopIteration:
+            break
+        kind, text = parse_chat_line(line)
+        if kind == "exit":
+            break
+        if kind == "help":
+            err.write(CHAT_HELP)
+        elif kind == "reset":
+            session.reset()
+            print("(new conversation)", file=err)
+        elif kind == "unknown":
+            print(f"Unknown command {text}; /help lists the commands.", file=err)
+        elif kind == "message":
+            try:
+                res = turn(text)
+            except NncpuError as e:
+                out.write("\n")
+                print(f"error ({e.kind}): {e}", file=err)
+                continue
+            out.write("\n")
+            out.flush()
+            print(_stats_line(res, o.verbose, o.n_predict), file=err)
+            _perf_end(o, "reply", res.n_prompt + res.n_generated, err)
+    return 0
+
+
+def run_chat(o: Options, stdin=None, out=sys.stdout, err=sys.stderr) -> int:
+    from . import Model, Session, SessionParams
+    from .text import load_tokenizer
+    if not o.model:
+        raise InvalidArgument("no model: pass -m DIR")
+    tok = load_tokenizer(o.model)
+    model = Model.load(o.model, dtype=o.dtype)
+    session = Session(model, SessionParams(n_ctx=o.n_ctx, seed=o.seed, kv_f32=o.kv_f32, max_batch=1,
+                                           system_prompt=o.system_prompt), tokenizer=tok)
+    info = model.info()
+    print(f"{o.model} ({info['architecture']}, {info['layers']} layers, {info['dtype']}) - "
+          f"{session.n_ctx}-token context", file=err)
+    _perf_begin(o)
+    stdin = stdin if stdin is not None else sys.stdin
+    return chat_loop(session, o, iter(stdin.readline, ""), out, err, interactive=stdin.isatty())
 
 
 def run_gen(o: Options, out=sys.stdout) -> int:
@@ -226,11 +373,13 @@ def run_gen(o: Options, out=sys.stdout) -> int:
     ctx = int(o.args[3]) if len(o.args) > 3 else max(256, len(ids) + n + 1)
     model = Model.load(folder, dtype=o.dtype)
     session = Session(model, SessionParams(n_ctx=ctx, seed=1, kv_f32=o.kv_f32, max_batch=1))
+    _perf_begin(o)
     res = session.generate([ids], GenerateParams(n, SamplerParams.greedy()))[0]
     out.write(" ".join(str(t) for t in res.tokens) + "\n")
     out.write(f"prefill: {res.n_prompt} tokens, {res.prefill * 1e3:.1f} ms ({res.n_prompt / max(res.prefill, 1e-9):.1f} tok/s)\n")
     out.write(f"decode: {res.n_generated} tokens, {res.decode * 1e3:.1f} ms ({res.n_generated / max(res.decode, 1e-9):.1f} tok/s)\n")
     out.write(f"stop: {res.stop.value}\n")
+    _perf_end(o, "gen", res.n_prompt + res.n_generated, out)
     return 0
 
 
@@ -280,6 +429,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             return 0
         if o.mode == "gen":
             return run_gen(o)
+        if o.mode == "chat":
+            return run_chat(o)
         if o.mode == "info":
             return run_info(o)
         if o.mode == "random-weights":

@@ -138,16 +138,18 @@ class Qwen3Config:
             "vocab_size": self.vocab_size,
             "rms_norm_eps": self.rms_norm_eps,
             "rope_theta": self.rope_theta,
-            "rope_scaling": None,
             "max_position_embeddings": self.max_position_embeddings,
             "tie_word_embeddings": self.tie_word_embeddings,
             "attention_bias": self.attention_bias,
             "hidden_act": self.hidden_act,
             "use_sliding_window": self.use_sliding_window,
-            "sliding_window": self.sliding_window,
-            "max_window_layers": self.max_window_layers,
             "torch_dtype": self.torch_dtype,
         }
+        # keys without a value are left out, so that the folder this library writes is one other tools load
+        if self.sliding_window is not None:
+            d["sliding_window"] = self.sliding_window
+        if self.max_window_layers is not None:
+            d["max_window_layers"] = self.max_window_layers
         if self.layer_types is not None:
             d["layer_types"] = list(self.layer_types)
         if self.eos_token_id:

@@ -46,8 +46,28 @@ def config_from_dict(d: dict):
     return config_class(archs[0]).from_dict(d)
 
 
+def _generation_stop_ids(folder) -> list:
+    """The ``eos_token_id`` entries of ``generation_config.json``, if the folder has one: checkpoints keep the
+    whole set of tokens that end a reply there, while ``config.json`` names one
+    (the reference's set: crates/nncpu/src/tokenizer/mod.rs:385-405)."""
+    path = Path(folder) / "generation_config.json"
+    if not path.exists():
+        return []
+    try:
+        g = json.loads(path.read_text())
+    except json.JSONDecodeError as e:
+        raise BadFormat(f"{path} is not JSON: {e}") from None
+    eos = g.get("eos_token_id") if isinstance(g, dict) else None
+    eos = eos if isinstance(eos, list) else ([] if eos is None else [eos])
+    for e in eos:
+        if isinstance(e, bool) or not isinstance(e, int):
+            raise BadFormat(f'{path}: "eos_token_id" holds {e!r}')
+    return eos
+
+
 def load_config(folder):
-    """The typed configuration of the model folder ``folder``."""
+    """The typed configuration of the model folder ``folder``: ``config.json``, with the stop tokens of
+    ``generation_config.json`` added to its ``eos_token_id``."""
     path = Path(folder) / "config.json"
     try:
         d = json.loads(path.read_text())
@@ -57,4 +77,9 @@ def load_config(folder):
         raise BadFormat(f"{path} is not JSON: {e}") from None
     if not isinstance(d, dict):
         raise BadFormat(f"{path} does not hold a JSON object")
+    extra = _generation_stop_ids(folder)
+    if extra:
+        own = d.get("eos_token_id")
+        own = own if isinstance(own, list) else ([] if own is None else [own])
+        d = dict(d, eos_token_id=own + [e for e in extra if e not in own])
     return config_from_dict(d)

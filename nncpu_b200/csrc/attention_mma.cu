@@ -558,13 +558,11 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     const size_t stages = (size_t)kDecodeStages * 2 * kPage * HD * 2;
     const size_t merge = (size_t)5 * G * (HD + 2) * sizeof(float);
     const size_t smem = stages > merge ? stages : merge;
-    static bool configured[4] = {false, false, false, false};
-    const int which = (cluster ? 2 : 0) + (G <= 8 ? 0 : 1);
-    if (!configured[which]) {
+    // set at every launch: the attribute belongs to the (kernel, device) pair, and setting it costs next to nothing
+    {
         const cudaError_t e = cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    (int)(stages > (size_t)5 * 16 * (HD + 2) * 4 ? stages : (size_t)5 * 16 * (HD + 2) * 4));
         NN_CHECK(e == cudaSuccess, "attention decode: cannot reserve shared memory: %s", cudaGetErrorString(e));
-        configured[which] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_splits, n_kv, n_tok);
@@ -597,10 +595,9 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
                    float scale, int window, cudaStream_t stream) {
     const int max_tiles = n_tok / 64 + n_seqs;
     constexpr int smem = 2 * 2 * kPage * HD * 2;
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
+    {
+        const cudaError_t e = cudaFuncSetAttribute(prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        NN_CHECK(e == cudaSuccess, "attention prefill: cannot reserve shared memory: %s", cudaGetErrorString(e));
     }
     dim3 grid(max_tiles, n_heads);
     prefill_kernel<HD><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,

@@ -6,8 +6,15 @@ engine captures the step once over static buffers and replays it afterwards;
 per step the host only refreshes a small block of int32 metadata (positions,
 page tables) and copies it to the device.
 
-Rows beyond the live sequences are padding: their sequence index is -1, so no
-kernel writes the cache for them and their outputs are zeros.
+Rows beyond the live sequences are padding: their sequence index and their
+slot are -1, so no kernel writes the cache for them, their outputs are zeros,
+and a part that keeps per-sequence state reads and writes the spare last row
+of its state area (index -1), which no sequence owns.
+
+The step that captures a graph runs the model once, kernel by kernel, and
+returns that result; the captured graph is replayed from the next step of that
+size on.  A part whose step is not idempotent (per-sequence state) therefore
+advances exactly once per step.
 """
 from __future__ import annotations
 
@@ -18,6 +25,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import perf
 from ..cache import pages_for
 from ..kernels import ops
 from .step import StepContext
@@ -91,8 +99,7 @@ class DecodeGraph:
             a[:] = -1
             a[self.o_seq:self.o_seq + n] = np.arange(n)
             a[self.o_pos:self.o_pos + B] = 0
-            a[self.o_slot:self.o_slot + n] = slots
-            a[self.o_slot + n:self.o_slot + B] = 0
+            a[self.o_slot:self.o_slot + n] = slots       # padding rows keep slot -1
             a[self.o_cu:self.o_cu + B + 1] = np.arange(B + 1)
             a[self.o_rows:self.o_rows + n] = np.arange(n)
             self.slots = tuple(slots)
@@ -139,13 +146,19 @@ class DecodeGraph:
         """One decode step for ``slots``.  ``tokens`` None: the step's tokens
         are the previous step's greedy choices, which never left the device.
         Returns float32 logits [len(slots), vocab], valid until the next step."""
+        with perf.paused():      # events cannot be timed inside a graph: a replay is not attributed to phases
+            return self._run(slots, tokens)
+
+    def _run(self, slots, tokens):
         self.ctx.memo.clear()
         self._fill(slots, tokens)
         if tokens is None:
             self.tok_ids.copy_(self.next_ids, non_blocking=True)
         if self.graph is None:
-            # the first step of this size runs kernel by kernel, then the same work is captured
+            # The first step of this size runs kernel by kernel and its result is the step's result.  The same
+            # work is then captured, not run: a second run would advance per-sequence state twice.
             self._forward()
+            eager = self.logits
             before = ops.launch_count()
             g = torch.cuda.CUDAGraph()
             torch.cuda.synchronize()
@@ -164,8 +177,7 @@ class DecodeGraph:
             self.n_kernels = ops.launch_count() - before
             ops.add_launches(-self.n_kernels)  # capturing launches nothing
             self.graph = g
-            g.replay()  # the captured buffers now hold this step's result
-            ops.add_launches(self.n_kernels)
+            self.logits.copy_(eager)  # the graph's own buffer holds this step's logits until its first replay
         else:
             self.graph.replay()
             ops.add_launches(self.n_kernels)

@@ -27,6 +27,11 @@ launched on top of them, and the host reads the tokens meanwhile and takes its
 decisions one step behind.  A sequence that the host then stops has run one
 step too many, which nobody sees: its slot is freed.  Steps in which a count
 limit (context, ``max_tokens``) can end a sequence are not run ahead.
+
+Wherever the loop has waited for the device it asks the engine whether a
+kernel gave up a bounded wait (``check_status``, if the engine has it): a step
+whose kernel did not finish its work raises instead of handing out tokens, and
+the batch's slots are freed on the way out.
 """
 from __future__ import annotations
 
@@ -60,11 +65,13 @@ def plan_batches(prompt_lens: Sequence[int], max_new: Sequence[int], max_batch: 
 def generate(engine, chooser, prompts: Sequence[Sequence[int]], params: GenerateParams,
              stop_token_ids: Sequence[int] = (), on_token: Optional[Callable[[int, int], bool]] = None,
              cancelled: Callable[[], bool] = lambda: False, max_batch: int = 64,
-             n_ctx: Optional[int] = None, n_pages: Optional[int] = None) -> List[GenerateResult]:
+             n_ctx: Optional[int] = None, n_pages: Optional[int] = None,
+             on_finish: Optional[Callable[[int], None]] = None) -> List[GenerateResult]:
     """Generates a continuation for every prompt.  ``chooser.choose(logits,
     indices)`` picks one token per logits row; ``on_token(index, token)`` is
     called for every generated token and may return False to stop that
-    sequence.  Results come in the order of the prompts."""
+    sequence; ``on_finish(index)`` is called once when a sequence has stopped.
+    Results come in the order of the prompts."""
     n_ctx = n_ctx or engine.max_seq_len
     stops = frozenset(int(t) for t in stop_token_ids)
     if not prompts:
@@ -81,11 +88,37 @@ def generate(engine, chooser, prompts: Sequence[Sequence[int]], params: Generate
     results: List[Optional[GenerateResult]] = [None] * len(prompts)
     for batch in batches:
         _run_batch(engine, chooser, [(i, list(prompts[i])) for i in batch], params, stops, on_token, cancelled,
-                   n_ctx, results)
+                   n_ctx, results, on_finish)
     return results  # type: ignore[return-value]
 
 
-def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_ctx, results) -> None:
+def generate_on_slot(engine, chooser, slot: int, tokens: List[int], n_evaluated: int, params: GenerateParams,
+                     stop_token_ids: Sequence[int] = (), on_token: Optional[Callable[[int, int], bool]] = None,
+                     cancelled: Callable[[], bool] = lambda: False, n_ctx: Optional[int] = None,
+                     on_finish: Optional[Callable[[int], None]] = None) -> GenerateResult:
+    """Continues the one sequence that lives in ``slot``: ``tokens`` is its whole
+    context, of which the cache already holds the first ``n_evaluated``; the rest
+    is run as one step, then tokens are generated as in ``generate``.  The slot
+    stays with the caller, and ``tokens`` is extended in place with what was
+    generated (a stop token included), as the reference keeps its context
+    (crates/nncpu/src/session/engine.rs:476-481,598-690)."""
+    n_ctx = n_ctx or engine.max_seq_len
+    if n_evaluated >= len(tokens):
+        raise InvalidArgument("there is nothing to continue from: no token is waiting to be evaluated")
+    if len(tokens) + 1 > n_ctx:
+        raise ContextFull(f"{len(tokens)} tokens of context leave no room in the {n_ctx}-token context")
+    results: List[Optional[GenerateResult]] = [None]
+    _run_batch(engine, chooser, [(0, tokens)], params, frozenset(int(t) for t in stop_token_ids), on_token, cancelled,
+               n_ctx, results, on_finish, held={0: (slot, n_evaluated)})
+    return results[0]  # type: ignore[return-value]
+
+
+def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_ctx, results, on_finish=None,
+               held=None) -> None:
+    """``held``: index -> (slot, tokens already in the cache) for sequences that continue on a slot of the
+    caller's, which is not given back."""
+    held = held or {}
+    check_status = getattr(engine, "check_status", None) or (lambda: None)
     live = []  # [index, slot, tokens so far (prompt + generated), result]
     on_device = ((getattr(chooser, "chooses_on_device", False) or getattr(chooser, "greedy_on_device", False))
                  and all(hasattr(engine, a) for a in ("choice_buffer", "fetch_choices", "step_again")))
@@ -110,21 +143,29 @@ def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_c
                 else:
                     still.append([idx, slot, toks, r])
                     continue
-            engine.free_slot(slot)
+            if idx not in held:
+                engine.free_slot(slot)
+            if on_finish is not None:
+                on_finish(idx)
         return still
 
     try:
+        first = []
         for idx, prompt in members:
-            live.append([idx, engine.alloc_slot(), prompt, GenerateResult(n_prompt=len(prompt))])
+            slot, start = held[idx] if idx in held else (engine.alloc_slot(), 0)
+            live.append([idx, slot, prompt, GenerateResult(n_prompt=len(prompt) - start)])
+            first.append(prompt[start:])
         t0 = time.perf_counter()
-        logits = engine.step([s for _, s, _, _ in live], [p for _, _, p, _ in live])
+        logits = engine.step([s for _, s, _, _ in live], first)
         done_results = [r for _, _, _, r in live]
         prefill = None
         t1 = t0
         while live:
             if cancelled():
-                for _, _, _, r in live:
+                for idx, _, _, r in live:
                     r.stop = StopReason.CANCELLED
+                    if on_finish is not None:
+                        on_finish(idx)
                 break
             ahead = None
             buffer = engine.choice_buffer(len(live)) if on_device and prefill is not None else None
@@ -142,6 +183,7 @@ def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_c
                 chosen = ids[:len(live)].tolist()
             else:
                 chosen = chooser.choose(logits, [idx for idx, _, _, _ in live])
+            check_status()      # the device has been waited for: did every kernel of the step finish its work?
             if prefill is None:  # the first choice waits for the prompt step to finish
                 t1 = time.perf_counter()
                 prefill = t1 - t0
@@ -159,6 +201,7 @@ def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_c
                     chooser.enqueue(ahead, [m[0] for m in live], engine.choice_buffer(len(live)))
                 event, ids = engine.fetch_choices(len(live))
                 event.synchronize()
+                check_status()
                 still = settle(still, [int(ids[k]) for k in rows])
             live = still
             if live:
@@ -170,5 +213,6 @@ def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_c
         for (idx, _), r in zip(members, done_results):
             results[idx] = r
     finally:
-        for _, slot, _, _ in live:
-            engine.free_slot(slot)
+        for idx, slot, _, _ in live:
+            if idx not in held:
+                engine.free_slot(slot)

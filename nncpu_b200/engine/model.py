@@ -16,7 +16,7 @@ import torch
 
 from ..cache import KVRequest, StateRequest
 from ..config import ModelSpec, load_config
-from ..errors import BadFormat, InvalidArgument
+from ..errors import BadFormat, InvalidArgument, translating_oom
 from ..kernels import ops
 from ..parts import EntryCache, Runtime, build
 from ..weights import ParamSpec, load_tensors, random_tensors_on_device
@@ -30,6 +30,17 @@ def resolve_dtype(dtype) -> torch.dtype:
         return _DTYPES[dtype]
     except KeyError:
         raise InvalidArgument(f"dtype {dtype!r} is not supported (bfloat16 or float32)") from None
+
+
+def _gib(params: List[ParamSpec], dtype: torch.dtype) -> float:
+    esize = 2 if dtype == torch.bfloat16 else 4
+    n = 0
+    for p in params:
+        c = 1
+        for d in p.shape:
+            c *= d
+        n += c
+    return n * esize / 2 ** 30
 
 
 def _shares(spec: ModelSpec) -> List[bool]:
@@ -79,6 +90,7 @@ class Model:
             block.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
         self.schedule = list(spec.schedule)
+        self._cache_plan = self._plan_cache()
 
     @classmethod
     def load(cls, folder, dtype="bfloat16", device="cuda:0", progress=None) -> "Model":
@@ -89,8 +101,10 @@ class Model:
         config = load_config(folder)
         dt = resolve_dtype(dtype)
         rt = Runtime(device, dt)
-        tensors = load_tensors(folder, parameter_list(config.model_spec()), dt, rt.device, progress)
-        return cls(config, tensors, rt)
+        params = parameter_list(config.model_spec())
+        with translating_oom(f"the weights of {folder} ({_gib(params, dt):.2f} GiB in {dtype})"):
+            tensors = load_tensors(folder, params, dt, rt.device, progress)
+            return cls(config, tensors, rt)
 
     @classmethod
     def random(cls, config, seed: int, dtype="bfloat16", device="cuda:0") -> "Model":
@@ -98,16 +112,31 @@ class Model:
         files).  ``write_model_folder`` is the mode that writes a folder."""
         dt = resolve_dtype(dtype)
         rt = Runtime(device, dt)
-        return cls(config, random_tensors_on_device(parameter_list(config.model_spec()), seed, dt, rt.device), rt)
+        params = parameter_list(config.model_spec())
+        with translating_oom(f"random weights ({_gib(params, dt):.2f} GiB in {dtype})"):
+            return cls(config, random_tensors_on_device(params, seed, dt, rt.device), rt)
 
     # -- storage the schedule asks for ------------------------------------------
 
     def cache_requests(self) -> Tuple[List[Tuple[Optional[KVRequest], Optional[StateRequest]]], List[Optional[int]]]:
+        return self._cache_plan
+
+    def _plan_cache(self):
+        """What the cache must hold: one (keys/values, state) request per cache user, and for each user the
+        user whose keys and values it reads instead of its own.  A schedule entry has as many users as its
+        block asks for (``Block.cache_requests()``: one per mixer, none for a block without one); an entry that
+        reads another entry's cache pairs its users with that entry's, in order."""
         requests, cache_of = [], []
-        for e in self.schedule:
-            mixer = self.blocks[e.layer].mixer
-            requests.append((None if e.cache_of is not None else mixer.kv_request(), mixer.state_request()))
-            cache_of.append(e.cache_of)
+        self._users = []   # per schedule entry: (first user, number of users)
+        for i, e in enumerate(self.schedule):
+            asked = self.blocks[e.layer].cache_requests()
+            if e.cache_of is not None and self._users[e.cache_of][1] != len(asked):
+                raise BadFormat(f"schedule entry {i} reads the cache of entry {e.cache_of}, whose block keeps "
+                                f"{self._users[e.cache_of][1]} caches where this one needs {len(asked)}")
+            self._users.append((len(requests), len(asked)))
+            for k, (kv, state) in enumerate(asked):
+                requests.append((None if e.cache_of is not None else kv, state))
+                cache_of.append(None if e.cache_of is None else self._users[e.cache_of][0] + k)
         return requests, cache_of
 
     # -- numbers for reports ------------------------------------------------------
@@ -132,12 +161,14 @@ class Model:
         logits [n_wanted, vocab] (None when no row is wanted)."""
         rt, spec = self.rt, self.spec
         residual = rt.empty(ctx.n_tokens, spec.hidden_size, dtype=torch.float32)
-        ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale)
-        for i, e in enumerate(self.schedule):
-            self.blocks[e.layer].forward(ctx, residual, ctx.entry_cache(cache, i))
+        with rt.phase("embed"):
+            ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale)
+        for e, (first, count) in zip(self.schedule, self._users):
+            self.blocks[e.layer].forward(ctx, residual, [ctx.entry_cache(cache, u) for u in range(first, first + count)])
         if ctx.n_wanted == 0:
             return None
         x = self.final_norm.forward(ctx, residual, rows=ctx.logit_rows)
         logits = rt.empty(ctx.n_wanted, spec.vocab_size, dtype=torch.float32)
-        rt.linear(x, self.lm_head, None, logits)
+        with rt.phase("lm_head", self.lm_head, ctx.n_wanted):
+            rt.linear(x, self.lm_head, None, logits)
         return logits

@@ -16,8 +16,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import perf
 from ..cache import Cache
-from ..errors import ContextFull, InvalidArgument
+from ..errors import ContextFull, InvalidArgument, translating_oom
 from ..parts import EntryCache
 
 
@@ -40,6 +41,22 @@ class StepContext:
     h2d_bytes: int = 0          # bytes of metadata copied to the device for this step
     max_kv_len: int = 0         # host: an upper bound of the longest sequence after this step
     memo: Dict = field(default_factory=dict)  # per-step results shared between layers
+
+    def span_sum(self, window: int = 0) -> int:
+        """Keys that the step's tokens attend to, summed over the tokens: a token at position p sees p + 1
+        keys, or the last ``window`` of them."""
+        key = ("span_sum", window)
+        n = self.memo.get(key)
+        if n is None:
+            n = 0
+            for q, after in zip(self.q_lens, self.kv_lens):
+                first = after - q + 1                      # keys seen by the sequence's first new token
+                if window > 0:
+                    n += sum(min(first + i, window) for i in range(q))
+                else:
+                    n += q * first + q * (q - 1) // 2
+            self.memo[key] = n
+        return n
 
     def entry_cache(self, cache: Cache, entry: int) -> EntryCache:
         g = cache.group_of(entry)
@@ -188,16 +205,27 @@ class Engine:
         slots = [int(s) for s in slots]
         self.check(slots, tokens, want)
         self.cache.prepare(slots, [len(t) for t in tokens])
-        if self.graphs is not None and all(len(t) == 1 for t in tokens) and all(list(w) == [0] for w in want):
-            g = self.graphs.get(len(slots))
-            logits = g.run(slots, [t[0] for t in tokens])
+        if (self.graphs is not None and not perf.enabled() and all(len(t) == 1 for t in tokens)
+                and all(list(w) == [0] for w in want)):
+            try:
+                with translating_oom(f"a decode step of {len(slots)} sequences"):
+                    g = self.graphs.get(len(slots))
+                    logits = g.run(slots, [t[0] for t in tokens])
+            except BaseException:
+                self.cache.rollback(slots)
+                raise
             self.h2d_bytes_last_step = g.h2d_bytes
             self.cache.commit(slots, [1] * len(slots))
             self._last_graph = g
             return logits
         self._last_graph = None
-        ctx = self.build_context(slots, tokens, want)
-        logits = self.model.forward(ctx, self.cache)
+        try:
+            with translating_oom(f"a step of {sum(len(t) for t in tokens)} tokens in {len(slots)} sequences"):
+                ctx = self.build_context(slots, tokens, want)
+                logits = self.model.forward(ctx, self.cache)
+        except BaseException:
+            self.cache.rollback(slots)     # the step did not happen: the cache is as it was
+            raise
         self.cache.commit(slots, ctx.q_lens)
         return logits
 
@@ -218,7 +246,13 @@ class Engine:
         g = self._last_graph
         if g is None:
             return None
+        self.model.rt.post_status()     # the status word travels with the tokens: checking it costs no wait
         return g.fetch_ids(n)
+
+    def check_status(self) -> None:
+        """Raises ``ExtensionError`` if a kernel of an earlier step gave up a bounded wait.  Call where the
+        device has been waited for."""
+        self.model.rt.check_status()
 
     def step_again(self, slots: Sequence[int]) -> torch.Tensor:
         """One more decode step for exactly the sequences of the last graph
@@ -244,9 +278,9 @@ class Engine:
         slots = [int(s) for s in slots]
         n = len(slots)
         out = torch.empty((n_steps, n), dtype=torch.int32, device=self.cache.device)
-        from .decode_graph import DecodeGraphs
-        graphs = self.graphs if self.graphs is not None else DecodeGraphs(self)
-        self.graphs = graphs
+        if self.graphs is None:
+            raise InvalidArgument("decode_run replays captured steps: the engine was made with use_graphs=False")
+        graphs = self.graphs
         g = graphs.get(n)
         for i in range(n_steps):
             self.cache.prepare(slots, [1] * n)

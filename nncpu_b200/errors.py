@@ -46,3 +46,24 @@ class ExtensionError(NncpuError, RuntimeError):
     """The CUDA extension is missing, did not build, or a kernel refused its
     sizes.  There is no fallback path: the call fails."""
     kind = "Extension"
+
+
+class translating_oom:
+    """``with translating_oom("what was being made"):`` turns the device allocator's out-of-memory error into
+    ``OutOfMemory`` with the sizes in the message, as the reference turns a failed allocation into its
+    ``OutOfMemory`` kind (crates/nncpu/src/model/kv.rs:182-187, crates/nncpu/src/model/load.rs:329-335)."""
+
+    def __init__(self, what: str):
+        self.what = what
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, kind, err, tb):
+        if kind is None:
+            return False
+        import torch
+        if issubclass(kind, torch.OutOfMemoryError):
+            first = str(err).split(". ")[0]
+            raise OutOfMemory(f"{self.what}: the device has no room ({first})") from None
+        return False

@@ -236,6 +236,20 @@ def attention_mma_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) ->
             and all(t.dtype == torch.bfloat16 for t in tensors))
 
 
+# How decode attention cuts a sequence's keys into splits: the kernel's launch bounds let two of its blocks run on
+# an SM at once, and a split shorter than this many keys costs more in merging than it gains.
+DECODE_BLOCKS_PER_SM = 2
+DECODE_MIN_KEYS_PER_SPLIT = 256
+DECODE_CLUSTER_MAX_SPLITS = 8      # up to here the splits merge inside a thread-block cluster, without scratch
+
+
+def attention_decode_splits(n_tokens: int, n_kv: int, longest: int, sm_count: int) -> int:
+    """As many splits as keep every block of the grid running at once (never a second wave), each with at
+    least ``DECODE_MIN_KEYS_PER_SPLIT`` keys of the longest sequence."""
+    pairs = max(1, n_tokens * n_kv)
+    return max(1, min(DECODE_BLOCKS_PER_SM * sm_count // pairs, longest // DECODE_MIN_KEYS_PER_SPLIT))
+
+
 def attention_decode_scratch_floats(n_tok: int, n_heads: int, n_kv: int, head_dim: int, n_splits: int) -> int:
     return 0 if n_splits <= 1 else n_tok * n_kv * n_splits * (n_heads // n_kv) * (head_dim + 2)
 

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import perf
 from ..cache import KVRequest
 from ..errors import UnsupportedModel
 from ..kernels import ops
@@ -86,21 +87,34 @@ class Attention(Mixer):
         if self._fused_qkv(x, cache):
             # a prompt: norm, rotation and the cache append happen in the projection's epilogue, on its
             # float32 accumulators; its threads are tokens, so the rotation table is laid out by pair
-            cos_sin = None if self.position is None else self.position.tables(ctx, by_pair=True)
-            ops.linear_tc_qkv(x, self.w_qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
-                              cache.block_table, cache.k_pages, cache.v_pages, q, rt.workspace, s.n_heads,
-                              s.n_kv_heads, s.head_dim)
+            with rt.phase("attn_rope"):
+                cos_sin = None if self.position is None else self.position.tables(ctx, by_pair=True)
+            with rt.phase("attn_qkv", self.w_qkv, n):
+                ops.linear_tc_qkv(x, self.w_qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
+                                  cache.block_table, cache.k_pages, cache.v_pages, q, rt.workspace, s.n_heads,
+                                  s.n_kv_heads, s.head_dim)
         else:
             # the projections stay in float32 until the per-head norm and the rotation have been applied
             qkv = rt.empty(n, self.q_size + 2 * self.kv_size, dtype=torch.float32)
-            rt.linear(x, self.w_qkv, self.b_qkv, qkv)
-            cos_sin = None if self.position is None else self.position.tables(ctx)
-            ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
-                                    cache.block_table, cache.k_pages, cache.v_pages, q, s.n_heads,
-                                    0 if self.shared_kv else s.n_kv_heads, s.head_dim)
+            with rt.phase("attn_qkv", self.w_qkv, n):
+                rt.linear(x, self.w_qkv, self.b_qkv, qkv)
+            with rt.phase("attn_rope"):
+                cos_sin = None if self.position is None else self.position.tables(ctx)
+                ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
+                                        cache.block_table, cache.k_pages, cache.v_pages, q, s.n_heads,
+                                        0 if self.shared_kv else s.n_kv_heads, s.head_dim)
         attn = rt.empty(n, self.q_size)
-        self._attend(ctx, q, cache, attn)
-        rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True)
+        if perf.enabled():
+            # every token streams the keys and values of its span (crates/nncpu/src/model/forward.rs:382-386)
+            keys = ctx.span_sum(s.window)
+            core = rt.phase("attn_core", nbytes=2.0 * keys * s.n_kv_heads * s.head_dim * cache.k_pages.element_size(),
+                            flops=4.0 * keys * self.q_size)
+        else:
+            core = perf._NULL
+        with core:
+            self._attend(ctx, q, cache, attn)
+        with rt.phase("attn_out", self.w_o, n):
+            rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True)
 
     def _fused_qkv(self, x, cache) -> bool:
         s = self.spec
@@ -118,12 +132,10 @@ class Attention(Mixer):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
                           s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
         elif ctx.is_decode:
-            # as many blocks as run at once (two per SM), never a second wave; at least 256 keys per split
             longest = min(ctx.max_kv_len, s.window) if s.window > 0 else ctx.max_kv_len
-            pairs = ctx.n_tokens * s.n_kv_heads
-            n_splits = max(1, min(296 // pairs, longest // 256))
-            # up to 8 splits merge inside a thread-block cluster; more go through scratch and a merge kernel
-            floats = 0 if n_splits <= 8 else ops.attention_decode_scratch_floats(
+            n_splits = ops.attention_decode_splits(ctx.n_tokens, s.n_kv_heads, longest, self.rt.sm_count)
+            # few splits merge inside a thread-block cluster; more go through scratch and a merge kernel
+            floats = 0 if n_splits <= ops.DECODE_CLUSTER_MAX_SPLITS else ops.attention_decode_scratch_floats(
                 ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
             scratch = self.rt.empty(floats, dtype=torch.float32) if floats else None
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,

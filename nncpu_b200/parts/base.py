@@ -20,7 +20,10 @@ stream ``[n_tokens, hidden]``):
 * ``FeedForward.forward(ctx, x, residual) -> None`` adds its output to ``residual``.
 * ``PositionEncoding.tables(ctx)`` gives what its mixers need for the step's
   positions, computed once per step.
-* ``Block.forward(ctx, residual, cache) -> None`` runs its parts in its arrangement.
+* ``Block.cache_requests()`` lists what its mixers keep from step to step, one
+  ``(KVRequest or None, StateRequest or None)`` pair per mixer (a block may have
+  one, several or none); ``Block.forward(ctx, residual, caches) -> None`` runs its
+  parts in its arrangement, ``caches[k]`` being the ``EntryCache`` of request ``k``.
 """
 from __future__ import annotations
 
@@ -94,9 +97,12 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    mixer: Mixer
+    def cache_requests(self) -> List[tuple]:
+        """One (KVRequest or None, StateRequest or None) pair per mixer of the block, in the order in which
+        ``forward`` finds their caches."""
+        return []
 
-    def forward(self, ctx, residual: torch.Tensor, cache: EntryCache) -> None:
+    def forward(self, ctx, residual: torch.Tensor, caches: List[EntryCache]) -> None:
         raise NotImplementedError
 
 

@@ -29,6 +29,9 @@ class PreNormBlock(Block):
     def weight_bytes(self):
         return sum(part.weight_bytes() for part in self._parts)
 
-    def forward(self, ctx, residual, cache):
-        self.mixer.forward(ctx, self.norm1.forward(ctx, residual), residual, cache)
+    def cache_requests(self):
+        return [(self.mixer.kv_request(), self.mixer.state_request())]
+
+    def forward(self, ctx, residual, caches):
+        self.mixer.forward(ctx, self.norm1.forward(ctx, residual), residual, caches[0])
         self.feed_forward.forward(ctx, self.norm2.forward(ctx, residual), residual)

@@ -49,9 +49,13 @@ class GatedMlp(FeedForward):
         n = x.shape[0]
         act = rt.empty(n, s.intermediate_size)
         if self.fused:
-            rt.linear(x, self.w_gate_up, None, act, epilogue="swiglu")
+            with rt.phase("ffn_gate_up", self.w_gate_up, n):
+                rt.linear(x, self.w_gate_up, None, act, epilogue="swiglu")
         else:
             gate_up = rt.empty(n, 2 * s.intermediate_size)
-            rt.linear(x, self.w_gate_up, None, gate_up)
-            ops.swiglu(gate_up, act)
-        rt.linear(act, self.w_down, None, residual, accumulate=True)
+            with rt.phase("ffn_gate_up", self.w_gate_up, n):
+                rt.linear(x, self.w_gate_up, None, gate_up)
+            with rt.phase("ffn_act"):
+                ops.swiglu(gate_up, act)
+        with rt.phase("ffn_down", self.w_down, n):
+            rt.linear(act, self.w_down, None, residual, accumulate=True)

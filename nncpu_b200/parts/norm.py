@@ -23,5 +23,6 @@ class RMSNorm(Norm):
     def forward(self, ctx, residual, rows=None):
         n = residual.shape[0] if rows is None else rows.numel()
         out = self.rt.empty(n, self.size)
-        ops.rmsnorm(residual, self.gamma, self.eps, out, rows)
+        with self.rt.phase("norm"):
+            ops.rmsnorm(residual, self.gamma, self.eps, out, rows)
         return out

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import perf
 from ..errors import ExtensionError
 from ..kernels import ops
 
@@ -18,7 +19,11 @@ class Runtime:
         if dtype not in (torch.bfloat16, torch.float32):
             raise ExtensionError(f"run element type {dtype} is not supported (bfloat16 or float32)")
         self.dtype = dtype
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._workspace = None
+        self._status_host = None
+        self._status_posted = []
+        self._status_turn = 0
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -46,11 +51,50 @@ class Runtime:
             assert epilogue == "plain", "the fused epilogue exists on the tensor-core path only"
             ops.linear_simt(x, w, bias, out, accumulate)
 
-    def check_status(self) -> None:
-        """Call after a synchronisation: raises if a kernel's bounded wait ran out."""
+    def phase(self, slot: str, weight=None, n_tokens: int = 0, nbytes: float = 0, flops: float = 0):
+        """A profiler scope for the launches of one phase (free when the profiler is off).  With ``weight`` the
+        phase is a product of ``n_tokens`` rows with that matrix: it streams the matrix once and does two
+        operations per element and row."""
+        if not perf.enabled():
+            return perf._NULL
+        if weight is not None:
+            nbytes += weight.numel() * weight.element_size()
+            flops += 2.0 * n_tokens * weight.numel()
+        return perf.scope(slot, nbytes, flops)
+
+    def post_status(self) -> None:
+        """Starts a copy of the status word to pinned host memory, in stream order.  A caller that then waits
+        for later work of the same stream (an event, a copy) can ``check_status()`` without waiting again."""
         if self._workspace is None:
             return
-        code = int(self._workspace.status.item())
+        if self._status_host is None:
+            self._status_host = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(8)]
+            self._status_events = [torch.cuda.Event() for _ in range(8)]
+            self._status_posted = []
+        i = self._status_turn = (self._status_turn + 1) % len(self._status_host)
+        self._status_posted = [j for j in self._status_posted if j != i]
+        self._status_host[i].copy_(self._workspace.status, non_blocking=True)
+        self._status_events[i].record()
+        self._status_posted.append(i)
+
+    def check_status(self) -> None:
+        """Raises if a kernel's bounded wait ran out.  Reads the copies that ``post_status`` started and that
+        have arrived; when none was posted it reads the word itself, which waits for the stream."""
+        if self._workspace is None:
+            return
+        code = 0
+        if self._status_posted:
+            waiting = []
+            for i in self._status_posted:
+                if self._status_events[i].query():
+                    code = code or int(self._status_host[i][0])
+                else:
+                    waiting.append(i)
+            self._status_posted = waiting
+        else:
+            code = int(self._workspace.status.item())
         if code:
+            torch.cuda.synchronize(self.device)
             self._workspace.status.zero_()
+            self._status_posted = []
             raise ExtensionError(f"a kernel gave up waiting (status {code}); the step's results are not valid")

@@ -28,6 +28,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import perf
 from ..kernels import ops
 from .chain import sample_from_candidates, sample_from_logits
 from .params import SamplerParams
@@ -85,13 +86,14 @@ class Sampler:
         """Launches the choice for every row of ``logits`` into ``out`` (int32 on the device) without waiting for
         it; only where ``chooses_on_device``."""
         p = self.params
-        if p.is_greedy:
-            ops.argmax(logits, out)
-        elif not p.truncates(self.vocab_size):
-            ops.sample_temperature(logits, self._uniforms(indices, logits.device), out, p.temperature)
-        else:
-            ops.sample_chain(logits, self._uniforms(indices, logits.device), out, p.top_k, p.temperature, p.top_p,
-                             p.min_p)
+        with perf.scope("sample"):
+            if p.is_greedy:
+                ops.argmax(logits, out)
+            elif not p.truncates(self.vocab_size):
+                ops.sample_temperature(logits, self._uniforms(indices, logits.device), out, p.temperature)
+            else:
+                ops.sample_chain(logits, self._uniforms(indices, logits.device), out, p.top_k, p.temperature, p.top_p,
+                                 p.min_p)
 
     def choose(self, logits: torch.Tensor, indices: Sequence[int]) -> List[int]:
         """``logits`` float32 [n, vocab] on the device, row i belonging to the
@@ -108,8 +110,9 @@ class Sampler:
             vals = torch.empty(n, _NO_TOPK_CANDIDATES, dtype=torch.float32, device=logits.device)
             ids = torch.empty(n, _NO_TOPK_CANDIDATES, dtype=torch.int32, device=logits.device)
             total = torch.empty(n, dtype=torch.float64, device=logits.device)
-            ops.topk(logits, vals, ids)
-            ops.row_exp_sum(logits, total)
+            with perf.scope("sample"):
+                ops.topk(logits, vals, ids)
+                ops.row_exp_sum(logits, total)
             vals, ids, total = vals.cpu().numpy(), ids.cpu().numpy(), total.cpu().numpy()
             out = []
             for r, i in enumerate(indices):

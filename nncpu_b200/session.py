@@ -7,8 +7,15 @@
 
 A ``Session`` owns an engine (model + cache).  Where the reference's session
 holds one sequence, this one holds up to ``max_batch`` at a time; the
-one-sequence calls ``eval`` / ``logits`` / ``sample`` / ``reset`` keep the
-reference's meaning on a sequence of their own.
+one-sequence calls ``eval`` / ``logits`` / ``sample`` / ``chat`` / ``reset``
+keep the reference's meaning on a sequence of the session's own, whose cache
+stays between calls.
+
+With a tokenizer (``Session(model, params, tokenizer=...)``) pieces carry text
+in whole UTF-8 characters beside the token id
+(crates/nncpu/src/session/chat.rs:63-118), and ``chat`` adds a message to the
+session's conversation as a ChatML turn and generates the reply
+(crates/nncpu/src/session/engine.rs:316-328).
 """
 from __future__ import annotations
 
@@ -21,10 +28,11 @@ from typing import Callable, List, Optional, Sequence
 import torch
 
 from .cache import PAGE
-from .engine.generate import generate as _generate
+from .engine.generate import generate as _generate, generate_on_slot as _generate_on_slot
 from .engine.step import Engine
-from .errors import InvalidArgument
+from .errors import ContextFull, InvalidArgument
 from .sampling import GenerateParams, GenerateResult, Sampler, SamplerParams
+from .text import TextStream, chat_turn, end_token_ids
 
 
 @dataclass(frozen=True)
@@ -33,18 +41,28 @@ class SessionParams:
     (crates/nncpu/src/session/engine.rs:113-117); ``seed`` 0 = random
     (crates/nncpu/src/session/engine.rs:125); ``kv_f32`` keeps the cache in
     float32 whatever the run's element type (the reference's ``--kv-f32``);
-    ``max_batch``: sequences generated together."""
+    ``max_batch``: sequences generated together; ``system_prompt`` opens the
+    session's conversation (crates/nncpu/src/session/mod.rs:37-83);
+    ``reply_open`` is text the chat template puts at the start of every reply
+    (Qwen3 without reasoning: ``"<think>\\n\\n</think>\\n\\n"``,
+    crates/nncpu/src/tokenizer/mod.rs:994-997)."""
     n_ctx: int = 0
     seed: int = 0
     kv_f32: bool = False
     max_batch: int = 8
+    system_prompt: str = ""
+    reply_open: str = ""
 
 
 @dataclass(frozen=True)
 class Piece:
-    """One generated token of sequence ``index``, handed to ``on_piece``."""
+    """One generated token of sequence ``index``, handed to ``on_piece``.  In a
+    session with a tokenizer ``text`` holds the whole characters that this
+    token completed (empty while a character is still cut off); when a sequence
+    ends with bytes left over, a last piece with ``token`` None carries them."""
     index: int
-    token: int
+    token: Optional[int]
+    text: str = ""
 
 
 class CancelHandle:
@@ -65,18 +83,26 @@ class CancelHandle:
 
 
 class Session:
-    def __init__(self, model, params: SessionParams = SessionParams()):
+    _make_sampler = staticmethod(Sampler)    # (SamplerParams, seed, vocabulary size) -> chooser
+
+    def __init__(self, model, params: SessionParams = SessionParams(), tokenizer=None, engine=None):
+        """``engine``: an engine made elsewhere for ``model`` (tests pass a scripted one); by default the
+        session makes its own, with room for ``max_batch`` sequences of ``n_ctx`` tokens and one more for the
+        session's own sequence."""
         if params.n_ctx < 0 or params.max_batch < 1:
             raise InvalidArgument(f"n_ctx {params.n_ctx}, max_batch {params.max_batch}")
         self.model = model
         self.params = params
+        self.tokenizer = tokenizer
         self.n_ctx = params.n_ctx if params.n_ctx > 0 else min(4096, model.spec.max_positions)
         per_seq = (self.n_ctx + PAGE - 1) // PAGE * PAGE
-        self.engine = Engine(model, max_tokens=per_seq * (params.max_batch + 1), max_seq_len=self.n_ctx,
-                             kv_dtype=torch.float32 if params.kv_f32 else None)
+        self.engine = engine if engine is not None else Engine(
+            model, max_tokens=per_seq * (params.max_batch + 1), max_seq_len=self.n_ctx,
+            kv_dtype=torch.float32 if params.kv_f32 else None)
         self.seed = params.seed if params.seed != 0 else int.from_bytes(os.urandom(8), "little") | 1
         self._cancel = CancelHandle()
         self._own_slot: Optional[int] = None
+        self._own_tokens: List[int] = []     # the session's own sequence: what the cache holds, then what waits
         self._own_logits: Optional[torch.Tensor] = None
         self._own_rngs: Optional[Sampler] = None
         self._n_generate_calls = 0
@@ -94,15 +120,48 @@ class Session:
         params.sampler.check("generate")
         if params.max_tokens < 0:
             raise InvalidArgument(f"generate: max_tokens {params.max_tokens}")
-        stops = self.model.spec.stop_token_ids if stop_token_ids is None else stop_token_ids
-        sampler = Sampler(params.sampler, self.seed + 1000003 * self._n_generate_calls, self.model.spec.vocab_size)
+        stops = self._stops(stop_token_ids)
+        sampler = self._make_sampler(params.sampler, self.seed + 1000003 * self._n_generate_calls, self.model.spec.vocab_size)
         self._n_generate_calls += 1
         self._cancel._start_call()
-        on_token = None if on_piece is None else (lambda i, t: on_piece(Piece(i, t)))
+        on_token, on_finish = self._piece_callbacks(on_piece)
         # one slot's worth of pages is kept for the one-sequence calls
         return _generate(self.engine, sampler, prompts, params, stops, on_token, self._cancel._is_set,
                          max_batch=self.params.max_batch, n_ctx=self.n_ctx,
-                         n_pages=self.engine.n_pages - (self.n_ctx + PAGE - 1) // PAGE)
+                         n_pages=self.engine.n_pages - (self.n_ctx + PAGE - 1) // PAGE, on_finish=on_finish)
+
+    def _stops(self, stop_token_ids):
+        """The configuration's end-of-sequence ids and, with a tokenizer, the end markers its vocabulary
+        holds (crates/nncpu/src/tokenizer/mod.rs:385-405); a caller's own list replaces both."""
+        if stop_token_ids is not None:
+            return stop_token_ids
+        stops = list(self.model.spec.stop_token_ids)
+        if self.tokenizer is not None:
+            stops += [t for t in end_token_ids(self.tokenizer) if t not in stops]
+        return stops
+
+    def _piece_callbacks(self, on_piece):
+        """``on_token`` and ``on_finish`` for the generation loop: pieces with text in whole characters when the
+        session has a tokenizer, token ids alone otherwise."""
+        if on_piece is None:
+            return None, None
+        tok = self.tokenizer
+        if tok is None:
+            return (lambda i, t: on_piece(Piece(i, t))), None
+        streams = {}
+
+        def on_token(i, t):
+            stream = streams.get(i)
+            if stream is None:
+                stream = streams[i] = TextStream()
+            return on_piece(Piece(i, t, stream.write(tok.token_bytes(t))))
+
+        def on_finish(i):
+            stream = streams.pop(i, None)
+            rest = stream.finish() if stream is not None else ""
+            if rest:
+                on_piece(Piece(i, None, rest))
+        return on_token, on_finish
 
     def cancel_handle(self) -> CancelHandle:
         return self._cancel
@@ -112,11 +171,16 @@ class Session:
     def eval(self, tokens: Sequence[int]) -> None:
         """Runs ``tokens`` through the model after what this session's own
         sequence already holds (crates/nncpu/src/session/engine.rs:217-251)."""
-        if len(tokens) == 0:
+        if len(tokens) == 0 and self.n_past() == len(self._own_tokens):
             return
         if self._own_slot is None:
             self._own_slot = self.engine.alloc_slot()
-        self._own_logits = self.engine.step([self._own_slot], [list(tokens)])
+        waiting = self._own_tokens[self.n_past():] + [int(t) for t in tokens]
+        # a copy: a one-token step returns a view of its decode graph's buffer, which the next step of that
+        # size (this session's generate() included) overwrites
+        self._own_logits = self.engine.step([self._own_slot], [waiting]).clone()
+        self.engine.check_status()
+        self._own_tokens += [int(t) for t in tokens]
 
     def logits(self) -> torch.Tensor:
         """float32 [vocab] on the device: the prediction after the last
@@ -138,11 +202,69 @@ class Session:
         return self._own_rngs.choose(self._own_logits, [0])[0]
 
     def n_past(self) -> int:
-        return 0 if self._own_slot is None else self.engine.cache.length(self._own_slot)
+        """Tokens of the session's own sequence that the cache holds."""
+        return 0 if self._own_slot is None else min(self.engine.cache.length(self._own_slot), len(self._own_tokens))
+
+    def tokens(self) -> List[int]:
+        """The session's own sequence: evaluated tokens, then those that wait (a reply's last token)."""
+        return list(self._own_tokens)
+
+    def extend(self, tokens: Sequence[int], params: GenerateParams = GenerateParams(),
+               on_piece: Optional[Callable[[Piece], bool]] = None,
+               stop_token_ids: Optional[Sequence[int]] = None) -> GenerateResult:
+        """Adds ``tokens`` to the session's own sequence and generates after
+        them, as the reference's one-sequence ``generate`` does
+        (crates/nncpu/src/session/engine.rs:289-299,598-690): the cache of
+        earlier calls is kept, only what is new is evaluated, and the generated
+        tokens (a stop token included) join the sequence; the last of them
+        waits to be evaluated by the next call."""
+        params.sampler.check("generate")
+        if params.max_tokens < 0:
+            raise InvalidArgument(f"generate: max_tokens {params.max_tokens}")
+        context = self._own_tokens + [int(t) for t in tokens]
+        if not context:
+            raise InvalidArgument("there is nothing to continue: the context and the new tokens are both empty")
+        if len(context) + 1 > self.n_ctx:
+            # refused before anything changes (crates/nncpu/src/session/engine.rs:605-615)
+            raise ContextFull(f"{len(context)} tokens of context ({len(tokens)} of them new) and room for one more "
+                              f"do not fit the {self.n_ctx}-token context")
+        if self._own_slot is None:
+            self._own_slot = self.engine.alloc_slot()
+        n_held = self.n_past()
+        if n_held == len(context):
+            # everything is evaluated already (eval() then extend([])): run the last token again from one back
+            self.engine.cache.truncate(self._own_slot, n_held - 1)
+            n_held -= 1
+        elif self.engine.cache.length(self._own_slot) > n_held:
+            self.engine.cache.truncate(self._own_slot, n_held)
+        sampler = self._make_sampler(params.sampler, self.seed + 1000003 * self._n_generate_calls, self.model.spec.vocab_size)
+        self._n_generate_calls += 1
+        self._cancel._start_call()
+        self._own_logits = None
+        on_token, on_finish = self._piece_callbacks(on_piece)
+        self._own_tokens = context
+        return _generate_on_slot(self.engine, sampler, self._own_slot, self._own_tokens, n_held, params,
+                                 self._stops(stop_token_ids), on_token, self._cancel._is_set, self.n_ctx, on_finish)
+
+    def chat(self, message: str, params: GenerateParams = GenerateParams(),
+             on_piece: Optional[Callable[[Piece], bool]] = None) -> GenerateResult:
+        """One chat turn: ``message`` joins the session's conversation as a user
+        turn in ChatML (the previous reply is closed first; the system prompt
+        opens the first turn) and the reply is generated.  ``ContextFull``
+        means that the turn does not fit; ``reset()`` makes room
+        (crates/nncpu/src/session/engine.rs:300-328)."""
+        if self.tokenizer is None:
+            raise InvalidArgument("chat needs a tokenizer: Session(model, params, tokenizer=...)")
+        end = self.tokenizer.special_id("<|im_end|>")
+        closed = bool(self._own_tokens) and self._own_tokens[-1] == end
+        turn = chat_turn(self.tokenizer, message, not self._own_tokens, closed, self.params.system_prompt,
+                         self.params.reply_open)
+        return self.extend(turn, params, on_piece)
 
     def reset(self) -> None:
         """Forgets this session's own sequence (crates/nncpu/src/session/engine.rs:201-209)."""
         if self._own_slot is not None:
             self.engine.free_slot(self._own_slot)
         self._own_slot = None
+        self._own_tokens = []
         self._own_logits = None

@@ -124,7 +124,7 @@ def test_window_group_gives_pages_back():
 def test_state_is_per_slot_and_cleared_on_start():
     c = make(state=True)
     st = c.state(1)
-    assert st.shape == (c.n_slots, 3) and c.state(0) is None
+    assert st.shape == (c.n_slots + 1, 3) and c.state(0) is None   # one spare row for padding
     a, b = c.alloc_slot(), c.alloc_slot()
     c.prepare([a, b], [4, 4])
     st[a] = 1.0
@@ -191,3 +191,20 @@ def test_sizes():
     assert Cache([(KVRequest(1, 16), None)], [None], 65, torch.float32, "cpu").max_tokens == 128
     with pytest.raises(InvalidArgument):
         Cache([(KVRequest(1, 16), None)], [None], 0, torch.float32, "cpu")
+
+
+def test_rollback_undoes_a_prepare_whose_step_did_not_happen():
+    c = make()
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.prepare([a], [70])
+    c.commit([a], [70])
+    before = (c.groups[0].pool.n_free, {s: list(t) for s, t in c.groups[0].tables.items()})
+    c.prepare([a, b], [PAGE * 2, 10])          # a grows by two pages, b takes its first
+    assert c.groups[0].pool.n_free == before[0] - 3
+    c.rollback([a, b])
+    assert (c.groups[0].pool.n_free, {s: list(t) for s, t in c.groups[0].tables.items()}) == before
+    c.check()
+    c.prepare([a, b], [1, 1])                  # and the cache goes on as if nothing had been
+    c.commit([a, b], [1, 1])
+    assert c.length(a) == 71 and c.length(b) == 1
+    c.check()

@@ -111,3 +111,27 @@ def test_load_config_errors(tmp_path):
     (tmp_path / "config.json").write_text("{not json")
     with pytest.raises(BadFormat, match="not JSON"):
         load_config(tmp_path)
+
+
+def test_generation_config_adds_its_stop_tokens(tmp_path):
+    d = dict(TINY["B"], eos_token_id=382)
+    (tmp_path / "config.json").write_text(json.dumps(d))
+    assert load_config(tmp_path).eos_token_id == (382,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [383, 382], "temperature": 0.6}))
+    cfg = load_config(tmp_path)
+    assert cfg.eos_token_id == (382, 383) and cfg.model_spec().stop_token_ids == (382, 383)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 5}))
+    assert load_config(tmp_path).eos_token_id == (382, 5)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": ["x"]}))
+    with pytest.raises(BadFormat, match="generation_config"):
+        load_config(tmp_path)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 99999}))
+    with pytest.raises(BadFormat, match="outside the vocabulary"):
+        load_config(tmp_path)
+
+
+def test_written_config_holds_no_key_without_a_value():
+    for name in TINY:
+        d = tiny_config(name).to_dict()
+        assert all(v is not None for v in d.values()), [k for k, v in d.items() if v is None]
+    assert "sliding_window" in tiny_config("C").to_dict() and "sliding_window" not in tiny_config("A").to_dict()

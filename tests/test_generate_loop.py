@@ -251,3 +251,63 @@ def test_running_ahead_when_one_sequence_stops_the_others_keep_their_step():
     assert ahead[0].stop == StopReason.END_OF_TURN and ahead[1].stop == StopReason.MAX_TOKENS
     # every decode step of sequence 1 ran exactly once: prompt + 6 steps for 7 tokens
     assert sum(1 for s in eng.steps[1:]) >= 6
+
+
+# -- a step whose kernel gave up, sequences that end, a sequence that continues on a slot of the caller's ----------
+
+def test_a_step_that_did_not_finish_raises_and_every_slot_goes_back():
+    from nncpu_b200.errors import ExtensionError
+
+    class GivingUp(FakeEngine):
+        def check_status(self):
+            if len(self.steps) == 3:
+                raise ExtensionError("a kernel gave up waiting (status 2)")
+    eng = GivingUp()
+    seen = []
+    with pytest.raises(ExtensionError, match="gave up"):
+        generate(eng, Script(), [[1, 2], [3]], GenerateParams(8, GREEDY), on_token=lambda i, t: seen.append(t) or True)
+    assert not eng.held
+    assert len(seen) == 4                     # the tokens of the third step were never handed out
+
+    class GivingUpAhead(AheadEngine):
+        def check_status(self):
+            if len(self.steps) == 4:
+                raise ExtensionError("a kernel gave up waiting (status 2)")
+    eng = GivingUpAhead()
+    chooser = Script()
+    chooser.greedy_on_device = True
+    with pytest.raises(ExtensionError):
+        generate(eng, chooser, [[1, 2], [3]], GenerateParams(8, GREEDY))
+    assert not eng.held
+
+
+def test_on_finish_is_called_once_per_sequence_when_it_stops():
+    done = []
+    res, _ = run([[1], [2, 2], [3, 3, 3]], max_tokens=5, stops=(103,), on_finish=done.append)
+    # sequence 2 (three prompt tokens) writes 103 as its first token and ends there, before the others
+    assert res[2].stop == StopReason.END_OF_TURN and res[2].n_generated == 0 and done == [2, 1, 0]
+    flag = iter([False, False, True])
+    done = []
+    res, _ = run([[1], [2]], cancelled=lambda: next(flag), on_finish=done.append)
+    assert all(r.stop == StopReason.CANCELLED for r in res) and sorted(done) == [0, 1]
+
+
+def test_continuing_on_a_slot_of_the_callers():
+    from nncpu_b200.engine.generate import generate_on_slot
+    eng = FakeEngine()
+    slot = eng.alloc_slot()
+    eng.step([slot], [[7, 8, 9]])                       # three tokens are in the cache already
+    context = [7, 8, 9, 10, 11]                         # two more wait
+    r = generate_on_slot(eng, Script(), slot, context, 3, GenerateParams(3, GREEDY))
+    assert eng.steps[1] == [2] and r.n_prompt == 2 and r.n_generated == 3 and r.stop == StopReason.MAX_TOKENS
+    assert context == [7, 8, 9, 10, 11] + r.tokens      # the caller's context grew in place
+    assert list(eng.held) == [slot] and eng.held[slot] == len(context) - 1   # kept; the last token waits
+    with pytest.raises(InvalidArgument, match="nothing to continue"):
+        generate_on_slot(eng, Script(), slot, context, len(context), GenerateParams(1, GREEDY))
+    with pytest.raises(ContextFull):
+        generate_on_slot(eng, Script(), slot, list(range(64)), 3, GenerateParams(1, GREEDY), n_ctx=64)
+    # a stop token joins the context (it ends the reply) but not the result
+    n = len(context)
+    r = generate_on_slot(eng, Script({(0, n + 1): 999}), slot, context, n - 1, GenerateParams(0, GREEDY), (999,))
+    assert r.stop == StopReason.END_OF_TURN and r.n_generated == 1 and context[-1] == 999
+    eng.free_slot(slot)

@@ -185,12 +185,12 @@ def test_prenorm_block(dtype, tol):
     h = r(P.rmsnorm(x, w["n2.weight"], 2e-6))
     x = x + P.linear(P.swiglu(P.linear(h, w["ff.gate_proj.weight"]), P.linear(h, w["ff.up_proj.weight"])),
                      w["ff.down_proj.weight"])
-    cache = Cache([(block.mixer.kv_request(), None)], [None], 64, dtype, DEV)
+    cache = Cache(block.cache_requests(), [None], 64, dtype, DEV)
     slot = cache.alloc_slot()
     cache.prepare([slot], [T])
     ctx = make_context(cache, [slot], [[0] * T], [[]])
     residual = x0.to(DEV).clone()
     k, v = cache.kv(0)
-    block.forward(ctx, residual, EntryCache(k, v, ctx.block_tables[0], True, None))
+    block.forward(ctx, residual, [EntryCache(k, v, ctx.block_tables[0], True, None)])
     assert residual.dtype == torch.float32          # the residual stream stays in 32-bit
     check(residual, x, tol, "pre-norm block")
