@@ -81,6 +81,8 @@ struct GemmParams {
     int vec;         // rows of `out` may be written 16 bytes at a time
     float* scratch;  // partial tiles of products that deal k-blocks out evenly: two slots of [BN][128] floats per block
     int* status;
+    unsigned long long wait_ns;  // limit of every mbarrier wait of gemm_bf16_kernel; 0: the default (2 s)
+    int tx_extra;      // bytes added to what a stage's barrier expects (the wait probe only: they never arrive)
     QkvParams qkv;     // epilogue kQkv only
 };
 
@@ -213,6 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = p.tiles_a * p.tiles_b;
+    const unsigned long long limit = p.wait_ns ? p.wait_ns : kWaitLimitNs;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -246,12 +249,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const int m0 = (w % p.tiles_a) * kBlockM, n0 = (w / p.tiles_a) * BN;
                 for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
                     const int s = kb_run % kStages;
-                    if (!mbar_wait(&empty[s], ((kb_run / kStages) & 1) ^ 1)) {
+                    if (!mbar_wait(&empty[s], ((kb_run / kStages) & 1) ^ 1, limit)) {
                         atomicExch(p.status, kTimeoutEmpty);
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&full[s], kBytesA + kBytesB);
+                    mbar_expect_tx(&full[s], kBytesA + kBytesB + p.tx_extra);
                     tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
                     tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                     issued = kb_run + 1;
@@ -259,7 +262,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
             if (!ok) {
                 // let the copies already in flight land before the block gives up its shared memory
-                for (int r = max(0, issued - kStages); r < issued; ++r) mbar_wait(&full[r % kStages], (r / kStages) & 1);
+                for (int r = max(0, issued - kStages); r < issued; ++r) mbar_wait(&full[r % kStages], (r / kStages) & 1, limit);
             }
         }
     } else if (warp == 1) {
@@ -269,7 +272,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             bool ok = true;
             for (int w = blockIdx.x; w < n_tiles && ok; w += gridDim.x, ++it) {
                 const int buf = it & 1;
-                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1)) {
+                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, limit)) {
                     atomicExch(p.status, kTimeoutAccumEmpty);
                     break;
                 }
@@ -277,7 +280,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kAccCols);
                 for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
                     const int s = kb_run % kStages;
-                    if (!mbar_wait(&full[s], (kb_run / kStages) & 1)) {
+                    if (!mbar_wait(&full[s], (kb_run / kStages) & 1, limit)) {
                         atomicExch(p.status, kTimeoutFull);
                         ok = false;
                         break;
@@ -305,7 +308,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int m0 = (w % p.tiles_a) * kBlockM, n0 = (w / p.tiles_a) * BN;
             const int a_row = m0 + row_in_tile;
             const int buf = it & 1;
-            if (!mbar_wait(&acc_full[buf], (it >> 1) & 1)) {
+            if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, limit)) {
                 if (lane == 0) atomicExch(p.status, kTimeoutAccumFull);
                 break;
             }
@@ -1283,22 +1286,46 @@ extern "C" int nncpu_linear_tc_qkv(const void* X, const void* W, int M, int K, i
     return launch_pair<6, kQkv>(ma, mb, p, stream);
 }
 
+// The library's check of its own failure path: one 128 x 256 tile of X[128, K] . W[256, K]^T through the persistent
+// kernel, whose stage barriers are told to expect 16 bytes more than the copies bring and whose waits are limited to
+// `limit_ms` instead of two seconds.  Every role of the block runs into its limit, the copies in flight are waited
+// for, tensor memory is freed, and the kernel returns with *status set: nothing traps, faults or waits without
+// bound, and the workspace serves the next product as before.  `out` (float [128, 256]) is not written.
+extern "C" int nncpu_linear_tc_wait_probe(const void* X, const void* W, float* out, int K, int limit_ms, int* status,
+                                          void* stream_) {
+    NN_CHECK(K >= 64 && K % 64 == 0 && K <= 4096, "gemm wait probe: K %d (a multiple of 64 up to 4096)", K);
+    NN_CHECK(limit_ms >= 1 && limit_ms <= 1000, "gemm wait probe: a limit of %d ms (1 to 1000)", limit_ms);
+    NN_CHECK(X && W && out && status, "gemm wait probe: operands and the status word are needed");
+    NN_CHECK(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm wait probe: operands must be 16-byte aligned");
+    GemmParams p{};
+    p.K = K;
+    p.kb_total = K / kBlockK;
+    p.out = out; p.out_dt = DT_F32; p.ldc = 256; p.status = status;
+    p.rows_a = 128; p.rows_b = 256; p.tiles_a = 1; p.tiles_b = 1; p.splits = 1;
+    p.wait_ns = (unsigned long long)limit_ms * 1000000ull;
+    p.tx_extra = 16;
+    CUtensorMap ma, mb;
+    if (int e = g_maps.get(&ma, X, 128, K, K, kBlockM)) return e;
+    if (int e = g_maps.get(&mb, W, 256, K, K, 256)) return e;
+    return launch<256, 4, kPlain>(ma, mb, p, 1, (cudaStream_t)stream_);
+}
+
 // C[M, N] (+)= X[M, K] . W[N, K]^T + bias, or with epilogue 1: C[M, N/2] = silu(gate) * up for W rows
 // interleaved in blocks of 8 (8 gate rows, the 8 up rows of the same outputs, ...).  X and W are
 // bfloat16; C is float or bfloat16 with row stride ldc.  `scratch` (nncpu_linear_tc_scratch_floats
 // floats) serves the products that deal their k-blocks out evenly; launches that share it must not
 // overlap on the GPU.  `status` is a device word that a kernel sets when one of its bounded waits ran out.
-// 1: products of 512 or more tokens run on pairs of SMs (256 x 256 tiles); 0: one SM per 128 x 256 tile.
-static int pair_mode = 1;
-extern "C" void nncpu_linear_tc_set_pair_mode(int on) { pair_mode = on; }
-// 1: products of 65 to 256 tokens cut their work evenly over the SMs (stream-K), fewer tokens take a cluster per
-// output tile; 2: stream-K from 17 tokens on; 0: never.
-static int streamk_mode = 1;
-extern "C" void nncpu_linear_tc_set_streamk_mode(int on) { streamk_mode = on; }
+// `plan` chooses among the kernels where a measurement or a test wants another one than the sizes would get:
+// 0 the default (products of 512 or more tokens on pairs of SMs with 256 x 256 tiles; 65 to 256 tokens with their
+// k-blocks dealt out evenly over the SMs; 17 to 64 tokens a cluster per output tile); kPlanEvenFrom17: dealt out
+// evenly from 17 tokens on; kPlanNeverEven: never dealt out evenly; kPlanNoPairs: one SM per 128 x 256 tile.
+enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4 };
 
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
-                               int N, int K, int lda, int ldc, int accumulate, int epilogue, float* scratch,
+                               int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, float* scratch,
                                int* status, void* stream_) {
+    const int streamk_mode = (plan & kPlanNeverEven) ? 0 : (plan & kPlanEvenFrom17) ? 2 : 1;
+    const int pair_mode = (plan & kPlanNoPairs) ? 0 : 1;
     cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(nncpu_linear_tc_supported(M, N, K, lda),
              "gemm: M %d, N %d, K %d, lda %d: K and lda must be multiples of 8 for the tensor-core path", M, N, K, lda);

@@ -61,14 +61,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-// Bounded wait: false when two seconds passed without the phase completing.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: false when `limit_ns` (two seconds unless the caller says otherwise) passed without the phase
+// completing.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     while (true) {
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > kWaitLimitNs) return false;
+        if (global_ns() - t0 > limit_ns) return false;
     }
 }
 

@@ -66,12 +66,13 @@ def generate(engine, chooser, prompts: Sequence[Sequence[int]], params: Generate
              stop_token_ids: Sequence[int] = (), on_token: Optional[Callable[[int, int], bool]] = None,
              cancelled: Callable[[], bool] = lambda: False, max_batch: int = 64,
              n_ctx: Optional[int] = None, n_pages: Optional[int] = None,
-             on_finish: Optional[Callable[[int], None]] = None) -> List[GenerateResult]:
+             on_finish: Optional[Callable[[int], None]] = None, run_ahead: bool = True) -> List[GenerateResult]:
     """Generates a continuation for every prompt.  ``chooser.choose(logits,
     indices)`` picks one token per logits row; ``on_token(index, token)`` is
     called for every generated token and may return False to stop that
     sequence; ``on_finish(index)`` is called once when a sequence has stopped.
-    Results come in the order of the prompts."""
+    ``run_ahead`` False keeps every step behind the host's decisions (the
+    tokens are the same either way).  Results come in the order of the prompts."""
     n_ctx = n_ctx or engine.max_seq_len
     stops = frozenset(int(t) for t in stop_token_ids)
     if not prompts:
@@ -88,7 +89,7 @@ def generate(engine, chooser, prompts: Sequence[Sequence[int]], params: Generate
     results: List[Optional[GenerateResult]] = [None] * len(prompts)
     for batch in batches:
         _run_batch(engine, chooser, [(i, list(prompts[i])) for i in batch], params, stops, on_token, cancelled,
-                   n_ctx, results, on_finish)
+                   n_ctx, results, on_finish, run_ahead=run_ahead)
     return results  # type: ignore[return-value]
 
 
@@ -114,13 +115,14 @@ def generate_on_slot(engine, chooser, slot: int, tokens: List[int], n_evaluated:
 
 
 def _run_batch(engine, chooser, members, params, stops, on_token, cancelled, n_ctx, results, on_finish=None,
-               held=None) -> None:
+               held=None, run_ahead=True) -> None:
     """``held``: index -> (slot, tokens already in the cache) for sequences that continue on a slot of the
     caller's, which is not given back."""
     held = held or {}
     check_status = getattr(engine, "check_status", None) or (lambda: None)
     live = []  # [index, slot, tokens so far (prompt + generated), result]
-    on_device = ((getattr(chooser, "chooses_on_device", False) or getattr(chooser, "greedy_on_device", False))
+    on_device = (run_ahead
+                 and (getattr(chooser, "chooses_on_device", False) or getattr(chooser, "greedy_on_device", False))
                  and all(hasattr(engine, a) for a in ("choice_buffer", "fetch_choices", "step_again")))
 
     def settle(rows, chosen):

@@ -64,6 +64,6 @@ class translating_oom:
             return False
         import torch
         if issubclass(kind, torch.OutOfMemoryError):
-            first = str(err).split(". ")[0]
-            raise OutOfMemory(f"{self.what}: the device has no room ({first})") from None
+            said = str(err).split(". GPU")[0][:200]       # the allocator's own sentence with the size it tried
+            raise OutOfMemory(f"{self.what}: the device has no room ({said})") from None
         return False

@@ -125,26 +125,36 @@ class GemmWorkspace:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
 
-def set_streamk_mode(mode: int) -> None:
-    """How products of 17 to 256 tokens are cut: 1 (default) evenly over the SMs from 65 tokens on and a
-    cluster per output tile below, 2 evenly from 17 tokens on, 0 never evenly.  For measurements and tests."""
-    library.load("gemm_sm100").nncpu_linear_tc_set_streamk_mode(int(mode))
-
+# Which kernel a tensor-core product runs with, where a measurement or a test wants another than its sizes would get.
+PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4}
 
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 
-def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = False, epilogue: str = "plain") -> None:
+def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = False, epilogue: str = "plain",
+              plan: str = "auto") -> None:
     """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16.  With
     ``epilogue="swiglu"`` the rows of w hold gate and up rows interleaved in
-    blocks of 8 and out [m, n/2] receives silu(gate) * up."""
+    blocks of 8 and out [m, n/2] receives silu(gate) * up.  ``plan``: "auto",
+    or for measurements and tests "even_from_17" (17 to 64 tokens deal their
+    k-blocks out evenly like 65 to 256), "never_even", "no_pairs"."""
     m, k = x.shape
     n = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert w.shape[1] == k and out.shape == (m, n // 2 if epilogue == "swiglu" else n)
     _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
           _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
-          _ptr(workspace.scratch), _ptr(workspace.status), _stream())
+          _i(PLANS[plan]), _ptr(workspace.scratch), _ptr(workspace.status), _stream())
+
+
+def linear_tc_wait_probe(x, w, out, workspace: GemmWorkspace, limit_ms: int = 5) -> None:
+    """The library's check of its own failure path: one tile of x [128, K] . w [256, K]^T whose copies are
+    expected to bring more bytes than they do, with every wait limited to ``limit_ms``.  The kernel gives up in
+    order, frees what it holds and sets the workspace's status word; ``out`` is not written."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.float32
+    assert x.shape[0] == 128 and w.shape[0] == 256 and x.shape[1] == w.shape[1] and out.shape == (128, 256)
+    _call("gemm_sm100", "nncpu_linear_tc_wait_probe", _ptr(x), _ptr(w), _ptr(out), _i(x.shape[1]), _i(limit_ms),
+          _ptr(workspace.status), _stream())
 
 
 def linear_tc_qkv_supported(x, n_heads: int, n_kv: int, head_dim: int) -> bool:

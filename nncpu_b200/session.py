@@ -30,7 +30,7 @@ import torch
 from .cache import PAGE
 from .engine.generate import generate as _generate, generate_on_slot as _generate_on_slot
 from .engine.step import Engine
-from .errors import ContextFull, InvalidArgument
+from .errors import ContextFull, InvalidArgument, NncpuError
 from .sampling import GenerateParams, GenerateResult, Sampler, SamplerParams
 from .text import TextStream, chat_turn, end_token_ids
 
@@ -52,6 +52,7 @@ class SessionParams:
     max_batch: int = 8
     system_prompt: str = ""
     reply_open: str = ""
+    run_ahead: bool = True      # launch each decode step on the device's own choices before the host reads them
 
 
 @dataclass(frozen=True)
@@ -128,7 +129,8 @@ class Session:
         # one slot's worth of pages is kept for the one-sequence calls
         return _generate(self.engine, sampler, prompts, params, stops, on_token, self._cancel._is_set,
                          max_batch=self.params.max_batch, n_ctx=self.n_ctx,
-                         n_pages=self.engine.n_pages - (self.n_ctx + PAGE - 1) // PAGE, on_finish=on_finish)
+                         n_pages=self.engine.n_pages - (self.n_ctx + PAGE - 1) // PAGE, on_finish=on_finish,
+                         run_ahead=self.params.run_ahead)
 
     def _stops(self, stop_token_ids):
         """The configuration's end-of-sequence ids and, with a tokenizer, the end markers its vocabulary
@@ -178,8 +180,19 @@ class Session:
         waiting = self._own_tokens[self.n_past():] + [int(t) for t in tokens]
         # a copy: a one-token step returns a view of its decode graph's buffer, which the next step of that
         # size (this session's generate() included) overwrites
-        self._own_logits = self.engine.step([self._own_slot], [waiting]).clone()
-        self.engine.check_status()
+        held = self.n_past()
+        try:
+            self._own_logits = self.engine.step([self._own_slot], [waiting]).clone()
+            self.engine.check_status()
+        except BaseException:
+            # the sequence stays what it was before the call (crates/nncpu/src/session/engine.rs:370-374)
+            self._own_logits = None
+            try:
+                if self.engine.cache.length(self._own_slot) > held:
+                    self.engine.cache.truncate(self._own_slot, held)
+            except NncpuError:
+                self.reset()        # a window or a state that cannot go back: the sequence starts over
+            raise
         self._own_tokens += [int(t) for t in tokens]
 
     def logits(self) -> torch.Tensor:

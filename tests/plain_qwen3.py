@@ -139,7 +139,12 @@ def rmsnorm(x: np.ndarray, gamma: np.ndarray, eps: float) -> np.ndarray:
 def linear(x: np.ndarray, w: np.ndarray, b=None) -> np.ndarray:
     """y = W x (+ b): rows of W are outputs (crates/nncpu/src/runtime.rs:98-108,
     crates/nncpu/src/model/forward.rs:238-272)."""
-    y = x.astype(F64) @ w.astype(F64).T
+    xd = x.astype(F64)
+    if w.shape[0] * w.shape[1] > (1 << 26):
+        # a large matrix is widened and multiplied a block of outputs at a time (the same sums; less memory)
+        y = np.concatenate([xd @ np.asarray(w[i:i + 8192], dtype=F64).T for i in range(0, w.shape[0], 8192)], axis=-1)
+    else:
+        y = xd @ np.asarray(w, dtype=F64).T
     if b is not None:
         y = y + b.astype(F64)
     return y.astype(F32)
@@ -258,14 +263,15 @@ class PlainQwen3:
             x = x + self.mlp_block(li, rmsnorm(x, w[p + "post_attention_layernorm.weight"], c.eps))
         return rmsnorm(x, w["model.norm.weight"], c.eps)
 
-    def logits(self, tokens) -> np.ndarray:
-        """Logits [T, vocab] at every position of one whole sequence; the
-        output matrix is the embedding when the file has none
-        (crates/nncpu/src/model/forward.rs:974-985,
+    def logits(self, tokens, rows=None) -> np.ndarray:
+        """Logits [T, vocab] at every position of one whole sequence (or at
+        the positions ``rows``); the output matrix is the embedding when the
+        file has none (crates/nncpu/src/model/forward.rs:974-985,
         crates/nncpu/src/model/mod.rs:367-372)."""
         w = self.w
         head = w["model.embed_tokens.weight"] if self.cfg.tied else w["lm_head.weight"]
-        return linear(self.round(self.hidden(tokens)), head)
+        h = self.hidden(tokens)
+        return linear(self.round(h if rows is None else h[list(rows)]), head)
 
 
 # --------------------------------------------------------------------------

@@ -132,24 +132,21 @@ def test_linear_tensor_core_with_work_cut_evenly(ops, m, n, k):
     b = torch.randn(n, generator=g).to(DEV)
     ws = ops.GemmWorkspace(DEV)
     want = (x.double() @ w.double().T).float()
-    ops.set_streamk_mode(2)
-    try:
-        out = torch.full((m, n), 9.0, device=DEV)
-        ops.linear_tc(x, w, b, out, ws)
-        check(out, want + b, 1e-5, "float32 out with bias")
-        again = torch.full((m, n), 9.0, device=DEV)
-        ops.linear_tc(x, w, b, again, ws)
-        assert torch.equal(out, again)
-        acc = torch.full((m, n), 0.5, dtype=torch.bfloat16, device=DEV)
-        ops.linear_tc(x, w, None, acc, ws, accumulate=True)
-        check(acc, want + 0.5, 8e-3, "accumulate in bfloat16")
-        if n % 16 == 0:
-            gated = torch.full((m, n // 2), 9.0, device=DEV)
-            ops.linear_tc(x, w, None, gated, ws, epilogue="swiglu")
-            y = want.cpu().numpy().reshape(m, -1, 2, 8)
-            check(gated, P.swiglu(y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)), 1e-5, "gated epilogue")
-    finally:
-        ops.set_streamk_mode(1)
+    plan = "even_from_17"
+    out = torch.full((m, n), 9.0, device=DEV)
+    ops.linear_tc(x, w, b, out, ws, plan=plan)
+    check(out, want + b, 1e-5, "float32 out with bias")
+    again = torch.full((m, n), 9.0, device=DEV)
+    ops.linear_tc(x, w, b, again, ws, plan=plan)
+    assert torch.equal(out, again)
+    acc = torch.full((m, n), 0.5, dtype=torch.bfloat16, device=DEV)
+    ops.linear_tc(x, w, None, acc, ws, accumulate=True, plan=plan)
+    check(acc, want + 0.5, 8e-3, "accumulate in bfloat16")
+    if n % 16 == 0:
+        gated = torch.full((m, n // 2), 9.0, device=DEV)
+        ops.linear_tc(x, w, None, gated, ws, epilogue="swiglu", plan=plan)
+        y = want.cpu().numpy().reshape(m, -1, 2, 8)
+        check(gated, P.swiglu(y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)), 1e-5, "gated epilogue")
     assert int(ws.status.item()) == 0
 
 

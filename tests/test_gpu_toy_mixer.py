@@ -51,15 +51,22 @@ class DecayMixer(Mixer):
         return StateRequest((self.spec.hidden_size,), torch.float32)
 
     def forward(self, ctx, x, residual, cache):
-        states = torch.empty(ctx.n_tokens, self.spec.hidden_size, device=x.device, dtype=torch.float32)
-        slots, at = ctx.seq_slots.tolist(), 0
-        for b, n in enumerate(ctx.q_lens):           # a toy: plain torch, token by token
-            s = cache.state[slots[b]]
-            for t in range(at, at + n):
-                s = self.spec.decay * s + x[t].float()
-                states[t] = s
-            cache.state[slots[b]] = s
-            at += n
+        # Tensor operations only, on the step's device metadata, so that a captured decode graph replays it:
+        # states[t] = decay^(i + 1) * state + sum_{j <= i} decay^(i - j) * x[first + j] for the i-th new token of
+        # its sequence.  Padding rows (sequence and slot -1) land on the state area's spare last row.
+        n, d = ctx.n_tokens, self.spec.decay
+        seq, flat = ctx.tok_seq[:n].long(), torch.arange(n, device=x.device)
+        first = ctx.cu_seqlens.long()[seq.clamp(min=0)]                      # first flat token of each token's sequence
+        lag = (flat[:, None] - flat[None, :]).clamp(min=0).float()
+        same = (seq[:, None] == seq[None, :]) & (flat[None, :] <= flat[:, None])
+        mix = torch.where(same, torch.pow(torch.full((), d, device=x.device), lag), torch.zeros((), device=x.device))
+        slots = ctx.seq_slots.long()
+        start = cache.state[slots][seq]                                      # [n, hidden]; seq -1 -> the last sequence's: unused
+        start = torch.where((seq >= 0)[:, None], start, cache.state[-1][None, :])
+        carry = torch.pow(torch.full((), d, device=x.device), (flat - first + 1).float())[:, None] * start
+        states = mix @ x.float() + carry
+        last = ctx.cu_seqlens.long()[1:ctx.n_seqs + 1] - 1
+        cache.state[slots] = states[last]
         self.rt.linear(states.to(x.dtype), self.w, None, residual, accumulate=True)
 
 
@@ -91,12 +98,10 @@ class RoutedFeedForward(FeedForward):
         logits = torch.empty(x.shape[0], self.spec.n_experts, device=x.device, dtype=torch.float32)
         ops.linear_simt(x, self.router, None, logits)
         choice = logits.argmax(-1)
-        for e, w in enumerate(self.experts):
-            rows = (choice == e).nonzero().flatten()
-            if rows.numel():
-                out = torch.zeros(rows.numel(), self.spec.hidden_size, device=x.device, dtype=torch.float32)
-                self.rt.linear(x[rows].contiguous(), w, None, out)
-                residual[rows] += out
+        for e, w in enumerate(self.experts):             # a toy: every expert sees every token, the choice masks
+            out = torch.empty(x.shape[0], self.spec.hidden_size, device=x.device, dtype=torch.float32)
+            self.rt.linear(x, w, None, out)
+            residual += torch.where((choice == e)[:, None], out, torch.zeros((), device=x.device))
 
 
 @register_position("toy_alibi_like")
@@ -202,26 +207,32 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
     write_safetensors(tmp_path / "model.safetensors", tensors)
     model = Model.load(tmp_path, dtype="float32")
-    engine = Engine(model, max_tokens=512, use_graphs=False)
+    engine = Engine(model, max_tokens=512)              # decode steps run as captured graphs
     cache = engine.cache
     assert [s is not None for s in cache.states] == [True, False, False, True]           # a state per run of layer 0
+    assert cache.states[0].shape == (cache.n_slots + 1, cfg.hidden)                       # and a spare row for padding
     assert cache.states[0].data_ptr() != cache.states[3].data_ptr()
     assert len(cache.groups) == 1 and cache.groups[0].k.shape[0] == 1 and not cache.owns_kv(2)
     w = {k: v.numpy() for k, v in tensors.items()}
     rs = np.random.RandomState(0)
-    a, b = rs.randint(0, 101, size=90).tolist(), rs.randint(0, 101, size=37).tolist()
-    want_a, want_b = plain_toy(cfg, w, a), plain_toy(cfg, w, b)
-    sa, sb = engine.alloc_slot(), engine.alloc_slot()
-    out = engine.step([sa, sb], [a[:70], b[:5]], [list(range(70)), list(range(5))])
-    got_a, got_b = [out[:70].clone()], [out[70:].clone()]
-    for i in range(20):                                   # one token each; the state carries on
-        out = engine.step([sa, sb], [[a[70 + i]], [b[5 + i]]])
+    a, b, c = rs.randint(0, 101, size=90).tolist(), rs.randint(0, 101, size=37).tolist(), rs.randint(0, 101, size=29).tolist()
+    want_a, want_b, want_c = plain_toy(cfg, w, a), plain_toy(cfg, w, b), plain_toy(cfg, w, c)
+    sa, sb, sc = engine.alloc_slot(), engine.alloc_slot(), engine.alloc_slot()
+    assert sa == 0                                        # a padding row that used slot 0 would spoil a's state
+    out = engine.step([sa, sb, sc], [a[:70], b[:5], c[:9]], [list(range(70)), list(range(5)), list(range(9))])
+    got_a, got_b, got_c = [out[:70].clone()], [out[70:75].clone()], [out[75:].clone()]
+    for i in range(20):                                   # one token each: three live rows in a graph of four,
+        out = engine.step([sa, sb, sc], [[a[70 + i]], [b[5 + i]], [c[9 + i]]])   # the state carries on across replays
         got_a.append(out[:1].clone())
-        got_b.append(out[1:].clone())
+        got_b.append(out[1:2].clone())
+        got_c.append(out[2:].clone())
+    g = engine.graphs.by_size[4]
+    assert g.graph is not None and g.n_kernels > 0        # captured at the first of these steps, replayed 19 times
     out = engine.step([sb], [b[25:]], [list(range(12))])  # several tokens at once on a running sequence
     got_b.append(out.clone())
     check(torch.cat(got_a), want_a, 1e-4, "toy model, sequence a")
     check(torch.cat(got_b), want_b, 1e-4, "toy model, sequence b")
+    check(torch.cat(got_c), want_c, 1e-4, "toy model, sequence c")
     # a slot that is used again starts from zero state
     engine.free_slot(sa)
     sc = engine.alloc_slot()

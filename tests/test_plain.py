@@ -104,3 +104,23 @@ def test_window_hides_far_keys(tmp_path):
     assert np.array_equal(la[3 + 157:], lb[3 + 157:])
     full = P.PlainQwen3(make_folder(tmp_path / "Cf", "C", seed=5, use_sliding_window=False))
     assert np.abs(full.logits(a)[199] - full.logits(b)[199]).max() > 0.0
+
+
+def test_two_independent_plain_implementations_agree(tmp_path):
+    """The oracle against a second plain implementation written another way (float64 PyTorch, masked-matrix
+    attention, angles by a direct power, its own file reader) on every tiny configuration: with and without
+    biases, tied and untied, windows, one key/value head for five, sizes that are no power of two; float32 and
+    bfloat16 files.  They differ by the first one's float32 rounding only."""
+    from plain_torch import TorchQwen3
+    from tiny import TINY
+    rs = np.random.RandomState(8)
+    for name in TINY:
+        for store in (torch.float32, torch.bfloat16):
+            folder = make_folder(tmp_path / f"{name}{store}", name, seed=9, store_dtype=store)
+            a, b = P.PlainQwen3(folder), TorchQwen3(folder)
+            toks = rs.randint(0, a.cfg.vocab, size=130).tolist()
+            la, lb = a.logits(toks), b.logits(toks)
+            assert la.shape == lb.shape
+            err = np.abs(la - lb).max() / np.abs(lb).max()
+            assert err < 5e-6, (name, store, err)
+            assert (la.argmax(-1) == lb.argmax(-1)).all()

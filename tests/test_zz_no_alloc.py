@@ -64,6 +64,36 @@ def test_entry_point_without_allocation_matches_the_regular_one_twice_in_a_row()
         assert torch.equal(got, want)      # the same kernel on the same inputs
 
 
+def test_stale_scratch_padding_rows_one_split_and_many_splits():
+    """What the built-in array holds from an earlier call never shows: a large call first, then a batch with a
+    padding row (zeros expected), a call with a single split (which needs no scratch at all) and one with more
+    splits than a cluster merges; each against the plain 32-bit attention kernel, not only its sibling entry."""
+    from nncpu_b200.kernels import library, ops
+    lib = library.load("attention_mma")
+    nh, nkv, hd = 8, 2, 128
+    seqs = [900, 700, 1100, 64]
+    kp, vp, table, _, _ = scatter_pages(64, nkv, hd, seqs, torch.bfloat16, seed=5)
+    n = len(seqs)
+    q = torch.randn(n, nh * hd, generator=torch.Generator().manual_seed(1)).bfloat16().to(DEV)
+    pos = torch.tensor([s - 1 for s in seqs], dtype=torch.int32, device=DEV)
+    for tok_seq, n_splits in (([0, 1, 2, 3], 16), ([0, -1, 2, 3], 3), ([0, 1, -1, 3], 1), ([0, 1, 2, 3], 12)):
+        seq = torch.tensor(tok_seq, dtype=torch.int32, device=DEV)
+        got = torch.full_like(q, 9.0)
+        rc = call_static(lib, q, kp, vp, table, seq, pos, got, nh, nkv, hd, 0, n_splits)
+        assert rc == 0, lib.last_error().decode()
+        want = torch.zeros(n, nh * hd, device=DEV)
+        live = [i for i, s in enumerate(tok_seq) if s >= 0]
+        idx = torch.tensor(live, device=DEV)
+        part = torch.empty(len(live), nh * hd, device=DEV)
+        ops.attention(q[idx].float().contiguous(), kp.float(), vp.float(), table, seq[idx].contiguous(),
+                      pos[idx].contiguous(), part, nh, nkv, hd, 1.0 / math.sqrt(hd), 0)
+        want[idx] = part
+        check(got, want, 1.5e-2, f"{n_splits} splits, rows {tok_seq}")
+        for i, s in enumerate(tok_seq):
+            if s < 0:
+                assert float(got[i].float().abs().max()) == 0.0     # a padding row is zeros whatever the array held
+
+
 def test_entry_point_without_allocation_refuses_what_does_not_fit():
     from nncpu_b200.kernels import library
     lib = library.load("attention_mma")
