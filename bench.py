@@ -127,7 +127,7 @@ def timed_decode(engine, slots, first_tokens, steps: int, warmup: int):
     return a.elapsed_time(b), mean_len, out
 
 
-def run_decode_point(model, cfg, batch: int, steps: int, warmup: int, seed: int = 0):
+def run_decode_point(model, cfg, batch: int, steps: int, warmup: int, seed: int = 0, with_phases: bool = False):
     import torch
     from nncpu_b200 import Engine
     per_seq = (CONTEXT + 63) // 64 * 64
@@ -147,11 +147,28 @@ def run_decode_point(model, cfg, batch: int, steps: int, warmup: int, seed: int 
     ms, mean_len, _ = timed_decode(engine, slots, firsts, steps, warmup)
     tok_s = batch * steps / (ms / 1e3)
     bytes_step = model.weight_bytes_per_step() + batch * mean_len * kv_bytes_per_token(cfg)
+    phases = None
+    if with_phases:
+        # the same engine, a few steps kernel by kernel under the phase profiler: where a step's time goes
+        from nncpu_b200 import perf_enable, perf_reset, perf_totals
+        for s in slots:
+            engine.cache.truncate(s, (PROMPT + CONTEXT) // 2)      # the middle of the timed range
+        room = 9
+        if room > 1:
+            toks = [[1]] * batch
+            engine.step(slots, toks)
+            perf_enable(True)
+            perf_reset()
+            for _ in range(room - 1):
+                engine.step(slots, toks)
+            phases = {k: round(v["ms"] / (room - 1), 4) for k, v in perf_totals().items()}
+            perf_enable(False)
+            perf_reset()
     for s in slots:
         engine.free_slot(s)
     del engine
     torch.cuda.empty_cache()
-    return tok_s, ms / steps, bytes_step
+    return tok_s, ms / steps, bytes_step, (mean_len - (steps + 1) / 2.0 + 1, mean_len + (steps + 1) / 2.0 - 1), phases
 
 
 def run_prefill(model, cfg, reps: int = 3):
@@ -320,7 +337,8 @@ def main() -> int:
     pf_flops = flops_prefill(cfg, PROMPT)
     launches0 = ops.launch_count()
     with ClockSampler() as clocks:
-        tok_s, ms_step, bytes_step = run_decode_point(model, cfg, BATCH, args.steps, args.warmup)
+        tok_s, ms_step, bytes_step, key_range, phases = run_decode_point(model, cfg, BATCH, args.steps, args.warmup,
+                                                                          with_phases=True)
     launches = ops.launch_count() - launches0
     points = {}
     if not args.skip_points:
@@ -329,7 +347,8 @@ def main() -> int:
     e2e = run_e2e(model, cfg, args.steps, args.warmup)
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     line = {
-        "metric": f"decode tokens/s, Qwen3-{args.model.upper()} sizes, bf16, batch 8, 2048-token prompts, context 4096",
+        "metric": f"decode tokens/s, Qwen3-{args.model.upper()} sizes, bf16, batch 8, 2048-token prompts, context 4096 "
+                  f"(timed steps read {int(key_range[0])} to {int(key_range[1])} keys per sequence)",
         "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": min(args.steps, CONTEXT - PROMPT - args.warmup - 1),
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
@@ -339,7 +358,8 @@ def main() -> int:
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
                    "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": pk["source"]},
+                   "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": pk["source"],
+                   "keys_first_timed_step": int(key_range[0]), "keys_last_timed_step": int(key_range[1])},
         "e2e": e2e,
         "gpu_launches": launches,
         "prefill": {"value": PROMPT / (prefill_ms / 1e3), "tokens": PROMPT, "ms": prefill_ms,
@@ -347,6 +367,11 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,
+        "phases": {"unit": "ms per decode step, kernel by kernel under the phase profiler (not the graph)",
+                   **(phases or {})},
+        "prefill_batched": {"tokens": BATCH * PROMPT, "ms": e2e["prefill_s"] * 1e3,
+                            "value": BATCH * PROMPT / e2e["prefill_s"],
+                            "note": "the 8 prompts of the end-to-end run as one step, host work included"},
         "clocks": clocks.summary(),
     }
     print(json.dumps(line))

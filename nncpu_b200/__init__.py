@@ -9,7 +9,7 @@ loop, sampling, and hand-written sm_100a kernels underneath.
 from .errors import (BadFormat, Cancelled, ContextFull, ExtensionError, InvalidArgument, NncpuError, OutOfMemory,
                      UnsupportedModel)
 from .engine import Engine, Model
-from .perf import perf_enable, perf_report, perf_reset, perf_totals
+from .perf import perf_enable, perf_report, perf_reset, perf_span_ms, perf_totals
 from .sampling import GenerateParams, GenerateResult, SamplerParams, StopReason
 from .session import CancelHandle, Piece, Session, SessionParams
 
@@ -18,4 +18,4 @@ __version__ = "0.1.0"
 __all__ = ["BadFormat", "Cancelled", "ContextFull", "ExtensionError", "InvalidArgument", "NncpuError",
            "OutOfMemory", "UnsupportedModel", "Engine", "Model", "GenerateParams", "GenerateResult", "SamplerParams",
            "StopReason", "CancelHandle", "Piece", "Session", "SessionParams", "perf_enable", "perf_report", "perf_reset",
-           "perf_totals", "__version__"]
+           "perf_span_ms", "perf_totals", "__version__"]

@@ -39,6 +39,8 @@ _paused = 0
 _lock = threading.Lock()
 _totals: Dict[str, List[float]] = {}        # slot -> [ns, bytes, flops, calls]
 _pending: List[Tuple[str, object, object, float, float]] = []
+_first = None                               # start event of the first scope since the last reset
+_span_ns = 0.0                              # from there to the end of the last scope read so far
 _event_pool: List[object] = []
 _MAX_PENDING = 8192
 
@@ -63,8 +65,11 @@ class _Scope:
         self.slot, self.bytes, self.flops, self.start = slot, nbytes, flops, None
 
     def __enter__(self):
+        global _first
         self.start = _event()
         self.start.record()
+        if _first is None:
+            _first = self.start
         return self
 
     def __exit__(self, *exc):
@@ -93,12 +98,15 @@ def _drain() -> None:
     if not todo:
         return
     import torch
+    global _span_ns
     torch.cuda.synchronize()
     for slot, a, b, nbytes, flops in todo:
         add(slot, a.elapsed_time(b) * 1e6, nbytes, flops)
+    if _first is not None:
+        _span_ns = max(_span_ns, _first.elapsed_time(todo[-1][2]) * 1e6)
     with _lock:
         for _, a, b, _, _ in todo:
-            if len(_event_pool) < 2 * _MAX_PENDING:
+            if len(_event_pool) < 2 * _MAX_PENDING and a is not _first:
                 _event_pool.extend((a, b))
 
 
@@ -147,9 +155,18 @@ def perf_enable(enabled: bool = True) -> None:
 
 def perf_reset() -> None:
     """Zeroes the profiler's totals; what is still in flight is dropped with them."""
+    global _first, _span_ns
     _drain()
     with _lock:
         _totals.clear()
+        _first, _span_ns = None, 0.0
+
+
+def perf_span_ms() -> float:
+    """Device time from the start of the first phase to the end of the last one since the last reset: what the
+    phases' sum falls short of it went to the seams between them (and to the host, where the device waited)."""
+    _drain()
+    return _span_ns / 1e6
 
 
 def perf_totals() -> Dict[str, dict]:
@@ -192,6 +209,9 @@ def perf_report(title: str = "", n_tokens: int = 0, peaks: Optional[dict] = None
         out.append(line.rstrip())
         total_bytes += t["bytes"]
     out.append(f"  {'TOTAL':<12} {total_ns / 1e6:>10.1f} {100.0:>6.1f}%")
+    if _span_ns > 0:
+        out.append(f"  the phases cover {100.0 * total_ns / _span_ns:.0f}% of the {_span_ns / 1e6:.1f} ms between the "
+                   f"first and the last of them")
     if total_bytes > 0:
         out.append(f"  memory traffic: {total_bytes / 2 ** 30:.2f} GB @ {total_bytes / total_ns:.1f} GB/s effective")
     if n_tokens > 0:

@@ -6,7 +6,7 @@ import torch
 
 import nncpu_b200
 from gpu_util import DEV, check
-from nncpu_b200 import Engine, Model, perf_enable, perf_report, perf_reset, perf_totals
+from nncpu_b200 import Engine, Model, perf_enable, perf_report, perf_reset, perf_span_ms, perf_totals
 from tiny import make_folder
 
 pytestmark = pytest.mark.gpu
@@ -29,9 +29,9 @@ def test_phases_add_up_and_count_the_models_bytes(dtype, hidden):
                       num_key_value_heads=4, vocab_size=32000, num_hidden_layers=4, layer_types=None,
                       use_sliding_window=False)
     model = Model.random(cfg, seed=3, dtype=dtype)
-    engine = Engine(model, max_tokens=64 * 140)
+    engine = Engine(model, max_tokens=64 * 300)
     rs = np.random.RandomState(0)
-    lens = (2000, 2100, 1800, 2011)          # long enough that the device, not the host, sets the step's time
+    lens = (2000, 2100, 1800, 2011) if dtype == "float32" else (4000, 4200, 4600, 4011, 1500)
     prompts = [rs.randint(0, 32000, size=n).tolist() for n in lens]
     slots = [engine.alloc_slot() for _ in prompts]
     plain_prefill = engine.step(slots, prompts).clone()
@@ -47,7 +47,7 @@ def test_phases_add_up_and_count_the_models_bytes(dtype, hidden):
     a.record()
     got_prefill = engine.step(slots, prompts).clone()
     b.record()
-    prefill = perf_totals()
+    prefill, prefill_span = perf_totals(), perf_span_ms()
     perf_reset()
     n_decode = 5
     c.record()
@@ -61,9 +61,10 @@ def test_phases_add_up_and_count_the_models_bytes(dtype, hidden):
     # switching the profiler on changes no result (the decode step leaves its graph for single kernels)
     assert torch.equal(got_prefill, plain_prefill)
     check(got_decode, plain_decode, 1e-5 if dtype == "float32" else 2e-2, "decode step kernel by kernel")
-    # the slots cut the step up: together they are the event-timed step, less the seams between the scopes
+    # The slots cut the step up.  From the first kernel to the last they leave out only the seams between scopes
+    # (within a tenth); the event-timed step around the call also holds the host's work before the first kernel.
     prefill_ms, step_ms = sum(t["ms"] for t in prefill.values()), a.elapsed_time(b)
-    assert 0.9 * step_ms <= prefill_ms <= 1.001 * step_ms, (prefill_ms, step_ms)
+    assert 0.9 * prefill_span <= prefill_ms <= 1.001 * prefill_span <= 1.002 * step_ms, (prefill_ms, prefill_span, step_ms)
     decode_ms, loop_ms = sum(t["ms"] for t in decode.values()), c.elapsed_time(d)
     assert decode_ms <= 1.001 * loop_ms, (decode_ms, loop_ms)
     # every product phase streamed its weights once per step
