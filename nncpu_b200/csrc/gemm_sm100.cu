@@ -31,6 +31,7 @@
 // *status and the block leaves through the common exit, which frees its
 // tensor memory.
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -83,8 +84,17 @@ struct GemmParams {
     int* status;
     unsigned long long wait_ns;  // limit of every mbarrier wait of gemm_bf16_kernel; 0: the default (2 s)
     int tx_extra;      // bytes added to what a stage's barrier expects (the wait probe only: they never arrive)
+    int a_tiled;       // the A operand is stored tile by tile: [rows / 128][K / 64][128][64], a tile 16 KB in one piece
     QkvParams qkv;     // epilogue kQkv only
 };
+
+// The copy of A's tile (rows m0 .. m0 + 127, k-block kb).  Row-major A: 128 pieces of 128 bytes, one per row, a row
+// stride apart.  A stored tile by tile: the tile's 16 KB lie together, so the copy reads memory front to back.
+__device__ __forceinline__ void load_a_tile(void* dst, const CUtensorMap* map, uint64_t* bar, const GemmParams& p, int kb,
+                                            int m0) {
+    if (p.a_tiled) tma_load_2d(dst, map, bar, 0, ((m0 / kBlockM) * p.kb_total + kb) * kBlockM);
+    else tma_load_2d(dst, map, bar, kb * kBlockK, m0);
+}
 
 // Stores up to 16 accumulator values of one thread: A row `a_row`, B rows b0 .. b0 + ncols - 1
 // (ncols below 16 only when A rows are output features).
@@ -255,7 +265,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         break;
                     }
                     mbar_expect_tx(&full[s], kBytesA + kBytesB + p.tx_extra);
-                    tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                    load_a_tile(smem_a + s * kBytesA, &map_a, &full[s], p, kb, m0);
                     tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                     issued = kb_run + 1;
                 }
@@ -435,7 +445,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         break;
                     }
                     mbar_expect_tx(&full[s], kBytesA + kBytesB);
-                    tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                    load_a_tile(smem_a + s * kBytesA, &map_a, &full[s], p, kb, m0);
                     tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                     issued = kb_run + 1;
                 }
@@ -604,6 +614,39 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
     return v;
 }
 
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
+}
+
+// Copies `bytes` of this block's shared memory into the shared memory of block `rank` of the cluster; the bytes
+// are counted by the mbarrier at `bar_local_addr` in that block.  The copy runs on its own: nothing waits here.
+__device__ __forceinline__ void bulk_copy_to_rank(uint32_t dst_local_addr, uint32_t src_addr, uint32_t bytes,
+                                                  uint32_t bar_local_addr, uint32_t rank) {
+    uint32_t dst, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(dst_local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(bar_local_addr), "r"(rank));
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "r"(src_addr), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Shared memory of the cluster kernel: the stage ring (which holds the block's partial tile once its products are
+// done), then the buffer that receives the cluster's partial sums for this block's share of the tile's columns
+// (one slot per sending block), then the barriers.
+template <int BN, int kStages>
+constexpr size_t cluster_smem_bytes() {
+    // shares of BN columns among up to 8 blocks are at most BN / S + 1 wide: S slots of that width fit BN + 8 columns
+    return 1024 + (size_t)kStages * (kBlockM * kBlockK * 2 + BN * kBlockK * 2) + (size_t)(BN + 8) * kBlockM * 4 +
+           (2 * kStages + 4) * sizeof(uint64_t) + 16;
+}
+
+// A cluster of S blocks shares one output tile: block r multiplies the r-th slice of K and owns the r-th share of
+// the tile's columns.  When its slice is done a block writes its partial tile into its own shared memory and
+// sends every owner its columns with one asynchronous bulk copy each; an owner's mbarrier counts the bytes that
+// arrive, and when all S senders' columns are there the owner adds them in sender order and runs the epilogue.
+// Nothing is read from another block's memory.  The cluster meets twice off the critical path: once before the
+// first copy (every block's shared memory and barrier exist) and once before leaving (every copy out of this
+// block's memory has landed, since every owner has seen all of its bytes).
 template <int BN, int kStages, int kEpi>
 __global__ void __launch_bounds__(kThreads)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -616,10 +659,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + kStages * kBytesA;
-    float* partial = (float*)smem;  // [BN][128], after the last tensor-core read of the stages
-    uint64_t* full = (uint64_t*)(smem_b + kStages * kBytesB);
+    float* send = (float*)smem;                           // [column][128 rows], after the last tensor-core read of the stages
+    float* recv = (float*)(smem_b + kStages * kBytesB);   // [sender][column of mine][128 rows]: at most BN + 8 columns
+    uint64_t* full = (uint64_t*)(recv + (BN + 8) * kBlockM);
     uint64_t* empty = full + kStages;
     uint64_t* acc_full = empty + kStages;
+    uint64_t* arrived = acc_full + 1;                     // counts the bytes of the partial sums sent to this block
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -628,15 +673,30 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int tile = blockIdx.x / S;
     const int m0 = (tile % p.tiles_a) * kBlockM, n0 = (tile / p.tiles_a) * BN;
     const int kb0 = (int)((long long)rank * p.kb_total / S), kb1 = (int)((long long)(rank + 1) * p.kb_total / S);
+    // columns of the tile that block r owns: [r * BN / S, (r + 1) * BN / S)
+    const int c_begin = rank * BN / S, c_end = (rank + 1) * BN / S;
+    const int cols = c_end - c_begin;
+    const int n_first = min(kStages, kb1 - kb0);   // copies that need no free stage: issued before anything else
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_full, 1);
+        mbar_init(arrived, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // S senders bring this block's columns, 128 rows of floats each
+        mbar_expect_tx(arrived, (uint32_t)(S * cols * kBlockM * 4));
+        // the first round of copies starts now, under the set-up of tensor memory
+        for (int i = 0; i < n_first; ++i) {
+            mbar_expect_tx(&full[i], kBytesA + kBytesB);
+            load_a_tile(smem_a + i * kBytesA, &map_a, &full[i], p, kb0 + i, m0);
+            tma_load_2d(smem_b + i * kBytesB, &map_b, &full[i], (kb0 + i) * kBlockK, n0);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -648,12 +708,16 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Every block of the cluster has started (its shared memory and its barrier exist) before anyone copies into
+    // it.  The wait for this arrival comes just before the copies.  The barriers' initialisation was published by
+    // its own fence above, so the arrival orders nothing else and does not flush this thread's memory operations.
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
+            int issued = n_first;
             bool ok = true;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            for (int kb = kb0 + n_first; kb < kb1; ++kb) {
                 const int i = kb - kb0, s = i % kStages;
                 if (!mbar_wait(&empty[s], ((i / kStages) & 1) ^ 1)) {
                     atomicExch(p.status, kTimeoutEmpty);
@@ -661,7 +725,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     break;
                 }
                 mbar_expect_tx(&full[s], kBytesA + kBytesB);
-                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                load_a_tile(smem_a + s * kBytesA, &map_a, &full[s], p, kb, m0);
                 tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                 issued = i + 1;
             }
@@ -690,36 +754,63 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (ok) umma_commit(acc_full);
         }
-    } else {
-        // this block's partial tile: tensor memory -> shared memory, a column at a time
-        const int quarter = warp & 3;
-        const int row_in_tile = quarter * 32 + lane;
+    }
+    // What the product is added to is asked for now, under the weight stream (plain epilogue, at most 16 columns a
+    // block: the usual case; wider shares load it in store16).
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int a_row = m0 + row_in_tile;
+    const bool early_old = kEpi == kPlain && p.swap && cols <= 16;
+    float old[16];
+    if (warp >= 2 && early_old) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int tok = n0 + c_begin + j;
+            old[j] = (p.accumulate && j < cols && tok < p.rows_b && a_row < p.rows_a)
+                         ? ld_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt) : 0.0f;
+        }
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // all blocks of the cluster are running
+    bool received = true;
+    if (warp >= 2) {
+        // this block's partial tile into its own shared memory, a column at a time (its products are done: the
+        // stage ring is free) ...
         const bool ok = kb1 > kb0 ? mbar_wait(acc_full, 0) : true;
         if (!ok && lane == 0) atomicExch(p.status, kTimeoutAccumFull);
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-            float v[16];
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
             if (ok && kb1 > kb0) {
-                tmem_ld16(taddr + (uint32_t)c0, v);
+                tmem_ld32(taddr + (uint32_t)c0, v);
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                for (int j = 0; j < 32; ++j) v[j] = 0u;
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) partial[(c0 + j) * kBlockM + row_in_tile] = v[j];
+            for (int j = 0; j < 32; ++j) send[(c0 + j) * kBlockM + row_in_tile] = __uint_as_float(v[j]);
         }
+        // ... visible to the copy engine, and when all four warps are there, one thread sends every owner its columns
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+            for (int d = 0; d < S; ++d) {
+                const int d_begin = d * BN / S, d_cols = (d + 1) * BN / S - d_begin;
+                bulk_copy_to_rank(smem_u32(recv + (size_t)rank * d_cols * kBlockM), smem_u32(send + (size_t)d_begin * kBlockM),
+                                  (uint32_t)(d_cols * kBlockM * 4), smem_u32(arrived), (uint32_t)d);
+            }
+        }
+        received = mbar_wait(arrived, 0);
+        if (!received && lane == 0) atomicExch(p.status, kTimeoutAccumEmpty);
     }
+    // This block has all it was sent; when every block of the cluster says so, no copy is still reading anybody's
+    // memory.  The wait comes at the very end.
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncwarp();
-    cluster_barrier();  // every block's partial tile is complete and visible in the cluster
-    if (warp >= 2) {
-        const int quarter = warp & 3;
-        const int row_in_tile = quarter * 32 + lane;
-        const int a_row = m0 + row_in_tile;
-        const int cols = BN / S;                 // this block's share of the tile's columns
-        const int c_begin = rank * cols;
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");   // a meeting in time only: no data rides on it
+    if (warp >= 2 && received) {
 #pragma unroll 1
         for (int c0 = 0; c0 < cols; c0 += 16) {
             const int n = min(16, cols - c0);
@@ -729,15 +820,24 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int r = 0; r < S; ++r) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    if (j < n)
-                        v[j] += ld_cluster_f32(smem_u32(&partial[(c_begin + c0 + j) * kBlockM + row_in_tile]), (uint32_t)r);
+                    if (j < n) v[j] += recv[(r * cols + c0 + j) * kBlockM + row_in_tile];
             }
-            store16<kEpi>(p, a_row, n0 + c_begin + c0, v, n);
+            if (early_old) {
+                // C[token, a_row] = (product + bias) + what was there, as store16 does for this layout
+                const float b = p.bias ? ld_f(p.bias, min(a_row, p.rows_a - 1), p.bias_dt) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = n0 + c_begin + j;
+                    if (j < n && tok < p.rows_b && a_row < p.rows_a)
+                        st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, (v[j] + b) + old[j]);
+                }
+            } else {
+                store16<kEpi>(p, a_row, n0 + c_begin + c0, v, n);
+            }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncwarp();
-    cluster_barrier();  // nobody leaves while its partial tile may still be read
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
@@ -1155,7 +1255,7 @@ int dispatch_streamk(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmP
 
 template <int BN, int kStages, int kEpi>
 int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
-    constexpr size_t smem = smem_bytes<BN, kStages>();
+    constexpr size_t smem = cluster_smem_bytes<BN, kStages>();
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_cluster_kernel<BN, kStages, kEpi>,
@@ -1214,10 +1314,10 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cud
 template <int kEpi>
 int dispatch_cluster(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
     switch (bn) {
+        // stages chosen so that two blocks share an SM up to 64 tokens (ring + receive buffer below 110 KB)
         case 32: return launch_cluster<32, 4, kEpi>(ma, mb, p, stream);
-        case 64: return launch_cluster<64, 4, kEpi>(ma, mb, p, stream);
-        case 128: return launch_cluster<128, 4, kEpi>(ma, mb, p, stream);
-        default: return launch_cluster<256, 4, kEpi>(ma, mb, p, stream);
+        case 64: return launch_cluster<64, 3, kEpi>(ma, mb, p, stream);
+        default: return launch_cluster<128, 3, kEpi>(ma, mb, p, stream);
     }
 }
 
@@ -1322,8 +1422,8 @@ extern "C" int nncpu_linear_tc_wait_probe(const void* X, const void* W, float* o
 enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4 };
 
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
-                               int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, float* scratch,
-                               int* status, void* stream_) {
+                               int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, int w_tiled,
+                               float* scratch, int* status, void* stream_) {
     const int streamk_mode = (plan & kPlanNeverEven) ? 0 : (plan & kPlanEvenFrom17) ? 2 : 1;
     const int pair_mode = (plan & kPlanNoPairs) ? 0 : 1;
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -1350,9 +1450,17 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         p.swap = 1;
         bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
         p.rows_a = N; p.rows_b = M;
-        if (int e = g_maps.get(&ma, W, N, K, K, kBlockM)) return e;
+        if (w_tiled) {
+            // W is stored as [ceil(N / 128)][ceil(K / 64)][128][64], padded with zeros: a tile is 16 KB in one piece
+            p.a_tiled = 1;
+            const int rows = ((N + kBlockM - 1) / kBlockM) * p.kb_total * kBlockM;
+            if (int e = g_maps.get(&ma, W, rows, kBlockK, kBlockK, kBlockM)) return e;
+        } else {
+            if (int e = g_maps.get(&ma, W, N, K, K, kBlockM)) return e;
+        }
         if (int e = g_maps.get(&mb, X, M, K, lda, bn)) return e;
     } else {
+        NN_CHECK(!w_tiled, "gemm: weights stored tile by tile serve products of at most 256 tokens (M %d)", M);
         p.swap = 0;
         bn = N >= 256 ? 256 : 128;
         p.rows_a = M; p.rows_b = N;
@@ -1384,13 +1492,19 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         return epilogue == kSwiglu ? dispatch_streamk<kSwiglu>(bn, ma, mb, p, stream)
                                    : dispatch_streamk<kPlain>(bn, ma, mb, p, stream);
     }
-    if (p.swap && bn >= 32) {
-        // Few tokens, wide token tile: a cluster per output tile cuts K into 2, 4 or 8 slices, as many as it
-        // takes to put a block on most SMs, with at least 4 k-blocks per slice.
-        int s = 1;
-        while (s < 8 && n_tiles * s < sm_count() && p.kb_total / (2 * s) >= 4 && bn / (2 * s) >= 1) s *= 2;
-        p.splits = s;
-        if (s > 1)
+    if (p.swap && bn >= 32 && bn <= 128 && n_tiles < sm_count()) {
+        // Few tokens, fewer tiles than SMs: a cluster of S blocks shares an output tile, each block a slice of K.
+        // S is the largest cluster (up to 8, at least 4 k-blocks a slice) whose blocks all run at once with room
+        // to spare: clusters are placed inside one GPC, and a grid that counts on the last free places leaves
+        // whole clusters waiting (measured at 64 tokens on the Qwen3-8B layer sizes: 48 tiles take 5 blocks each,
+        // 17.3 us, where 6 take 25 us; 32 tiles take 8).  With as many tiles as SMs or more, whole tiles per block
+        // stream as fast and need no exchange.
+        const int places = (bn <= 64 ? 2 : 1) * sm_count() * 87 / 100;
+        int best = 1;
+        for (int s = 2; s <= 8 && s <= bn && p.kb_total / s >= 4; ++s)
+            if (n_tiles * s <= places) best = s;
+        p.splits = best;
+        if (best > 1)
             return epilogue == kSwiglu ? dispatch_cluster<kSwiglu>(bn, ma, mb, p, stream)
                                        : dispatch_cluster<kPlain>(bn, ma, mb, p, stream);
     }
