@@ -84,17 +84,8 @@ struct GemmParams {
     int* status;
     unsigned long long wait_ns;  // limit of every mbarrier wait of gemm_bf16_kernel; 0: the default (2 s)
     int tx_extra;      // bytes added to what a stage's barrier expects (the wait probe only: they never arrive)
-    int a_tiled;       // the A operand is stored tile by tile: [rows / 128][K / 64][128][64], a tile 16 KB in one piece
     QkvParams qkv;     // epilogue kQkv only
 };
-
-// The copy of A's tile (rows m0 .. m0 + 127, k-block kb).  Row-major A: 128 pieces of 128 bytes, one per row, a row
-// stride apart.  A stored tile by tile: the tile's 16 KB lie together, so the copy reads memory front to back.
-__device__ __forceinline__ void load_a_tile(void* dst, const CUtensorMap* map, uint64_t* bar, const GemmParams& p, int kb,
-                                            int m0) {
-    if (p.a_tiled) tma_load_2d(dst, map, bar, 0, ((m0 / kBlockM) * p.kb_total + kb) * kBlockM);
-    else tma_load_2d(dst, map, bar, kb * kBlockK, m0);
-}
 
 // Stores up to 16 accumulator values of one thread: A row `a_row`, B rows b0 .. b0 + ncols - 1
 // (ncols below 16 only when A rows are output features).
@@ -265,7 +256,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         break;
                     }
                     mbar_expect_tx(&full[s], kBytesA + kBytesB + p.tx_extra);
-                    load_a_tile(smem_a + s * kBytesA, &map_a, &full[s], p, kb, m0);
+                    tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
                     tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                     issued = kb_run + 1;
                 }
@@ -445,7 +436,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         break;
                     }
                     mbar_expect_tx(&full[s], kBytesA + kBytesB);
-                    load_a_tile(smem_a + s * kBytesA, &map_a, &full[s], p, kb, m0);
+                    tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
                     tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                     issued = kb_run + 1;
                 }
@@ -694,7 +685,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // the first round of copies starts now, under the set-up of tensor memory
         for (int i = 0; i < n_first; ++i) {
             mbar_expect_tx(&full[i], kBytesA + kBytesB);
-            load_a_tile(smem_a + i * kBytesA, &map_a, &full[i], p, kb0 + i, m0);
+            tma_load_2d(smem_a + i * kBytesA, &map_a, &full[i], (kb0 + i) * kBlockK, m0);
             tma_load_2d(smem_b + i * kBytesB, &map_b, &full[i], (kb0 + i) * kBlockK, n0);
         }
     }
@@ -725,7 +716,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     break;
                 }
                 mbar_expect_tx(&full[s], kBytesA + kBytesB);
-                load_a_tile(smem_a + s * kBytesA, &map_a, &full[s], p, kb, m0);
+                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
                 tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                 issued = i + 1;
             }
@@ -1422,8 +1413,8 @@ extern "C" int nncpu_linear_tc_wait_probe(const void* X, const void* W, float* o
 enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4 };
 
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
-                               int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, int w_tiled,
-                               float* scratch, int* status, void* stream_) {
+                               int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, float* scratch,
+                               int* status, void* stream_) {
     const int streamk_mode = (plan & kPlanNeverEven) ? 0 : (plan & kPlanEvenFrom17) ? 2 : 1;
     const int pair_mode = (plan & kPlanNoPairs) ? 0 : 1;
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -1450,17 +1441,9 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         p.swap = 1;
         bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
         p.rows_a = N; p.rows_b = M;
-        if (w_tiled) {
-            // W is stored as [ceil(N / 128)][ceil(K / 64)][128][64], padded with zeros: a tile is 16 KB in one piece
-            p.a_tiled = 1;
-            const int rows = ((N + kBlockM - 1) / kBlockM) * p.kb_total * kBlockM;
-            if (int e = g_maps.get(&ma, W, rows, kBlockK, kBlockK, kBlockM)) return e;
-        } else {
-            if (int e = g_maps.get(&ma, W, N, K, K, kBlockM)) return e;
-        }
+        if (int e = g_maps.get(&ma, W, N, K, K, kBlockM)) return e;
         if (int e = g_maps.get(&mb, X, M, K, lda, bn)) return e;
     } else {
-        NN_CHECK(!w_tiled, "gemm: weights stored tile by tile serve products of at most 256 tokens (M %d)", M);
         p.swap = 0;
         bn = N >= 256 ? 256 : 128;
         p.rows_a = M; p.rows_b = N;

@@ -131,43 +131,20 @@ PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4}
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 
-TILE_ROWS, TILE_K = 128, 64     # a weight tile of the tensor-core product: 16 KB of bfloat16
-
-
-def tile_weights(w: torch.Tensor) -> torch.Tensor:
-    """``w`` [n, k] stored tile by tile: [ceil(n / 128), ceil(k / 64), 128, 64], padded with zeros.  A product of
-    17 to 256 tokens streams the weights one tile at a time; with this layout each tile is 16 KB in one piece
-    instead of 128 pieces of 128 bytes a row stride apart."""
-    n, k = w.shape
-    nt, kt = (n + TILE_ROWS - 1) // TILE_ROWS, (k + TILE_K - 1) // TILE_K
-    if n % TILE_ROWS or k % TILE_K:
-        padded = torch.zeros(nt * TILE_ROWS, kt * TILE_K, dtype=w.dtype, device=w.device)
-        padded[:n, :k] = w
-        w = padded
-    return w.view(nt, TILE_ROWS, kt, TILE_K).permute(0, 2, 1, 3).contiguous()
-
-
 def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = False, epilogue: str = "plain",
-              plan: str = "auto", w_tiles: Optional[torch.Tensor] = None) -> None:
+              plan: str = "auto") -> None:
     """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16.  With
     ``epilogue="swiglu"`` the rows of w hold gate and up rows interleaved in
     blocks of 8 and out [m, n/2] receives silu(gate) * up.  ``plan``: "auto",
     or for measurements and tests "even_from_17" (17 to 64 tokens deal their
-    k-blocks out evenly like 65 to 256), "never_even", "no_pairs".
-    ``w_tiles``: the same weights as ``tile_weights(w)``, read instead of ``w``
-    by products of at most 256 tokens."""
+    k-blocks out evenly like 65 to 256), "never_even", "no_pairs"."""
     m, k = x.shape
     n = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert w.shape[1] == k and out.shape == (m, n // 2 if epilogue == "swiglu" else n)
-    tiled = w_tiles is not None and m <= 256
-    if tiled:
-        assert w_tiles.dtype == torch.bfloat16 and w_tiles.shape == ((n + TILE_ROWS - 1) // TILE_ROWS,
-                                                                     (k + TILE_K - 1) // TILE_K, TILE_ROWS, TILE_K)
-    _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w_tiles if tiled else w), _ptr(bias), _i(_code(bias)),
-          _ptr(out), _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate),
-          _i(EPILOGUES[epilogue]), _i(PLANS[plan]), _i(tiled), _ptr(workspace.scratch), _ptr(workspace.status),
-          _stream())
+    _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
+          _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
+          _i(PLANS[plan]), _ptr(workspace.scratch), _ptr(workspace.status), _stream())
 
 
 def linear_tc_wait_probe(x, w, out, workspace: GemmWorkspace, limit_ms: int = 5) -> None:
