@@ -1354,6 +1354,7 @@ extern "C" int nncpu_linear_tc_qkv(const void* X, const void* W, int M, int K, i
              ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0,
              "gemm (q/k/v epilogue): operands must be 16-byte aligned");
     NN_CHECK(tok_seq && tok_pos && block_table && status, "gemm (q/k/v epilogue): token places and status are needed");
+    NN_CHECK((uintptr_t)cos_sin % 8 == 0, "gemm (q/k/v epilogue): the rotation table must be 8-byte aligned (cos/sin pairs)");
     const int N = (n_heads + 2 * n_kv) * 128;
     GemmParams p{};
     p.K = K;

@@ -238,6 +238,7 @@ extern "C" int nncpu_rope_table(const int* pos, const float* inv_freq, float* cs
     NN_CHECK(n_tok >= 0 && half > 0, "rope_table: %d tokens, %d pairs", n_tok, half);
     if (n_tok == 0) return 0;
     const int total = n_tok * half;
+    NN_CHECK((uintptr_t)cs % 8 == 0, "rope_table: the table must be 8-byte aligned (it is written as cos/sin pairs)");
     rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(pos, inv_freq, (float2*)cs, n_tok,
                                                                              half, pos_scale, by_pair);
     NN_LAUNCH_OK("rope_table");
@@ -381,6 +382,7 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
     NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv >= 0 && hd > 0, "qk_norm_rope_append: sizes");
     NN_CHECK(hd % 2 == 0 && 2 * rot_half <= hd, "qk_norm_rope_append: head size %d with %d rotated pairs", hd,
              rot_half);
+    NN_CHECK((uintptr_t)cs % 8 == 0, "qk_norm_rope_append: the rotation table must be 8-byte aligned (cos/sin pairs)");
     NN_CHECK(hd <= 1024, "qk_norm_rope_append: head size %d is above 1024", hd);
     if (n_tok == 0) return 0;
     if (in_dt == DT_F32 && q_dt == DT_BF16 && (n_kv == 0 || kv_dt == DT_BF16) && (hd == 64 || hd == 128) &&

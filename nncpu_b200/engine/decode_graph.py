@@ -28,6 +28,7 @@ import torch
 from .. import perf
 from ..cache import pages_for
 from ..kernels import ops
+from ..parts.runtime import Arena
 from .step import StepContext
 
 _RING = 4  # pinned host copies of the metadata in flight
@@ -71,6 +72,7 @@ class DecodeGraph:
             block_tables=[m[o:o + B * self.width].view(B, self.width) for o in self.o_tables],
             q_lens=[1] * B, kv_lens=[0] * B, is_decode=True, max_kv_len=cache.max_seq_len)
         self.logits: Optional[torch.Tensor] = None
+        self.arena = Arena(dev)     # the captured step's intermediate tensors: its addresses are part of the graph
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.n_kernels = 0
         self.slots: Optional[tuple] = None
@@ -139,7 +141,9 @@ class DecodeGraph:
         return self.ids_events[i], self.ids_host[i]
 
     def _forward(self) -> None:
-        self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
+        with self.engine.model.rt.using(self.arena):
+            self.arena.begin()
+            self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
         ops.argmax(self.logits, self.next_ids)
 
     def run(self, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> torch.Tensor:
@@ -159,6 +163,8 @@ class DecodeGraph:
             # work is then captured, not run: a second run would advance per-sequence state twice.
             self._forward()
             eager = self.logits
+            self.arena.begin()          # now as large as that run needed;
+            self.arena.frozen = True    # from here on its addresses belong to the graph
             before = ops.launch_count()
             g = torch.cuda.CUDAGraph()
             torch.cuda.synchronize()

@@ -17,9 +17,11 @@ import numpy as np
 import torch
 
 from .. import perf
-from ..cache import Cache
+from ..cache import Cache, pages_for
 from ..errors import ContextFull, InvalidArgument, translating_oom
+from ..kernels import ops
 from ..parts import EntryCache
+from ..parts.runtime import Arena
 
 
 @dataclass
@@ -91,9 +93,10 @@ class Staging:
 
 
 def make_context(cache: Cache, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-                 want: Sequence[Sequence[int]], staging: Optional[Staging] = None) -> StepContext:
+                 want: Sequence[Sequence[int]], staging: Optional[Staging] = None, alloc=None) -> StepContext:
     """The step's metadata as one block of int32, copied to the device once.
-    Call after ``cache.prepare``: the page tables must already cover the new tokens."""
+    Call after ``cache.prepare``: the page tables must already cover the new tokens.
+    ``alloc(n, dtype=...)`` gives the device block (the step's arena); without it the allocator does."""
     starts = [cache.length(s) for s in slots]
     q_lens = [len(t) for t in tokens]
     n, B = sum(q_lens), len(slots)
@@ -124,7 +127,11 @@ def make_context(cache: Cache, slots: Sequence[int], tokens: Sequence[Sequence[i
     a[offsets[5]:offsets[5] + len(rows)] = rows
     for at, t in zip(table_at, tables):
         a[at:at + B * len(t[0])] = np.asarray(t, dtype=np.int64).reshape(-1)
-    dev = host.to(cache.device, non_blocking=True)
+    if alloc is not None and on_gpu:
+        dev = alloc(total, dtype=torch.int32)
+        dev.copy_(host, non_blocking=True)
+    else:
+        dev = host.to(cache.device, non_blocking=True)
     if staging is not None and on_gpu:
         staging.sent(turn)
     views = [dev[offsets[i]:offsets[i + 1]] for i in range(5)] + [dev[offsets[5]:offsets[5] + len(rows)]]
@@ -136,11 +143,33 @@ def make_context(cache: Cache, slots: Sequence[int], tokens: Sequence[Sequence[i
                        max_kv_len=max(s + q for s, q in zip(starts, q_lens)))
 
 
+def shape_context(cache: Cache, n_tokens: int, n_seqs: int, n_wanted: int, max_kv_len: int) -> StepContext:
+    """A step of these sizes without data: every tensor is shape-only (``meta``).  For the pass that measures
+    how much memory a step needs."""
+    def ints(*shape):
+        return torch.empty(shape, dtype=torch.int32, device="meta")
+    width = max(1, pages_for(max_kv_len))
+    per = max(1, n_tokens // n_seqs)
+    q_lens = [per] * (n_seqs - 1) + [n_tokens - per * (n_seqs - 1)]
+    return StepContext(n_tokens=n_tokens, n_seqs=n_seqs, n_wanted=n_wanted, tok_ids=ints(n_tokens), tok_seq=ints(n_tokens),
+                       tok_pos=ints(n_tokens), seq_slots=ints(n_seqs), cu_seqlens=ints(n_seqs + 1),
+                       logit_rows=ints(n_wanted), block_tables=[ints(n_seqs, width) for _ in cache.groups],
+                       q_lens=q_lens, kv_lens=list(q_lens), is_decode=all(q == 1 for q in q_lens),
+                       max_kv_len=max_kv_len)
+
+
 class Engine:
-    """A model with its cache.  ``step`` is the only way tokens reach the model."""
+    """A model with its cache.  ``step`` is the only way tokens reach the model.
+
+    A step's intermediate tensors come out of one arena that is sized when the engine is made, by a pass of the
+    model's forward over the shapes of the largest expected step (``max_step_tokens`` tokens, by default the
+    cache's capacity up to 8 192): a step asks the allocator for nothing.  A step that turns out larger (more
+    tokens, or many rows of logits wanted) is served by the allocator once, and the arena is as large from then on
+    (the reference sizes its scratch once, crates/nncpu/src/model/kv.rs:295-332)."""
 
     def __init__(self, model, max_tokens: int, n_slots: Optional[int] = None, max_seq_len: Optional[int] = None,
-                 kv_dtype: Optional[torch.dtype] = None, use_graphs: bool = True):
+                 kv_dtype: Optional[torch.dtype] = None, use_graphs: bool = True,
+                 max_step_tokens: Optional[int] = None):
         from .decode_graph import DecodeGraphs
         self.model = model
         self.graphs = DecodeGraphs(self) if use_graphs else None
@@ -155,6 +184,28 @@ class Engine:
         self.cache = Cache(requests, cache_of, max_tokens, kv_dtype or rt.dtype, rt.device, n_slots=n_slots,
                            max_seq_len=max_seq_len)
         self.vocab_size = model.spec.vocab_size
+        self.arena = Arena(rt.device)
+        self.max_step_tokens = min(max_step_tokens or 8192, self.cache.max_tokens)
+        self._size_arena()
+
+    def _size_arena(self) -> None:
+        """Runs the forward pass over shapes alone for a prompt step of ``max_step_tokens`` tokens (one sequence,
+        and as many sequences as fit) and makes the arena hold the larger of the two."""
+        rt, n = self.model.rt, self.max_step_tokens
+        self.arena.measuring = True
+        try:
+            with rt.using(self.arena), ops.shapes_only():
+                for n_seqs in {1, max(1, min(n, self.cache.n_slots, 256))}:
+                    self.arena.begin()
+                    ctx = shape_context(self.cache, n, n_seqs, n_seqs, min(n, self.cache.max_seq_len))
+                    rt.empty(3 * n + 4 * n_seqs + 1 + sum(t.numel() for t in ctx.block_tables), dtype=torch.int32)
+                    self.model.forward(ctx, self.cache)
+        except Exception:
+            self.arena.peak = 0      # a part that cannot run on shapes alone: the arena learns from the first steps
+        finally:
+            self.arena.measuring = False
+        with translating_oom(f"the arena of a step of {n} tokens ({self.arena.peak / 2 ** 20:.0f} MiB)"):
+            self.arena.begin()
 
     @property
     def max_seq_len(self) -> int:
@@ -189,7 +240,7 @@ class Engine:
                     raise InvalidArgument(f"sequence {b}: wanted place {i} is outside its {len(toks)} tokens")
 
     def build_context(self, slots, tokens, want) -> StepContext:
-        ctx = make_context(self.cache, slots, tokens, want, self._staging)
+        ctx = make_context(self.cache, slots, tokens, want, self._staging, alloc=self.model.rt.empty)
         self.h2d_bytes_last_step = ctx.h2d_bytes
         return ctx
 
@@ -199,7 +250,10 @@ class Engine:
         lists the places among ``tokens[b]`` whose logits are returned
         (default: the last).  Returns float32 [n_wanted, vocab] on the device,
         rows in the order of the sequences and of ``want``; None if nothing is
-        wanted."""
+        wanted.  The result lives in the step's arena (or its graph's buffer):
+        it is valid until the engine's next step, so copy what must last longer
+        (the reference's logits are likewise those of the last evaluation,
+        crates/nncpu/src/session/engine.rs:255-270)."""
         if want is None:
             want = [[len(t) - 1] for t in tokens]
         slots = [int(s) for s in slots]
@@ -220,7 +274,9 @@ class Engine:
             return logits
         self._last_graph = None
         try:
-            with translating_oom(f"a step of {sum(len(t) for t in tokens)} tokens in {len(slots)} sequences"):
+            with translating_oom(f"a step of {sum(len(t) for t in tokens)} tokens in {len(slots)} sequences"), \
+                    self.model.rt.using(self.arena):
+                self.arena.begin()
                 ctx = self.build_context(slots, tokens, want)
                 logits = self.model.forward(ctx, self.cache)
         except BaseException:

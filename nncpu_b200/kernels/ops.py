@@ -31,6 +31,8 @@ def _code(t: Optional[torch.Tensor]) -> int:
 def _ptr(t: Optional[torch.Tensor]):
     if t is None:
         return _vp(0)
+    if t.is_meta and _dry:
+        return _vp(0)           # a pass over shapes alone: nothing is launched, so nothing is pointed at
     if not t.is_cuda:
         raise ExtensionError("the kernels run on the GPU: a tensor on the CPU was passed, and there is no CPU path")
     if not t.is_contiguous():
@@ -50,6 +52,22 @@ def _stream():
 
 
 _launches = 0
+_dry = False
+
+
+class shapes_only:
+    """Inside, every function of this module checks its arguments and launches nothing: a forward pass over
+    shape-only (``meta``) tensors, which the engine runs once to learn how much memory a step needs."""
+
+    def __enter__(self):
+        global _dry
+        self.before, _dry = _dry, True
+
+    def __exit__(self, *exc):
+        global _dry
+        _dry = self.before
+        return False
+
 
 
 def launch_count() -> int:
@@ -66,6 +84,8 @@ def add_launches(n: int) -> None:
 def _call(libname: str, fn: str, *args) -> None:
     global _launches
     lib = library.load(libname)
+    if _dry:
+        return
     f = getattr(lib, fn)
     if f(*args) != 0:
         raise ExtensionError(lib.last_error().decode())

@@ -23,6 +23,7 @@ class PreNormBlock(Block):
         return [p for part in self._parts for p in part.params()]
 
     def bind(self, tensors, rt):
+        self.rt = rt
         for part in self._parts:
             part.bind(tensors, rt)
 
@@ -33,5 +34,7 @@ class PreNormBlock(Block):
         return [(self.mixer.kv_request(), self.mixer.state_request())]
 
     def forward(self, ctx, residual, caches):
-        self.mixer.forward(ctx, self.norm1.forward(ctx, residual), residual, caches[0])
-        self.feed_forward.forward(ctx, self.norm2.forward(ctx, residual), residual)
+        with self.rt.scope():       # the mixer's temporaries are done with when the feed-forward starts
+            self.mixer.forward(ctx, self.norm1.forward(ctx, residual), residual, caches[0])
+        with self.rt.scope():
+            self.feed_forward.forward(ctx, self.norm2.forward(ctx, residual), residual)

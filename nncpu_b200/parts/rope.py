@@ -39,7 +39,7 @@ class RopeNeox(PositionEncoding):
         t = ctx.memo.get(key)
         if t is None:
             shape = (self.half, ctx.n_tokens, 2) if by_pair else (ctx.n_tokens, self.half, 2)
-            t = self.rt.empty(*shape, dtype=torch.float32)
+            t = self.rt.empty(*shape, dtype=torch.float32, keep=True)     # every later layer of the step reads it
             ops.rope_table(ctx.tok_pos, self.inv_freq, t, self.spec.position_scale, by_pair)
             ctx.memo[key] = t
         return t

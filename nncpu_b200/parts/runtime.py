@@ -4,11 +4,92 @@ between the tensor-core and the CUDA-core matrix product.
 """
 from __future__ import annotations
 
+from contextlib import contextmanager
+from typing import List, Optional
+
 import torch
 
 from .. import perf
 from ..errors import ExtensionError
 from ..kernels import ops
+
+
+class Arena:
+    """The memory of one step's intermediate tensors: one device buffer that ``Runtime.empty`` carves pieces
+    from, front to back, so that a step asks the allocator for nothing
+    (the reference sizes its forward scratch once: crates/nncpu/src/model/kv.rs:45-47,295-332).
+
+    * ``begin()`` starts a step: everything handed out before is void.
+    * ``mark()`` / ``release(mark)`` give back what a part of the step no longer needs (a block's
+      temporaries when the block is done), so the buffer holds the widest moment of a step, not its sum.
+      What must live until the step ends although it is made inside such a part (a table that later layers
+      read) is taken with ``keep=True``, from the buffer's other end.
+    * ``measure()``: pieces are shape-only (``meta``) tensors and only the sizes are added up; a forward pass
+      run this way launches nothing and tells how large the buffer must be.
+    * A request that does not fit is served by the allocator once, and the next ``begin()`` makes the buffer
+      large enough for it; an arena that a CUDA graph has captured is ``frozen`` instead and refuses, because its
+      addresses are part of the graph."""
+    ALIGN = 256
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.buf: Optional[torch.Tensor] = None
+        self.typed = {}                 # the buffer seen as each element type that was asked for
+        self.capacity = 0
+        self.offset = 0                 # bytes in use from the front (given back by release)
+        self.top = 0                    # bytes in use from the back (kept until the step ends)
+        self.peak = 0
+        self.overflow: List[torch.Tensor] = []
+        self.measuring = False
+        self.frozen = False
+
+    def reserve(self, nbytes: int) -> None:
+        nbytes = (nbytes + self.ALIGN - 1) // self.ALIGN * self.ALIGN    # pieces from the back are aligned too
+        if nbytes > self.capacity:
+            if self.frozen:
+                raise ExtensionError("a captured step's arena cannot grow")
+            self.buf = None             # the old buffer goes back before the new one is asked for
+            self.typed = {}
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self.capacity = nbytes
+
+    def begin(self) -> None:
+        self.overflow.clear()
+        if self.peak > self.capacity and not self.measuring:
+            self.reserve(self.peak)
+        self.offset = self.top = 0
+
+    def mark(self) -> int:
+        return self.offset
+
+    def release(self, mark: int) -> None:
+        self.offset = mark
+
+    def alloc(self, shape, dtype: torch.dtype, keep: bool = False) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        size = dtype.itemsize
+        nbytes = n * size
+        if keep:
+            self.top += (nbytes + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+            start = self.capacity - self.top
+        else:
+            start = (self.offset + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+            self.offset = start + nbytes
+        self.peak = max(self.peak, self.offset + self.top)
+        if self.measuring:
+            return torch.empty(shape, dtype=dtype, device="meta")
+        if self.offset + self.top <= self.capacity:
+            whole = self.typed.get(dtype)
+            if whole is None:
+                whole = self.typed[dtype] = self.buf[:self.capacity // size * size].view(dtype)
+            return whole[start // size:start // size + n].view(shape)
+        if self.frozen:
+            raise ExtensionError(f"a captured step asked for {nbytes} bytes beyond its arena of {self.capacity}")
+        t = torch.empty(shape, dtype=dtype, device=self.device)
+        self.overflow.append(t)
+        return t
 
 
 class Runtime:
@@ -21,12 +102,37 @@ class Runtime:
         self.dtype = dtype
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._workspace = None
+        self.arena: Optional[Arena] = None      # set by the engine around a step; without one, the allocator serves
         self._status_host = None
         self._status_posted = []
         self._status_turn = 0
 
-    def empty(self, *shape, dtype=None) -> torch.Tensor:
+    def empty(self, *shape, dtype=None, keep: bool = False) -> torch.Tensor:
+        """An uninitialised tensor for this step: a piece of the step's arena, void when the next step begins, or
+        when the part that asked for it is done (``scope``) unless it is to ``keep``."""
+        if self.arena is not None:
+            return self.arena.alloc(shape, dtype or self.dtype, keep)
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    @contextmanager
+    def using(self, arena: Optional[Arena]):
+        """Steps inside take their tensors from ``arena``."""
+        before, self.arena = self.arena, arena
+        try:
+            yield arena
+        finally:
+            self.arena = before
+
+    @contextmanager
+    def scope(self):
+        """What is taken from the arena inside is given back at the end: for a part's temporaries."""
+        arena = self.arena
+        mark = arena.mark() if arena is not None else 0
+        try:
+            yield
+        finally:
+            if arena is not None and self.arena is arena:
+                arena.release(mark)
 
     @property
     def workspace(self) -> ops.GemmWorkspace:

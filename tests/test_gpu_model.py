@@ -49,7 +49,7 @@ def test_whole_then_last_32_one_by_one(folders, plains, name, dtype):
     toks = tokens_for(plain, 150, 1)
     want = plain.logits(toks)
     s = engine.alloc_slot()
-    whole = engine.step([s], [toks], [list(range(150))])
+    whole = engine.step([s], [toks], [list(range(150))]).clone()      # a step's result is valid until the next step
     check(whole, want, TOL[dtype], "whole request")
     s2 = engine.alloc_slot()
     head = engine.step([s2], [toks[:118]], [list(range(118))]).clone()
@@ -111,7 +111,7 @@ def test_long_prompts_whole_cut_and_batched(folders, plains, dtype):
     want_a, want_b = plain.logits(a), plain.logits(b)
     places = sorted(set(range(0, 700, 37)) | {127, 128, 255, 256, 511, 512, 639, 640, 699})
     s = engine.alloc_slot()
-    whole = engine.step([s], [a], [places])
+    whole = engine.step([s], [a], [places]).clone()      # a step's result is valid until the next step
     check(whole, want_a[places], TOL[dtype], "whole request")
     engine.free_slot(s)
     s = engine.alloc_slot()

@@ -147,3 +147,58 @@ def test_evaluated_logits_outlive_a_generate_call(folders, dtype):
     if dtype == "float32":
         assert session.sample(SamplerParams.greedy()) == argmax_first(want)
     assert session.n_past() == 12 and session.tokens() == own
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_step_asks_the_allocator_for_nothing(folders, dtype):
+    """The engine's arena is sized when the engine is made; 50 steps of every kind (prompts of unequal lengths,
+    mixed steps, decode steps through graphs after their first) then leave the allocator's counters alone."""
+    plain = PlainQwen3(folders["G", dtype])
+    model = Model.load(folders["G", dtype], dtype=dtype)
+    engine = Engine(model, max_tokens=64 * 40, max_step_tokens=2000)
+    assert engine.arena.capacity > 0
+    rs = np.random.RandomState(9)
+
+    def run(n_steps, check_logits):
+        slots, seqs = [], []
+        for step in range(n_steps):
+            kind = step % 5
+            if kind == 0:                                  # a batch starts: prompts of unequal lengths
+                for s in slots:
+                    engine.free_slot(s)
+                lens = [int(x) for x in rs.choice([3, 40, 200, 600], size=rs.randint(1, 4))]
+                seqs = [toks(plain, n, 1000 + step + i) for i, n in enumerate(lens)]
+                slots = [engine.alloc_slot() for _ in seqs]
+                out = engine.step(slots, seqs)
+            elif kind == 3 and len(slots) < 4:             # a newcomer's prompt beside the others' next tokens
+                new = toks(plain, 90, 2000 + step)
+                nxt = [[int(rs.randint(0, plain.cfg.vocab))] for _ in slots]
+                slots.append(engine.alloc_slot())
+                for q, t in zip(seqs, nxt):
+                    q.append(t[0])
+                seqs.append(list(new))
+                out = engine.step(slots, nxt + [new])
+            else:                                          # everybody goes on by one token
+                nxt = [[int(rs.randint(0, plain.cfg.vocab))] for _ in slots]
+                for q, t in zip(seqs, nxt):
+                    q.append(t[0])
+                out = engine.step(slots, nxt)
+            if check_logits and step % 7 == 0:
+                check(out[-1:], plain.logits(seqs[-1], rows=[-1]), TOL[dtype], f"step {step}")
+        for s in slots:
+            engine.free_slot(s)
+    run(15, False)                                         # every path has run once,
+    for b in (1, 2, 4):                                    # and every graph size is captured
+        slots = [engine.alloc_slot() for _ in range(b)]
+        engine.step(slots, [[1, 2, 3]] * b)
+        engine.step(slots, [[4]] * b)
+        for s in slots:
+            engine.free_slot(s)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    capacity = engine.arena.capacity
+    run(50, True)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
+    assert engine.arena.capacity == capacity and not engine.arena.overflow
+    model.rt.check_status()
