@@ -558,8 +558,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     const size_t stages = (size_t)kDecodeStages * 2 * kPage * HD * 2;
     const size_t merge = (size_t)5 * G * (HD + 2) * sizeof(float);
     const size_t smem = stages > merge ? stages : merge;
-    // set at every launch: the attribute belongs to the (kernel, device) pair, and setting it costs next to nothing
-    {
+    static bool configured[4][64] = {};
+    if (first_use_on_this_device(configured[(cluster ? 2 : 0) + (G <= 8 ? 0 : 1)])) {
         const cudaError_t e = cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    (int)(stages > (size_t)5 * 16 * (HD + 2) * 4 ? stages : (size_t)5 * 16 * (HD + 2) * 4));
         NN_CHECK(e == cudaSuccess, "attention decode: cannot reserve shared memory: %s", cudaGetErrorString(e));
@@ -595,7 +595,8 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
                    float scale, int window, cudaStream_t stream) {
     const int max_tiles = n_tok / 64 + n_seqs;
     constexpr int smem = 2 * 2 * kPage * HD * 2;
-    {
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
         const cudaError_t e = cudaFuncSetAttribute(prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         NN_CHECK(e == cudaSuccess, "attention prefill: cannot reserve shared memory: %s", cudaGetErrorString(e));
     }

@@ -507,13 +507,12 @@ template <int HD, int kStreams>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int n_tok,
            cudaStream_t stream) {
     constexpr int smem = kStreams * kQRows * HD * 2 + 2 * kStages * kKeys * HD * 2 + 256 + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
         const cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<HD, kStreams>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         NN_CHECK(e == cudaSuccess, "attention (tensor cores): %d bytes of shared memory refused: %s", smem,
                  cudaGetErrorString(e));
-        configured = true;
     }
     // tiles: an upper bound, since the sequence boundaries live on the device; spare blocks leave at once
     const int group = p.n_heads / p.n_kv;

@@ -60,6 +60,16 @@ __device__ __forceinline__ void st_f(void* p, size_t i, int dt, float v) {
     else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
 }
 
+// True the first time a call site asks on the current device: for set-up that belongs to a (kernel, device)
+// pair, such as the shared-memory attribute.  `done` is the call site's own static array.
+inline bool first_use_on_this_device(bool (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -1193,12 +1193,11 @@ constexpr size_t smem_bytes() {
 template <int BN, int kStages, int kEpi>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int blocks_per_sm, cudaStream_t stream) {
     constexpr size_t smem = smem_bytes<BN, kStages>();
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, kStages, kEpi>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
     }
     const int n_items = p.tiles_a * p.tiles_b;
     const int grid = n_items < blocks_per_sm * sm_count() ? n_items : blocks_per_sm * sm_count();
@@ -1210,12 +1209,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int bloc
 template <int BN, int kStages, int kEpi>
 int launch_streamk(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
     constexpr size_t smem = smem_bytes<BN, kStages>();
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_streamk_kernel<BN, kStages, kEpi>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
     }
     // one block per SM with a deep pipeline; at least 4 k-blocks per block
     const long units = (long)p.tiles_a * p.tiles_b * p.kb_total;
@@ -1247,12 +1245,11 @@ int dispatch_streamk(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmP
 template <int BN, int kStages, int kEpi>
 int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
     constexpr size_t smem = cluster_smem_bytes<BN, kStages>();
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_cluster_kernel<BN, kStages, kEpi>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(p.tiles_a * p.tiles_b * p.splits));
@@ -1275,12 +1272,11 @@ template <int kStages, int kEpi>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
     constexpr size_t smem = 1024 + (size_t)kStages * (kBlockM * kBlockK * 2 + 128 * kBlockK * 2) +
                             (2 * kStages + 4) * sizeof(uint64_t) + 16;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<kStages, kEpi>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
     }
     const int n_items = p.tiles_a * p.tiles_b;
     const int max_pairs = sm_count() / 2;
