@@ -110,15 +110,20 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
                 for (int j = 0; j < 8; ++j) st_f(p.out, o + j, p.out_dt, act[j]);
             }
         } else {
-            // rows hold 8 gate rows, then 8 up rows: lane l and lane l ^ 8 hold a pair
+            // Rows hold 8 gate rows, then 8 up rows: lane l and lane l ^ 8 hold the gate and the up value of one
+            // feature.  The pair shares the work: of two neighbouring tokens the gate lane finishes the first and
+            // the up lane the second, so every lane computes one activation per two columns.
             const bool is_gate = (a_row & 8) == 0;
             const int feature = (a_row >> 4) * 8 + (a_row & 7);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
-                const int tok = b0 + j;
-                if (is_gate && a_ok && j < ncols && tok < p.rows_b)
-                    st_f(p.out, (size_t)tok * p.ldc + feature, p.out_dt, silu_mul(v[j], other));
+            for (int j = 0; j < 16; j += 2) {
+                const float o0 = __shfl_xor_sync(0xffffffffu, v[j], 8);
+                const float o1 = __shfl_xor_sync(0xffffffffu, v[j + 1], 8);
+                const float g = is_gate ? v[j] : o1, u = is_gate ? o0 : v[j + 1];
+                const int jj = is_gate ? j : j + 1;
+                const int tok = b0 + jj;
+                if (a_ok && jj < ncols && tok < p.rows_b)
+                    st_f(p.out, (size_t)tok * p.ldc + feature, p.out_dt, silu_mul(g, u));
             }
         }
         return;
