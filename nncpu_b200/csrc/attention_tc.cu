@@ -23,7 +23,7 @@
 //     (between two O updates, never under one) and sum are rescaled and the
 //     step's weights computed again.
 // The output row is O / sum.  The reference computes the same attention row by
-// row (crates/nncpu/src/model/forward.rs:730-800); softmax runs in 32-bit here
+// row (crates/nncpu/src/model/forward.rs:141-160,383-426); softmax runs in 32-bit here
 // as there.
 //
 // Every wait on an mbarrier is bounded in time; a wait that runs out sets

@@ -897,7 +897,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 // heads get the per-head RMS norm (32-bit sum over the head) and the rotation of the pairs (i, i + 64); value
 // heads are only rounded.  Queries go to q_out, keys and values to the token's place in the cache pages.
 // The same arithmetic as the separate kernel (x * scale * gamma, then the rotation), so prefill and decode
-// agree to rounding (crates/nncpu/src/model/forward.rs:681-728).
+// agree to rounding (crates/nncpu/src/model/forward.rs:278-324).
 __device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float (*s_gamma)[128], uint32_t taddr,
                                                int a_row, int n0) {
     const QkvParams& e = p.qkv;

@@ -148,11 +148,18 @@ class Model:
         return sum(self.blocks[e.layer].weight_bytes() for e in self.schedule) + head
 
     def info(self) -> dict:
+        """What the model is, in the reference's terms (crates/nncpu/src/lib.rs:150-190): sizes, counts and the
+        bytes its weights hold on the device.  Head counts are those of the first mixer that has heads."""
         n_params = sum(int(torch.tensor(p.shape).prod()) for p in parameter_list(self.spec) if p.required)
+        heads = next((b.mixer for b in self.spec.layers if hasattr(b.mixer, "n_heads")), None)
+        weights = self.weight_bytes_per_step() + (0 if self.spec.output.tied else
+                                                  self.embed_table.numel() * self.embed_table.element_size())
         return {"architecture": self.spec.architecture, "dtype": str(self.rt.dtype).replace("torch.", ""),
                 "layers": len(self.spec.layers), "schedule": len(self.schedule),
                 "hidden_size": self.spec.hidden_size, "vocab_size": self.spec.vocab_size,
-                "parameters": n_params, "max_positions": self.spec.max_positions}
+                "n_heads": getattr(heads, "n_heads", None), "n_kv_heads": getattr(heads, "n_kv_heads", None),
+                "head_dim": getattr(heads, "head_dim", None),
+                "parameters": n_params, "weight_bytes": weights, "max_positions": self.spec.max_positions}
 
     # -- one step -------------------------------------------------------------------
 
