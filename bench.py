@@ -159,8 +159,8 @@ def run_decode_point(model, cfg, batch: int, steps: int, warmup: int, seed: int 
     if with_phases:
         # the same engine, a few steps kernel by kernel under the phase profiler: where a step's time goes
         from nncpu_b200 import perf_enable, perf_reset, perf_totals
-        for s in slots:
-            engine.cache.truncate(s, (PROMPT + CONTEXT) // 2)      # the middle of the timed range
+        for s in slots:      # the middle of the timed range, and in any case room for the steps below
+            engine.cache.truncate(s, min(engine.cache.length(s), (PROMPT + CONTEXT) // 2, CONTEXT - 16))
         room = 9
         if room > 1:
             toks = [[1]] * batch
