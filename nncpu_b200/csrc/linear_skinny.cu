@@ -16,6 +16,20 @@
 //
 // The reference computes these products with its BF16 row kernels
 // (crates/nncpu/src/kernels/mod.rs:337-360, crates/nncpu/src/kernels/scalar.rs:555-567).
+//
+// A decode step is a chain of these products with an RMS norm between every two of them, and at a few
+// tokens such a norm is all launch and no work.  So the norm can ride on the products around it
+// (y = (x * scale) * gamma with scale = 1 / sqrt(mean(x^2) + eps), crates/nncpu/src/kernels/scalar.rs:270-292):
+//   * the product that adds into the residual stream ("producer") also writes x * gamma in bfloat16 for the
+//     rows it has just finished, and adds the sum of squares of its 16 columns of every row to that row's total:
+//     the blocks' sums meet in an exact accumulator per row: eight 64-bit integers, one per 32 binary orders of
+//     magnitude, into which a float is added as its 24-bit mantissa shifted to its place.  Integer addition does
+//     not care about order, so the blocks add with plain atomic adds that nobody waits for, and the total is the
+//     same whatever the timing;
+//   * the product that reads the normed rows ("consumer") takes x * gamma as its input, fetches the rows'
+//     accumulators when it starts (72 bytes a row), turns them into the rows' scales after its weight stream, and
+//     multiplies its own result by them, which a product commutes with.
+// A producer also clears the accumulators of the norm before it, whose consumer has run by then.
 
 #include <math.h>
 
@@ -47,13 +61,53 @@ __device__ __forceinline__ uint4 ldg16_stream(const __nv_bfloat16* p) {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
 
+// What a product does for the norms around it (all null or zero: nothing).
+constexpr int kBinWords = 16;    // 64-bit words a row: 8 accumulator bins, a word that says "not finite", 7 spare
+struct NormFusion {
+    // producer: besides C, leave the input of the norm that reads C next
+    __nv_bfloat16* xg_out;        // [M, N]: C * gamma, not yet multiplied by the row's scale
+    const void* gamma;            // [N] weights of that norm
+    int gamma_dt;
+    unsigned long long* bins_out; // [16, kBinWords], zero before the launch: the rows' sums of squares of C
+    unsigned long long* bins_clear;  // [16, kBinWords] of an earlier norm whose consumer has run: set to zero (or null)
+    // consumer: X is such an input; the rows' scales are applied to this product's result
+    const unsigned long long* bins_in;   // [16, kBinWords]
+    float eps;
+};
+
+// A non-negative float into its row's accumulator: value = mantissa * 2^(E - 150) with E = 32 * bin + shift.
+__device__ __forceinline__ void bins_add(unsigned long long* bins, float v) {
+    const uint32_t bits = __float_as_uint(v);
+    const uint32_t e = (bits >> 23) & 0xFF;
+    if (e == 0xFF) {                       // infinity or NaN: the row has no finite norm
+        atomicAdd(bins + 8, 1ull);
+        return;
+    }
+    const uint32_t ee = e ? e : 1;         // subnormals have the exponent of the smallest normal and no hidden bit
+    const unsigned long long mant = (bits & 0x7FFFFF) | (e ? 0x800000u : 0u);
+    if (mant) atomicAdd(bins + ee / 32, mant << (ee % 32));
+}
+
+// The sum that an accumulator holds, rounded once to float.
+__device__ __forceinline__ float bins_total(const unsigned long long* bins) {
+    if (bins[8] != 0) return __int_as_float(0x7FC00000);   // NaN
+    double s = 0.0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b)   // 2^(32 b - 150), spelled as the bits of the double
+        s += (double)bins[b] * __longlong_as_double((long long)(1023 + 32 * b - 150) << 52);
+    return (float)s;
+}
+
 // NT = number of 8-token tiles (1: up to 8 tokens, 2: up to 16).
 template <int NT, int kEpi>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, const void* __restrict__ bias,
-              int bias_dt, void* __restrict__ out, int out_dt, int M, int N, int K, int lda, int ldc, int accumulate) {
+              int bias_dt, void* __restrict__ out, int out_dt, int M, int N, int K, int lda, int ldc, int accumulate,
+              const NormFusion nf) {
     constexpr int kU = NT == 1 ? kUnroll : 6;
     __shared__ float part[kWarps][kRows][NT * 8 + 1];
+    __shared__ float row_scale[16];
+    __shared__ unsigned long long bins_s[16][9];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = lane & 3, r = lane >> 2;
     const int row0 = blockIdx.x * kRows;
@@ -74,6 +128,20 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
         const int tok = threadIdx.x / kRows, row = row0 + threadIdx.x % kRows;
         if (tok < M && row < N) before = ld_f(out, (size_t)tok * ldc + row, out_dt);
     }
+
+    // Consumer of a norm: the rows' accumulators are asked for now (asynchronous 8-byte copies into shared memory
+    // that hold no register and stall nobody) and turned into scales after the weight stream.
+    if (nf.bins_in != nullptr && threadIdx.x < M) {
+        // thread t fetches row t's accumulator for itself: when its own copies have landed it needs nobody else
+#pragma unroll
+        for (int word = 0; word < 9; ++word)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(&bins_s[threadIdx.x][word])),
+                         "l"(nf.bins_in + threadIdx.x * kBinWords + word)
+                         : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    // Producer of a norm: the accumulators of the norm before it are cleared for their next use.
+    if (nf.bins_clear != nullptr && blockIdx.x == 0) nf.bins_clear[threadIdx.x] = 0ull;   // 16 * kBinWords = 256 words
 
     // this warp's share of K, in groups of 32
     const int n_groups = (K + 31) / 32;
@@ -127,6 +195,10 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
         part[warp][r + 8][t * 8 + 2 * c] = acc[t][2];
         part[warp][r + 8][t * 8 + 2 * c + 1] = acc[t][3];
     }
+    if (nf.bins_in != nullptr && threadIdx.x < M) {
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        row_scale[threadIdx.x] = 1.0f / sqrtf(bins_total(bins_s[threadIdx.x]) * (1.0f / (float)K) + nf.eps);
+    }
     __syncthreads();
     if (kEpi == kSwiglu) {
         // rows 0..7 of the block are gate rows, rows 8..15 the up rows of the same outputs
@@ -139,30 +211,45 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
                 g += part[w][j][tok];
                 u += part[w][j + 8][tok];
             }
+            if (nf.bins_in != nullptr) {
+                g *= row_scale[tok];
+                u *= row_scale[tok];
+            }
             st_f(out, (size_t)tok * ldc + (row0 >> 1) + j, out_dt, silu_mul(g, u));
         }
     } else {
-        for (int i = threadIdx.x; i < kRows * M; i += kWarps * 32) {
-            const int tok = i / kRows, j = i % kRows;
-            const int row = row0 + j;
-            if (row >= N) continue;
-            float v = 0.0f;
+        // thread i owns output (token i / 16, row i % 16): one element per thread, and every thread of the block
+        // walks through (the producer's sums of squares are taken with shuffles)
+        const int tok = threadIdx.x / kRows, j = threadIdx.x % kRows;
+        const int row = row0 + j;
+        const bool valid = tok < M && row < N;
+        float v = 0.0f;
+        if (valid) {
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) v += part[w][j][tok];
+            if (nf.bins_in != nullptr) v *= row_scale[tok];
             if (bias) v += ld_f(bias, row, bias_dt);
-            const size_t o = (size_t)tok * ldc + row;
-            if (accumulate) v += before;   // i == threadIdx.x: kRows * M is at most the block's 256 threads
-            st_f(out, o, out_dt, v);
+            if (accumulate) v += before;
+            st_f(out, (size_t)tok * ldc + row, out_dt, v);
+        }
+        if (nf.xg_out != nullptr) {
+            // producer of a norm: x * gamma for the consumer, and this block's part of every row's sum of squares
+            // (the 16 lanes that hold a row's 16 columns add up through the shuffle tree)
+            if (valid) nf.xg_out[(size_t)tok * N + row] = __float2bfloat16(v * ld_f(nf.gamma, row, nf.gamma_dt));
+            float sq = valid ? v * v : 0.0f;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (j == 0 && tok < M) bins_add(nf.bins_out + tok * kBinWords, sq);
         }
     }
 }
 
 template <int NT, int kEpi>
 int launch(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M, int N, int K, int lda,
-           int ldc, int accumulate, cudaStream_t stream) {
+           int ldc, int accumulate, const NormFusion& nf, cudaStream_t stream) {
     const int blocks = (N + kRows - 1) / kRows;
     skinny_kernel<NT, kEpi><<<blocks, kWarps * 32, 0, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias,
-                                                                bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate);
+                                                                bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf);
     NN_LAUNCH_OK("linear_skinny");
     return 0;
 }
@@ -173,10 +260,22 @@ extern "C" int nncpu_linear_skinny_supported(int M, int N, int K, int lda) {
     return M > 0 && M <= 16 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0;
 }
 
+// 64-bit words of the accumulators of one norm (16 rows): what a producer adds into and a consumer reads.
+extern "C" int nncpu_linear_skinny_norm_words() { return 16 * kBinWords; }
+
 // C[M, N] (+)= X[M, K] . W[N, K]^T + bias for M <= 16, or with epilogue 1: C[M, N/2] = silu(gate) * up
 // for W rows interleaved in blocks of 8.  X and W are bfloat16 and 16-byte aligned; C is float or bfloat16.
+//
+// Norm fusion (see the head of this file), all optional; an accumulator block is nncpu_linear_skinny_norm_words()
+// 64-bit words:
+//   producer (plain epilogue): xg_out bfloat16 [M, N] receives C * gamma (gamma: N weights of type gamma_dt) and
+//     bins_out, which must be zero, the sums of squares of C's rows; bins_clear (may be null) is set to zero;
+//   consumer: X holds such C * gamma rows of width K and bins_in their accumulators: the result is multiplied by
+//     1 / sqrt(sum / K + eps) per row before bias and activation.
 extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt,
-                                   int M, int N, int K, int lda, int ldc, int accumulate, int epilogue, void* stream_) {
+                                   int M, int N, int K, int lda, int ldc, int accumulate, int epilogue, void* xg_out,
+                                   const void* gamma, int gamma_dt, void* bins_out, void* bins_clear,
+                                   const void* bins_in, float eps, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(nncpu_linear_skinny_supported(M, N, K, lda),
              "linear (few tokens): M %d, N %d, K %d, lda %d: at most 16 tokens, K and lda multiples of 8", M, N, K, lda);
@@ -184,12 +283,30 @@ extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bia
     NN_CHECK(epilogue == kPlain || epilogue == kSwiglu, "linear (few tokens): unknown epilogue %d", epilogue);
     const int n_out = epilogue == kSwiglu ? N / 2 : N;
     NN_CHECK(ldc >= n_out, "linear (few tokens): ldc %d is below the %d output features", ldc, n_out);
+    NormFusion nf{};
+    if (xg_out != nullptr) {
+        NN_CHECK(epilogue == kPlain && gamma != nullptr && bins_out != nullptr && ((uintptr_t)bins_out % 8) == 0 &&
+                     ((uintptr_t)bins_clear % 8) == 0,
+                 "linear (few tokens): leaving a norm's input needs the plain epilogue, the norm's weights and its "
+                 "accumulators (8-byte aligned)");
+        nf.xg_out = (__nv_bfloat16*)xg_out;
+        nf.gamma = gamma;
+        nf.gamma_dt = gamma_dt;
+        nf.bins_out = (unsigned long long*)bins_out;
+        nf.bins_clear = (unsigned long long*)bins_clear;
+    }
+    if (bins_in != nullptr) {
+        NN_CHECK(((uintptr_t)bins_in % 8) == 0 && eps >= 0.0f, "linear (few tokens): a norm's accumulators (8-byte aligned), eps %g",
+                 eps);
+        nf.bins_in = (const unsigned long long*)bins_in;
+        nf.eps = eps;
+    }
     if (epilogue == kSwiglu) {
         NN_CHECK(N % 16 == 0 && bias == nullptr && !accumulate,
                  "linear (few tokens): the gated epilogue needs N %% 16 == 0, no bias and no accumulation (N %d)", N);
-        return M <= 8 ? launch<1, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream)
-                      : launch<2, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream);
+        return M <= 8 ? launch<1, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream)
+                      : launch<2, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream);
     }
-    return M <= 8 ? launch<1, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream)
-                  : launch<2, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, stream);
+    return M <= 8 ? launch<1, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream)
+                  : launch<2, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream);
 }

@@ -43,6 +43,8 @@ class StepContext:
     h2d_bytes: int = 0          # bytes of metadata copied to the device for this step
     max_kv_len: int = 0         # host: an upper bound of the longest sequence after this step
     memo: Dict = field(default_factory=dict)  # per-step results shared between layers
+    next_norm: Optional[object] = None    # a NormRequest for the part that is running: see parts.base.NormRequest
+    after_block: Optional[object] = None  # the request of the block that follows, for the running block's last part
 
     def span_sum(self, window: int = 0) -> int:
         """Keys that the step's tokens attend to, summed over the tokens: a token at position p sees p + 1

@@ -207,16 +207,39 @@ def linear_tc_qkv(x, w_qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, bl
 SKINNY_MAX_TOKENS = 16
 
 
-def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "plain") -> None:
+def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "plain", norm_out=None,
+                  norm_in=None) -> None:
     """The same product for at most 16 tokens: a stream over the weights that
-    uses every SM, with no scratch memory."""
+    uses every SM, with no scratch memory.
+
+    The product can carry the RMS norms around it.  ``norm_out = (xg, gamma, bins, bins_clear)``: besides ``out``
+    it leaves ``xg`` (bfloat16 [m, n]) = out * gamma and adds the sums of squares of out's rows into ``bins`` (int64
+    [NORM_WORDS], zero before the call: exact accumulators that do not depend on the order of additions);
+    ``bins_clear`` (or None) is another such block, which is set to zero.  ``norm_in = (bins, eps)``: ``x`` holds
+    such rows times gamma, and the result is multiplied by 1 / sqrt(sum / k + eps) per row before bias and
+    activation."""
     m, k = x.shape
     n = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert w.shape[1] == k and out.shape == (m, n // 2 if epilogue == "swiglu" else n)
+    xg = gamma = bins_out = bins_clear = bins_in = None
+    eps = 0.0
+    if norm_out is not None:
+        xg, gamma, bins_out, bins_clear = norm_out
+        assert xg.dtype == torch.bfloat16 and xg.shape == (m, n) and gamma.numel() == n
+        assert bins_out.dtype == torch.int64 and bins_out.numel() == NORM_WORDS
+        assert bins_clear is None or (bins_clear.dtype == torch.int64 and bins_clear.numel() == NORM_WORDS)
+    if norm_in is not None:
+        assert norm_out is None, "a product is a norm's producer or its consumer"
+        bins_in, eps = norm_in
+        assert bins_in.dtype == torch.int64 and bins_in.numel() == NORM_WORDS
     _call("linear_skinny", "nncpu_linear_skinny", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
           _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
+          _ptr(xg), _ptr(gamma), _i(_code(gamma)), _ptr(bins_out), _ptr(bins_clear), _ptr(bins_in), _f(eps),
           _stream())
+
+
+NORM_WORDS = 256    # 64-bit words of the accumulators of one norm: 16 rows of 16 (8 bins, a flag, spare)
 
 
 def rope_table(positions, inv_freq, out, position_scale: float = 1.0, by_pair: bool = False) -> None:

@@ -23,6 +23,8 @@ from .base import Mixer, register_mixer
 
 @register_mixer("attention")
 class Attention(Mixer):
+    accepts_deferred_norm = True    # x goes to Runtime.linear, which finishes a norm's unfinished output
+
     def __init__(self, spec, reads_other_cache: bool = False):
         s = self.spec = spec
         self.shared_kv = reads_other_cache
@@ -114,11 +116,12 @@ class Attention(Mixer):
         with core:
             self._attend(ctx, q, cache, attn)
         with rt.phase("attn_out", self.w_o, n):
-            rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True)
+            # the last write into the residual stream: it may leave the next norm its input
+            rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
 
     def _fused_qkv(self, x, cache) -> bool:
         s = self.spec
-        return (not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
+        return (not isinstance(x, base.DeferredNorm) and not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
                 and self.w_qkv.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and (self.position is None or (self.position.tables_by_pair and self.position.half * 2 == s.head_dim))
                 and ops.linear_tc_qkv_supported(x, s.n_heads, s.n_kv_heads, s.head_dim))

@@ -13,7 +13,8 @@ Interfaces (``ctx`` is the engine's ``StepContext``; ``x`` is ``[n_tokens,
 hidden]`` in the run's element type; ``residual`` is the float32 residual
 stream ``[n_tokens, hidden]``):
 
-* ``Norm.forward(ctx, residual, rows=None) -> x``
+* ``Norm.forward(ctx, residual, rows=None) -> x``; optionally ``Norm.request(ctx, residual)`` (see
+  ``NormRequest``: at a few tokens a norm can ride on the products around it instead of being a launch)
 * ``Mixer.forward(ctx, x, residual, cache) -> None`` adds its output to
   ``residual``; ``cache`` is the ``EntryCache`` of the schedule entry.  A mixer
   asks for storage with ``kv_request()`` / ``state_request()``.
@@ -56,6 +57,48 @@ class Norm(Part):
     def forward(self, ctx, residual: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def request(self, ctx, residual: torch.Tensor) -> Optional["NormRequest"]:
+        """A request that whoever writes ``residual`` last before this norm reads it leaves the norm's input as
+        a by-product, or None if this norm (or this step) has no such short cut."""
+        return None
+
+
+@dataclass
+class NormRequest:
+    """Handed down through ``ctx.next_norm`` to the part that writes the residual stream last before ``norm``
+    reads it.  A part that can fulfil it passes it to ``Runtime.linear(..., then_norm=request)`` with that last
+    write and only with it; ``result`` is then a ``DeferredNorm``.  A part that ignores it loses nothing."""
+    norm: "Norm"
+    residual: torch.Tensor
+    gamma: torch.Tensor
+    eps: float
+    size: int
+    result: Optional["DeferredNorm"] = None
+
+
+@dataclass
+class DeferredNorm:
+    """A norm's output that is not finished: ``x_gamma`` [n, size] holds residual * gamma in the run's element
+    type and ``bins`` the exact accumulators of the sums of squares of the residual's rows.  ``Runtime.linear`` takes
+    it in place of a tensor: the few-token product turns the sums into the rows' scales and applies them in its
+    epilogue; any other path first makes the ordinary tensor with ``finish()``.  Only parts that set
+    ``accepts_deferred_norm`` are given one."""
+    x_gamma: torch.Tensor
+    bins: torch.Tensor
+    request: NormRequest
+
+    @property
+    def shape(self):
+        return self.x_gamma.shape
+
+    @property
+    def dtype(self):
+        return self.x_gamma.dtype
+
+    def finish(self, ctx=None) -> torch.Tensor:
+        """The norm's output as an ordinary tensor (the norm's own kernel on the residual it was asked for)."""
+        return self.request.norm.forward(ctx, self.request.residual)
+
 
 class PositionEncoding(Part):
     """``tables(ctx)`` gives float32 [n_tokens, half, 2]: for every token of the
@@ -81,6 +124,8 @@ class EntryCache:
 
 
 class Mixer(Part):
+    accepts_deferred_norm = False      # whether ``x`` may be a DeferredNorm (it is then passed to Runtime.linear)
+
     def kv_request(self) -> Optional[KVRequest]:
         return None
 
@@ -92,11 +137,17 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_deferred_norm = False      # whether ``x`` may be a DeferredNorm (it is then passed to Runtime.linear)
+
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
         raise NotImplementedError
 
 
 class Block(Part):
+    def entry_norm_request(self, ctx, residual: torch.Tensor) -> Optional[NormRequest]:
+        """The request of the norm this block begins with, for the block before it to fulfil (None: none)."""
+        return None
+
     def cache_requests(self) -> List[tuple]:
         """One (KVRequest or None, StateRequest or None) pair per mixer of the block, in the order in which
         ``forward`` finds their caches."""

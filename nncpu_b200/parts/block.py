@@ -33,8 +33,32 @@ class PreNormBlock(Block):
     def cache_requests(self):
         return [(self.mixer.kv_request(), self.mixer.state_request())]
 
+    def entry_norm_request(self, ctx, residual):
+        return self.norm1.request(ctx, residual) if self.mixer.accepts_deferred_norm else None
+
+    @staticmethod
+    def _normed(norm, consumer, ctx, residual, request):
+        """``norm``'s output for ``consumer``: what the writer of the residual left, if it fulfilled the request
+        of this very norm and the consumer takes it unfinished; else the norm's own kernel."""
+        if (request is not None and request.norm is norm and request.result is not None
+                and consumer.accepts_deferred_norm):
+            return request.result
+        return norm.forward(ctx, residual)
+
     def forward(self, ctx, residual, caches):
+        # At a few tokens the norms ride on the products around them: the block before may have left norm1's
+        # input (ctx.next_norm), the mixer's last product is asked for norm2's, and the feed-forward's last
+        # product for the first norm of the block that follows (ctx.after_block).
+        handed, after = ctx.next_norm, ctx.after_block
+        ctx.next_norm = ctx.after_block = None
         with self.rt.scope():       # the mixer's temporaries are done with when the feed-forward starts
-            self.mixer.forward(ctx, self.norm1.forward(ctx, residual), residual, caches[0])
+            x = self._normed(self.norm1, self.mixer, ctx, residual, handed)
+            asked = self.norm2.request(ctx, residual) if self.feed_forward.accepts_deferred_norm else None
+            ctx.next_norm = asked
+            self.mixer.forward(ctx, x, residual, caches[0])
+            ctx.next_norm = None
         with self.rt.scope():
-            self.feed_forward.forward(ctx, self.norm2.forward(ctx, residual), residual)
+            x = self._normed(self.norm2, self.feed_forward, ctx, residual, asked)
+            ctx.next_norm = after
+            self.feed_forward.forward(ctx, x, residual)
+        # ctx.next_norm stays: the block that follows finds its request there, fulfilled or not

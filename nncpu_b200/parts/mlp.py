@@ -15,6 +15,8 @@ from .base import FeedForward, register_feed_forward
 
 @register_feed_forward("gated_mlp")
 class GatedMlp(FeedForward):
+    accepts_deferred_norm = True    # x goes to Runtime.linear, which finishes a norm's unfinished output
+
     def __init__(self, spec):
         if spec.activation != "silu":
             raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported (supported: silu)")
@@ -58,4 +60,5 @@ class GatedMlp(FeedForward):
             with rt.phase("ffn_act"):
                 ops.swiglu(gate_up, act)
         with rt.phase("ffn_down", self.w_down, n):
-            rt.linear(act, self.w_down, None, residual, accumulate=True)
+            # the last write into the residual stream: it may leave the next norm its input
+            rt.linear(act, self.w_down, None, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))

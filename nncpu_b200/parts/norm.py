@@ -2,9 +2,11 @@
 (crates/nncpu/src/kernels/scalar.rs:270-292), computed in 32-bit."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from ..weights.params import ParamSpec
-from .base import Norm, register_norm
+from .base import Norm, NormRequest, register_norm
 
 
 @register_norm("rmsnorm")
@@ -26,3 +28,10 @@ class RMSNorm(Norm):
         with self.rt.phase("norm"):
             ops.rmsnorm(residual, self.gamma, self.eps, out, rows)
         return out
+
+    def request(self, ctx, residual):
+        """At up to 16 tokens in a bfloat16 run the few-token products around this norm can carry it."""
+        if (ctx.n_tokens > ops.SKINNY_MAX_TOKENS or self.rt.dtype != torch.bfloat16 or self.size % 8
+                or residual.dtype != torch.float32):
+            return None
+        return NormRequest(self, residual, self.gamma, self.eps, self.size)

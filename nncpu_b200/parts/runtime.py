@@ -12,6 +12,7 @@ import torch
 from .. import perf
 from ..errors import ExtensionError
 from ..kernels import ops
+from .base import DeferredNorm
 
 
 class Arena:
@@ -103,6 +104,8 @@ class Runtime:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._workspace = None
         self.arena: Optional[Arena] = None      # set by the engine around a step; without one, the allocator serves
+        self._norm_bins = None          # accumulators of the norms that ride on the few-token products
+        self._norm_turn = 0
         self._status_host = None
         self._status_posted = []
         self._status_turn = 0
@@ -144,18 +147,52 @@ class Runtime:
     def tensor_cores_take(self, x_dtype, w, k: int) -> bool:
         return x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.linear_tc_supported(1, w.shape[0], k)
 
-    def linear(self, x, w, bias, out, accumulate: bool = False, epilogue: str = "plain") -> None:
+    def linear(self, x, w, bias, out, accumulate: bool = False, epilogue: str = "plain", then_norm=None) -> None:
         """out (+)= x . w^T + bias.  bfloat16 inputs whose sizes keep TMA's
         alignment rule go to the tensor cores; everything else, and every
-        float32 product, runs in true 32-bit on CUDA cores."""
+        float32 product, runs in true 32-bit on CUDA cores.
+
+        ``x`` may be a ``DeferredNorm`` (a norm's unfinished output): the few-token product finishes it, any
+        other path makes the ordinary tensor first.  ``then_norm`` (a ``NormRequest``): this product is the last
+        write into ``out`` before that norm reads it; where the few-token product runs it fulfils the request."""
+        deferred = x if isinstance(x, DeferredNorm) else None
+        few = (x.shape[0] <= ops.SKINNY_MAX_TOKENS and self.tensor_cores_take(x.dtype, w, x.shape[1]))
+        if deferred is not None:
+            if few:
+                x, norm_in = deferred.x_gamma, (deferred.bins, deferred.request.eps)
+            else:
+                x, norm_in = deferred.finish(), None
+        else:
+            norm_in = None
         if self.tensor_cores_take(x.dtype, w, x.shape[1]):
-            if x.shape[0] <= ops.SKINNY_MAX_TOKENS:
-                ops.linear_skinny(x, w, bias, out, accumulate, epilogue)
+            if few:
+                norm_out = None
+                if (then_norm is not None and self._norm_bins is not None and epilogue == "plain" and out.dtype == torch.float32
+                        and out.shape[1] == then_norm.size == w.shape[0] and out.is_contiguous()):
+                    m, n = out.shape
+                    # two blocks of accumulators take turns: this product adds into one (zero since it was last
+                    # cleared) and clears the other, whose consumer has run by now
+                    mine, other = self._norm_bins[self._norm_turn], self._norm_bins[1 - self._norm_turn]
+                    self._norm_turn = 1 - self._norm_turn
+                    made = DeferredNorm(self.empty(m, n, keep=True), mine, then_norm)
+                    norm_out = (made.x_gamma, then_norm.gamma, mine, other)
+                ops.linear_skinny(x, w, bias, out, accumulate, epilogue, norm_out, norm_in)
+                if norm_out is not None:
+                    then_norm.result = made
             else:
                 ops.linear_tc(x, w, bias, out, self.workspace, accumulate, epilogue)
         else:
             assert epilogue == "plain", "the fused epilogue exists on the tensor-core path only"
             ops.linear_simt(x, w, bias, out, accumulate)
+
+    def begin_norm_fusion(self) -> None:
+        """Once per step that may fuse norms into the few-token products: both blocks of accumulators start at
+        zero (one small fill), whatever an earlier step or another captured graph left in them."""
+        if self._norm_bins is None:
+            self._norm_bins = torch.zeros(2, ops.NORM_WORDS, dtype=torch.int64, device=self.device)
+        else:
+            self._norm_bins.zero_()
+        self._norm_turn = 0
 
     def phase(self, slot: str, weight=None, n_tokens: int = 0, nbytes: float = 0, flops: float = 0):
         """A profiler scope for the launches of one phase (free when the profiler is off).  With ``weight`` the

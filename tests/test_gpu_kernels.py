@@ -206,6 +206,57 @@ def test_linear_for_few_tokens_with_gated_epilogue(ops, m, inter, k):
         check(out, want, tol, "few tokens, gated epilogue")
 
 
+@pytest.mark.parametrize("m,hidden,inter", [(1, 64, 48), (5, 200, 136), (8, 4096, 512), (13, 1000, 264), (16, 320, 4096),
+                                            (3, 5120, 64), (16, 8192, 32)])
+def test_few_token_products_carry_the_norm_between_them(ops, m, hidden, inter):
+    """residual += act . w_down^T, then rmsnorm(residual) . w_next^T: the first product leaves residual * gamma and
+    its blocks' sums of squares, the second one finishes the norm in its epilogue.  Against the plain norm and
+    products, for the plain and the gated epilogue, with a width that is no multiple of 16."""
+    g = torch.Generator().manual_seed(m + hidden + inter)
+    act = torch.randn(m, inter, generator=g).bfloat16().to(DEV)
+    w_down = (torch.randn(hidden, inter, generator=g) * 0.1).bfloat16().to(DEV)
+    residual0 = torch.randn(m, hidden, generator=g).to(DEV)
+    gamma = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16().to(DEV)
+    eps = 1e-5
+    residual = residual0.clone()
+    xg = torch.full((m, hidden), 9.0, dtype=torch.bfloat16, device=DEV)
+    bins = torch.zeros(ops.NORM_WORDS, dtype=torch.int64, device=DEV)
+    stale = torch.full((ops.NORM_WORDS,), 77, dtype=torch.int64, device=DEV)
+    ops.linear_skinny(act, w_down, None, residual, accumulate=True, norm_out=(xg, gamma, bins, stale))
+    plain = residual0.clone()
+    ops.linear_skinny(act, w_down, None, plain, accumulate=True)
+    assert torch.equal(residual, plain)                                   # the product itself is untouched
+    assert int(stale.abs().max()) == 0                                    # the other norm's accumulators are cleared
+    check(xg, residual * gamma.float(), 8e-3, "residual * gamma")
+    # the accumulators hold the sums of the blocks' float sums exactly: bin b counts units of 2^(32 b - 150)
+    words = bins.view(16, 16).cpu().numpy().astype(object)
+    total = np.array([float(sum(int(words[t][b]) * 2.0 ** (32 * b - 150) for b in range(8))) for t in range(m)])
+    want_ss = (residual.double() ** 2).sum(-1).cpu().numpy()
+    assert np.abs(total - want_ss).max() <= 1e-6 * want_ss.max() and int(bins.view(16, 16)[:, 8].sum()) == 0
+    again_bins = torch.zeros_like(bins)                                   # the same bits whatever the blocks' order
+    ops.linear_skinny(act, w_down, None, residual0.clone(), accumulate=True, norm_out=(torch.empty_like(xg), gamma, again_bins, None))
+    assert torch.equal(again_bins, bins)
+    normed = P.rmsnorm(residual.cpu().numpy(), gamma.float().cpu().numpy(), eps)
+    n_out = 16 * ((inter + 15) // 16)
+    w_next = (torch.randn(n_out, hidden, generator=g) * 0.1).bfloat16().to(DEV)
+    bias = torch.randn(n_out, generator=g).to(DEV)
+    out = torch.full((m, n_out), 9.0, device=DEV)
+    ops.linear_skinny(xg, w_next, bias, out, norm_in=(bins, eps))
+    want = P.linear(normed, w_next.float().cpu().numpy(), bias.cpu().numpy())
+    check(out, want, 8e-3, "consumer, plain epilogue")                    # x * gamma was rounded to bfloat16 on the way
+    gated = torch.full((m, n_out // 2), 9.0, device=DEV)
+    ops.linear_skinny(xg, w_next, None, gated, epilogue="swiglu", norm_in=(bins, eps))
+    y = P.linear(normed, w_next.float().cpu().numpy()).reshape(m, -1, 2, 8)
+    check(gated, P.swiglu(y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)), 8e-3, "consumer, gated epilogue")
+    # a row that is not finite has no finite scale: NaN comes out, as from the norm itself
+    bad = residual0.clone()
+    bad[0, 3] = float("inf")
+    bins.zero_()
+    ops.linear_skinny(act, w_down, None, bad, accumulate=True, norm_out=(xg, gamma, bins, None))
+    ops.linear_skinny(xg, w_next, None, out, norm_in=(bins, eps))
+    assert torch.isnan(out[0]).all() and (m == 1 or torch.isfinite(out[1:]).all())
+
+
 def test_linear_for_few_tokens_refuses(ops):
     x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)

@@ -71,7 +71,8 @@ def test_phases_add_up_and_count_the_models_bytes(dtype, hidden):
     assert sum(decode[k]["bytes"] for k in PRODUCTS) == n_decode * model.weight_bytes_per_step()
     assert sum(prefill[k]["bytes"] for k in PRODUCTS) == model.weight_bytes_per_step()
     assert decode["attn_qkv"]["calls"] == n_decode * 4 and decode["lm_head"]["calls"] == n_decode
-    assert decode["norm"]["calls"] == n_decode * 9 and decode["embed"]["calls"] == n_decode
+    # in bfloat16 the few-token products carry the norms between them: only the first and the final norm are launches
+    assert decode["norm"]["calls"] == n_decode * (2 if dtype == "bfloat16" else 9) and decode["embed"]["calls"] == n_decode
     # attention counts, per token, the keys and values of its span
     spec = model.spec.layers[0].mixer
     row = 2 * spec.n_kv_heads * spec.head_dim * (2 if dtype == "bfloat16" else 4)
