@@ -317,13 +317,71 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 // ---------------------------------------------------------------------------
 constexpr int kDecodeStages = 3;
 
-template <int HD, int NT, bool kCluster>
+// The decode kernel can start from the float32 q/k/v projections of its tokens instead of finished queries: every
+// block then makes its own queries (per-head RMS norm, rotation: crates/nncpu/src/model/forward.rs:278-324), and the
+// block whose keys end with the token itself also makes the token's key and value, appends them to the cache for the
+// steps to come, and puts them into its copy of the page, where nobody else looks for them in this step.  The
+// arithmetic is that of the separate kernel for norm, rotation and append, operation for operation.
+struct FusedQK {
+    const float* qkv;         // [n_tok, per_tok * HD]: the heads of q, then (if appended here) of k, then of v
+    int per_tok;              // heads a token's row holds
+    const void* q_gamma;      // per-head norm weights [HD], or null
+    const void* k_gamma;
+    int g_dt;
+    float eps;
+    const float2* cs;         // [n_tok, HD / 2] (cos, sin) of the tokens' positions, or null: no rotation
+    __nv_bfloat16* k_pages;   // the cache, writable; null: the keys and values are another entry's, nothing is appended
+    __nv_bfloat16* v_pages;
+};
+
+// One head's HD float32 values through norm (if gamma) and rotation (if cs) to bfloat16; a warp's job.  A lane holds
+// HD / 32 neighbouring lanes of the head, so a rotation pair (i, i + HD / 2) sits in the lanes l and l ^ 16.
+template <int HD>
+__device__ __forceinline__ void finish_head(const float* __restrict__ src, const void* __restrict__ gamma, int g_dt, float eps,
+                                            const float2* __restrict__ cs_row, __nv_bfloat16* __restrict__ dst, int lane) {
+    constexpr int EPL = HD / 32;
+    float x[EPL];
+    if (EPL == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src + lane * EPL);
+        x[0] = v.x; x[1] = v.y; x[2 % EPL] = v.z; x[3 % EPL] = v.w;
+    } else {
+        const float2 v = *reinterpret_cast<const float2*>(src + lane * EPL);
+        x[0] = v.x; x[1] = v.y;
+    }
+    if (gamma) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) ss = fmaf(x[e], x[e], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float scale = 1.0f / sqrtf(ss * (1.0f / (float)HD) + eps);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) x[e] = (x[e] * scale) * ld_f(gamma, lane * EPL + e, g_dt);
+    }
+    if (cs_row != nullptr) {
+        const int i0 = (lane & 15) * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+            const float2 c = cs_row[i0 + e];
+            x[e] = lane < 16 ? c.x * x[e] - c.y * other : c.y * other + c.x * x[e];
+        }
+    }
+    if (EPL == 4) {
+        __nv_bfloat162 o[2] = {__floats2bfloat162_rn(x[0], x[1]), __floats2bfloat162_rn(x[2 % EPL], x[3 % EPL])};
+        *reinterpret_cast<uint2*>(dst + lane * 4) = *reinterpret_cast<uint2*>(o);
+    } else {
+        *reinterpret_cast<__nv_bfloat162*>(dst + lane * 2) = __floats2bfloat162_rn(x[0], x[1]);
+    }
+}
+
+template <int HD, int NT, bool kCluster, bool kFused>
 __global__ void __launch_bounds__(128, 2)
 decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv, float scale2,
-                   int window) {
+                   int window, const FusedQK f) {
     constexpr int kTileBytes = kPage * HD * 2;
     constexpr int kChunks = HD / 8;
     constexpr int W = HD + 2;
@@ -367,12 +425,37 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
     if (p0 + 1 <= p1) issue(p0 + 1, 1);
     cp_async_commit();
 
+    // Started from the projections: this block's queries, and, in the block whose pages end with the token's own
+    // position, the token's key and value (appended to the cache for later steps; for this step they are put into
+    // the block's copy of the page when that has arrived).
+    __shared__ __align__(16) __nv_bfloat16 q_s[kFused ? 16 * HD : 8];
+    __shared__ __align__(16) __nv_bfloat16 kv_s[kFused ? 2 * HD : 8];
+    const bool owner = kFused && f.k_pages != nullptr && p0 <= p_last && p_last <= p1;
+    if constexpr (kFused) {
+        const float* row = f.qkv + (size_t)t * f.per_tok * HD;
+        const float2* cs_row = f.cs ? f.cs + (size_t)t * (HD / 2) : nullptr;
+        for (int g = warp; g < G; g += 4)
+            finish_head<HD>(row + (size_t)(kvh * G + g) * HD, f.q_gamma, f.g_dt, f.eps, cs_row, q_s + g * HD, lane);
+        if (owner) {
+            if (warp == 0)
+                finish_head<HD>(row + (size_t)(n_heads + kvh) * HD, f.k_gamma, f.g_dt, f.eps, cs_row, kv_s, lane);
+            if (warp == 1)
+                finish_head<HD>(row + (size_t)(n_heads + n_kv + kvh) * HD, nullptr, 0, 0.0f, nullptr, kv_s + HD, lane);
+        }
+        __syncthreads();
+        if (owner && threadIdx.x < 2 * kChunks) {
+            const int which = threadIdx.x / kChunks, chunk = threadIdx.x % kChunks;
+            __nv_bfloat16* page = (which ? f.v_pages : f.k_pages) +
+                                  (((size_t)table[p_last] * n_kv + kvh) * kPage + pos % kPage) * (size_t)HD;
+            *reinterpret_cast<uint4*>(page + chunk * 8) = *reinterpret_cast<const uint4*>(kv_s + which * HD + chunk * 8);
+        }
+    }
     // queries of the heads 8 * tt + r as right-hand operands: (lanes 2c, 2c + 1) and (2c + 8, 2c + 9) of each 16
     uint32_t qb[NT][HD / 16][2];
 #pragma unroll
     for (int tt = 0; tt < NT; ++tt) {
         const bool ok = 8 * tt + r < G;
-        const __nv_bfloat16* qrow = q + out_row + (size_t)(8 * tt + r) * HD;
+        const __nv_bfloat16* qrow = kFused ? q_s + (size_t)(8 * tt + r) * HD : q + out_row + (size_t)(8 * tt + r) * HD;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
             qb[tt][ks][0] = ok ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c) : 0u;
@@ -395,6 +478,15 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
         __syncthreads();           // everybody's have, and everybody is done with the stage refilled next
         if (pg + 2 <= p1) issue(pg + 2, (pg + 2 - p0) % kDecodeStages);
         cp_async_commit();
+        if (kFused && owner && pg == p_last) {
+            // the token's own key and value take their row of the page that has just arrived
+            if (threadIdx.x < 2 * kChunks) {
+                const int which = threadIdx.x / kChunks, chunk = threadIdx.x % kChunks;
+                *reinterpret_cast<uint4*>(dsm + stage * 2 * kTileBytes + which * kTileBytes + tile_off<HD>(pos % kPage, chunk)) =
+                    *reinterpret_cast<const uint4*>(kv_s + which * HD + chunk * 8);
+            }
+            __syncthreads();
+        }
         const int k0 = pg * kPage + 16 * warp;             // this warp's 16 keys of the page
         if (k0 > pos || k0 + 15 < first) continue;
         const uint32_t ks_addr = smem_u32_(dsm) + stage * 2 * kTileBytes;
@@ -545,21 +637,25 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
 template <int HD>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                   const int* tok_seq, const int* tok_pos, void* out, float* scratch, int n_tok, int n_heads, int n_kv,
-                  float scale, int window, int n_splits, cudaStream_t stream) {
+                  float scale, int window, int n_splits, cudaStream_t stream, const FusedQK* fused = nullptr) {
     using Kernel = void (*)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, const int*, int, const int*,
-                            const int*, __nv_bfloat16*, float*, float*, int, int, float, int);
+                            const int*, __nv_bfloat16*, float*, float*, int, int, float, int, const FusedQK);
     const int G = n_heads / n_kv;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_tok * n_kv * n_splits * G * HD : nullptr;
     // without scratch the splits merge inside a cluster (the caller checked n_splits <= 8)
     const bool cluster = scratch == nullptr && n_splits > 1;
-    const Kernel kernel = cluster ? (G <= 8 ? (Kernel)decode_kernel<HD, 1, true> : (Kernel)decode_kernel<HD, 2, true>)
-                                  : (G <= 8 ? (Kernel)decode_kernel<HD, 1, false> : (Kernel)decode_kernel<HD, 2, false>);
+    const Kernel plain = cluster ? (G <= 8 ? (Kernel)decode_kernel<HD, 1, true, false> : (Kernel)decode_kernel<HD, 2, true, false>)
+                                 : (G <= 8 ? (Kernel)decode_kernel<HD, 1, false, false> : (Kernel)decode_kernel<HD, 2, false, false>);
+    const Kernel from_qkv = cluster ? (G <= 8 ? (Kernel)decode_kernel<HD, 1, true, true> : (Kernel)decode_kernel<HD, 2, true, true>)
+                                    : (G <= 8 ? (Kernel)decode_kernel<HD, 1, false, true> : (Kernel)decode_kernel<HD, 2, false, true>);
+    const Kernel kernel = fused ? from_qkv : plain;
+    const FusedQK f = fused ? *fused : FusedQK{};
     const size_t stages = (size_t)kDecodeStages * 2 * kPage * HD * 2;
     const size_t merge = (size_t)5 * G * (HD + 2) * sizeof(float);
     const size_t smem = stages > merge ? stages : merge;
-    static bool configured[4][64] = {};
-    if (first_use_on_this_device(configured[(cluster ? 2 : 0) + (G <= 8 ? 0 : 1)])) {
+    static bool configured[8][64] = {};
+    if (first_use_on_this_device(configured[(fused ? 4 : 0) + (cluster ? 2 : 0) + (G <= 8 ? 0 : 1)])) {
         const cudaError_t e = cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    (int)(stages > (size_t)5 * 16 * (HD + 2) * 4 ? stages : (size_t)5 * 16 * (HD + 2) * 4));
         NN_CHECK(e == cudaSuccess, "attention decode: cannot reserve shared memory: %s", cudaGetErrorString(e));
@@ -578,7 +674,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     cfg.numAttrs = cluster ? 1 : 0;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                                              (const __nv_bfloat16*)v_pages, block_table, bt_stride, tok_seq, tok_pos,
-                                             (__nv_bfloat16*)out, part_o, part_ml, n_heads, n_kv, scale * kLog2e, window);
+                                             (__nv_bfloat16*)out, part_o, part_ml, n_heads, n_kv, scale * kLog2e, window, f);
     NN_CHECK(e == cudaSuccess, "attention decode (%d splits%s): launch failed: %s", n_splits, cluster ? ", cluster" : "",
              cudaGetErrorString(e));
     if (n_splits > 1 && !cluster) {
@@ -647,6 +743,47 @@ extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, co
                                  n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream);
     return launch_decode<128>(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
                               n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream);
+}
+
+// The same from the float32 projections: qkv [n_tok, per_tok * hd] holds, per token, the heads of q and, if `append`,
+// of k and v after them (per_tok = n_heads + 2 n_kv, else n_heads).  Every block makes its queries itself (per-head RMS
+// norm with q_gamma if given, rotation by cos_sin [n_tok, hd / 2, 2] if given); with `append` the token's key (k_gamma,
+// rotation) and value are made too, written to their row of the cache pages and used in this step.  Replaces the
+// separate kernel for norm, rotation and append in a decode step; the arithmetic is the same.
+extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void* q_gamma, const void* k_gamma, int g_dt,
+                                                   float eps, const float* cos_sin, void* k_pages, void* v_pages,
+                                                   int append, const int* block_table, int bt_stride,
+                                                   const int* tok_seq, const int* tok_pos, void* out, float* scratch,
+                                                   long scratch_floats, int n_tok, int n_heads, int n_kv, int hd,
+                                                   float scale, int window, int n_splits, void* stream) {
+    NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
+             "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
+             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+    NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535 && window >= 0, "attention decode: %d tokens, %d splits",
+             n_tok, n_splits);
+    NN_CHECK(qkv != nullptr && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)cos_sin % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 &&
+                 ((uintptr_t)v_pages % 16) == 0,
+             "attention decode (from projections): the projections and the cache must be 16-byte aligned, the rotation "
+             "table 8-byte aligned");
+    if (scratch == nullptr && n_splits > 1)
+        NN_CHECK(n_splits <= 8, "attention decode: %d splits without scratch (a cluster merges at most 8)", n_splits);
+    else
+        NN_CHECK(scratch_floats >= nncpu_attention_decode_scratch_floats(n_tok, n_heads, n_kv, hd, n_splits),
+                 "attention decode: %ld floats of scratch, %ld needed", scratch_floats,
+                 nncpu_attention_decode_scratch_floats(n_tok, n_heads, n_kv, hd, n_splits));
+    if (n_tok == 0) return 0;
+    FusedQK f{};
+    f.qkv = qkv;
+    f.per_tok = append ? n_heads + 2 * n_kv : n_heads;
+    f.q_gamma = q_gamma; f.k_gamma = k_gamma; f.g_dt = g_dt; f.eps = eps;
+    f.cs = (const float2*)cos_sin;
+    f.k_pages = append ? (__nv_bfloat16*)k_pages : nullptr;
+    f.v_pages = append ? (__nv_bfloat16*)v_pages : nullptr;
+    if (hd == 64)
+        return launch_decode<64>(nullptr, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
+                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, &f);
+    return launch_decode<128>(nullptr, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
+                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, &f);
 }
 
 // Any mix of new tokens per sequence: sequence b brings the flat tokens cu_seqlens[b] .. cu_seqlens[b + 1] - 1

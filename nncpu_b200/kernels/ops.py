@@ -323,6 +323,28 @@ def attention_decode_mma(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out
           _f(scale), _i(window), _i(n_splits), _stream())
 
 
+def attention_decode_mma_from_qkv(qkv, q_gamma, k_gamma, eps, cos_sin, k_pages, v_pages, append: bool, block_table,
+                                  tok_seq, tok_pos, out, scratch, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                                  window: int, n_splits: int) -> None:
+    """Decode attention that starts from the float32 projections ``qkv`` [n, per_tok * head_dim] (q heads, then with
+    ``append`` the k and v heads): every block makes its queries itself (per-head norm, rotation by ``cos_sin``
+    [n, head_dim / 2, 2]), and with ``append`` the token's key and value are made, written to the cache and used.
+    One launch in place of ``qk_norm_rope_append`` and ``attention_decode_mma``, with the same arithmetic."""
+    n = out.shape[0]
+    per_tok = n_heads + 2 * n_kv if append else n_heads
+    assert qkv.dtype == torch.float32 and qkv.shape == (n, per_tok * head_dim) and qkv.is_contiguous()
+    assert out.shape == (n, n_heads * head_dim) and out.dtype == torch.bfloat16
+    assert k_pages.dtype == v_pages.dtype == torch.bfloat16 and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (n, head_dim // 2, 2))
+    assert q_gamma is None or k_gamma is None or q_gamma.dtype == k_gamma.dtype
+    assert scratch is None or scratch.dtype == torch.float32
+    g = q_gamma if q_gamma is not None else k_gamma
+    _call("attention_mma", "nncpu_attention_decode_mma_from_qkv", _ptr(qkv), _ptr(q_gamma), _ptr(k_gamma), _i(_code(g)),
+          _f(eps), _ptr(cos_sin), _ptr(k_pages), _ptr(v_pages), _i(append), _ptr(block_table), _i(block_table.shape[1]),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _ptr(scratch), ctypes.c_long(0 if scratch is None else scratch.numel()),
+          _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _i(n_splits), _stream())
+
+
 def attention_prefill_mma(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, n_seqs: int, n_heads: int,
                           n_kv: int, head_dim: int, scale: float, window: int) -> None:
     """Any number of new tokens per sequence, at consecutive positions."""

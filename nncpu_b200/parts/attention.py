@@ -85,16 +85,19 @@ class Attention(Mixer):
         s, rt = self.spec, self.rt
         n = x.shape[0]
         eps = s.qk_norm.eps if s.qk_norm else 0.0
-        q = rt.empty(n, self.q_size)
+        attn = rt.empty(n, self.q_size)
         if self._fused_qkv(x, cache):
             # a prompt: norm, rotation and the cache append happen in the projection's epilogue, on its
             # float32 accumulators; its threads are tokens, so the rotation table is laid out by pair
+            q = rt.empty(n, self.q_size)
             with rt.phase("attn_rope"):
                 cos_sin = None if self.position is None else self.position.tables(ctx, by_pair=True)
             with rt.phase("attn_qkv", self.w_qkv, n):
                 ops.linear_tc_qkv(x, self.w_qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
                                   cache.block_table, cache.k_pages, cache.v_pages, q, rt.workspace, s.n_heads,
                                   s.n_kv_heads, s.head_dim)
+            with self._core_phase(ctx, cache):
+                self._attend(ctx, q, cache, attn)
         else:
             # the projections stay in float32 until the per-head norm and the rotation have been applied
             qkv = rt.empty(n, self.q_size + 2 * self.kv_size, dtype=torch.float32)
@@ -102,22 +105,54 @@ class Attention(Mixer):
                 rt.linear(x, self.w_qkv, self.b_qkv, qkv)
             with rt.phase("attn_rope"):
                 cos_sin = None if self.position is None else self.position.tables(ctx)
-                ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
-                                        cache.block_table, cache.k_pages, cache.v_pages, q, s.n_heads,
-                                        0 if self.shared_kv else s.n_kv_heads, s.head_dim)
-        attn = rt.empty(n, self.q_size)
-        if perf.enabled():
-            # every token streams the keys and values of its span (crates/nncpu/src/model/forward.rs:382-386)
-            keys = ctx.span_sum(s.window)
-            core = rt.phase("attn_core", nbytes=2.0 * keys * s.n_kv_heads * s.head_dim * cache.k_pages.element_size(),
-                            flops=4.0 * keys * self.q_size)
-        else:
-            core = perf._NULL
-        with core:
-            self._attend(ctx, q, cache, attn)
+            if self._decode_from_projections(ctx, cache):
+                # a decode step: norm, rotation and append are the attention kernel's own first steps
+                with self._core_phase(ctx, cache):
+                    n_splits, scratch = self._decode_splits(ctx)
+                    ops.attention_decode_mma_from_qkv(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, cache.k_pages,
+                                                      cache.v_pages, not self.shared_kv, cache.block_table, ctx.tok_seq,
+                                                      ctx.tok_pos, attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim,
+                                                      s.scale, s.window, n_splits)
+            else:
+                q = rt.empty(n, self.q_size)
+                with rt.phase("attn_rope"):
+                    ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
+                                            cache.block_table, cache.k_pages, cache.v_pages, q, s.n_heads,
+                                            0 if self.shared_kv else s.n_kv_heads, s.head_dim)
+                with self._core_phase(ctx, cache):
+                    self._attend(ctx, q, cache, attn)
         with rt.phase("attn_out", self.w_o, n):
             # the last write into the residual stream: it may leave the next norm its input
             rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+
+    def _core_phase(self, ctx, cache):
+        """The profiler's scope of the attention itself: every token streams the keys and values of its span
+        (crates/nncpu/src/model/forward.rs:382-386)."""
+        if not perf.enabled():
+            return perf._NULL
+        s = self.spec
+        keys = ctx.span_sum(s.window)
+        return self.rt.phase("attn_core", nbytes=2.0 * keys * s.n_kv_heads * s.head_dim * cache.k_pages.element_size(),
+                             flops=4.0 * keys * self.q_size)
+
+    def _decode_from_projections(self, ctx, cache) -> bool:
+        """Whether this step's attention can start from the float32 projections: a decode step on the tensor-core
+        kernel, every lane of a head rotated (or none), norm weights of one type."""
+        s = self.spec
+        return (ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
+                and ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim)
+                and (self.position is None or self.position.half * 2 == s.head_dim)
+                and (self.q_gamma is None or self.k_gamma is None or self.q_gamma.dtype == self.k_gamma.dtype))
+
+    def _decode_splits(self, ctx):
+        """Splits of every token's keys in a decode step, and the scratch their merge needs (None: they merge
+        inside a thread-block cluster)."""
+        s = self.spec
+        longest = min(ctx.max_kv_len, s.window) if s.window > 0 else ctx.max_kv_len
+        n_splits = ops.attention_decode_splits(ctx.n_tokens, s.n_kv_heads, longest, self.rt.sm_count)
+        floats = 0 if n_splits <= ops.DECODE_CLUSTER_MAX_SPLITS else ops.attention_decode_scratch_floats(
+            ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
+        return n_splits, (self.rt.empty(floats, dtype=torch.float32) if floats else None)
 
     def _fused_qkv(self, x, cache) -> bool:
         s = self.spec
@@ -135,12 +170,7 @@ class Attention(Mixer):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
                           s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
         elif ctx.is_decode:
-            longest = min(ctx.max_kv_len, s.window) if s.window > 0 else ctx.max_kv_len
-            n_splits = ops.attention_decode_splits(ctx.n_tokens, s.n_kv_heads, longest, self.rt.sm_count)
-            # few splits merge inside a thread-block cluster; more go through scratch and a merge kernel
-            floats = 0 if n_splits <= ops.DECODE_CLUSTER_MAX_SPLITS else ops.attention_decode_scratch_floats(
-                ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
-            scratch = self.rt.empty(floats, dtype=torch.float32) if floats else None
+            n_splits, scratch = self._decode_splits(ctx)
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
                                      attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits)
         elif ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(

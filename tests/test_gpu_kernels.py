@@ -530,6 +530,53 @@ def test_attention_tensor_core_decode(ops, nh, nkv, hd, window):
             assert torch.equal(clustered, out)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,with_norm,with_rope", [(4, 2, 64, 0, True, True), (8, 1, 128, 0, True, True),
+                                                                  (32, 8, 128, 0, True, True), (16, 1, 64, 70, False, True),
+                                                                  (3, 3, 128, 33, True, False), (12, 2, 128, 500, True, True)])
+def test_attention_decode_from_the_projections(ops, nh, nkv, hd, window, with_norm, with_rope):
+    """One launch (norm, rotation and append as the attention kernel's first steps) against the two it replaces:
+    the same outputs and the same cache rows, bit for bit, for every number of splits, with a padding row, with
+    sequences whose new token opens a page (position 64) or closes one (63), and also when the keys and values
+    are another entry's (queries only, nothing appended)."""
+    seqs = [700, 1, 64, 65, 16, 17, 300]
+    kp0, vp0, table, _, _ = scatter_pages(24, nkv, hd, seqs, torch.bfloat16, seed=hd + nh)
+    tok_seq = torch.tensor([0, 1, 2, -1, 3, 4, 5, 6], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([699, 0, 63, 5, 64, 15, 16, 299], dtype=torch.int32, device=DEV)
+    n = len(tok_seq)
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd, generator=g).to(DEV)
+    qg = (1 + 0.1 * torch.randn(hd, generator=g)).bfloat16().to(DEV) if with_norm else None
+    kg = (1 + 0.1 * torch.randn(hd, generator=g)).bfloat16().to(DEV) if with_norm else None
+    cs = None
+    if with_rope:
+        inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+        cs = torch.empty(n, hd // 2, 2, device=DEV)
+        ops.rope_table(tok_pos, inv.float().to(DEV), cs)
+    scale = 1.0 / math.sqrt(hd)
+    for n_splits in (1, 3, 8, 20):
+        floats = ops.attention_decode_scratch_floats(n, nh, nkv, hd, n_splits)
+        for use_scratch in ([True] if n_splits > 8 else [True, False] if n_splits > 1 else [False]):
+            scratch = torch.empty(floats, device=DEV) if (use_scratch and floats) else None
+            kp, vp = kp0.clone(), vp0.clone()
+            q = torch.empty(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+            ops.qk_norm_rope_append(qkv, qg, kg, 1e-6, cs, tok_seq, tok_pos, table, kp, vp, q, nh, nkv, hd)
+            want = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+            ops.attention_decode_mma(q, kp, vp, table, tok_seq, tok_pos, want, scratch, nh, nkv, hd, scale, window, n_splits)
+            kp2, vp2 = kp0.clone(), vp0.clone()
+            got = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+            ops.attention_decode_mma_from_qkv(qkv, qg, kg, 1e-6, cs, kp2, vp2, True, table, tok_seq, tok_pos, got, scratch,
+                                              nh, nkv, hd, scale, window, n_splits)
+            assert torch.equal(got, want), (n_splits, use_scratch)
+            assert torch.equal(kp2, kp) and torch.equal(vp2, vp)          # the same rows were appended, and only those
+            # queries only: the cache already holds the token's key and value (another entry appended them)
+            q_only = qkv[:, :nh * hd].contiguous()
+            kp3, vp3 = kp.clone(), vp.clone()
+            shared = torch.full((n, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+            ops.attention_decode_mma_from_qkv(q_only, qg, None, 1e-6, cs, kp3, vp3, False, table, tok_seq, tok_pos, shared,
+                                              scratch, nh, nkv, hd, scale, window, n_splits)
+            assert torch.equal(shared, want) and torch.equal(kp3, kp) and torch.equal(vp3, vp)
+
+
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 0), (8, 1, 128, 0), (6, 3, 128, 40), (16, 1, 64, 17)])
 def test_attention_tensor_core_prefill(ops, nh, nkv, hd, window):
     # sequence 0 adds 70 tokens to 130 cached ones, 1 starts with 1 token, 2 starts with 100, 3 adds 1 to 64, 4 adds 16 to 5
