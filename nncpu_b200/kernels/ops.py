@@ -298,9 +298,12 @@ DECODE_CLUSTER_MAX_SPLITS = 8      # up to here the splits merge inside a thread
 
 def attention_decode_splits(n_tokens: int, n_kv: int, longest: int, sm_count: int) -> int:
     """As many splits as keep every block of the grid running at once (never a second wave), each with at
-    least ``DECODE_MIN_KEYS_PER_SPLIT`` keys of the longest sequence."""
+    least ``DECODE_MIN_KEYS_PER_SPLIT`` keys of the longest sequence.  Up to twice what a cluster merges is cut
+    back to what it merges: one launch instead of two costs less than the finer cut gains (one sequence of 3 072
+    keys: 8 splits in a cluster 9.1 us, 12 through scratch and a merge kernel 9.3 us before the kernel boundary)."""
     pairs = max(1, n_tokens * n_kv)
-    return max(1, min(DECODE_BLOCKS_PER_SM * sm_count // pairs, longest // DECODE_MIN_KEYS_PER_SPLIT))
+    n = max(1, min(DECODE_BLOCKS_PER_SM * sm_count // pairs, longest // DECODE_MIN_KEYS_PER_SPLIT))
+    return DECODE_CLUSTER_MAX_SPLITS if DECODE_CLUSTER_MAX_SPLITS < n <= 2 * DECODE_CLUSTER_MAX_SPLITS else n
 
 
 def attention_decode_scratch_floats(n_tok: int, n_heads: int, n_kv: int, head_dim: int, n_splits: int) -> int:
