@@ -365,6 +365,8 @@ def main() -> int:
                     help="instead of the contract's line: one of the description's larger workloads, end to end")
     ap.add_argument("--fp32-check", action="store_true",
                     help="instead of timing: logits of a short prompt in bfloat16 against the true 32-bit path")
+    ap.add_argument("--no-launch-overlap", action="store_true",
+                    help="for comparison: every kernel of a decode step waits for the end of the one before it")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -382,6 +384,8 @@ def main() -> int:
     from nncpu_b200 import Model
     from nncpu_b200.kernels import ops
 
+    if args.no_launch_overlap:
+        ops.launch_overlap(False)
     d = dict(QWEN3_8B, **SIZES[args.model])
     full_layers = d["num_hidden_layers"]
     if args.layers:

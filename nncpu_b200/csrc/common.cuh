@@ -70,6 +70,26 @@ inline bool first_use_on_this_device(bool (&done)[64]) {
     return true;
 }
 
+// Programmatic dependent launch: a kernel launched with `overlap_attribute` may start while the kernel before it in
+// the stream still runs, once every block of that kernel has called let_next_kernel_start() (or has ended).  It
+// may do only what does not depend on earlier kernels (fetch weights) until wait_for_previous_kernels() returns:
+// from then on everything that earlier kernels wrote is visible and nothing of them still runs.  Every kernel that is
+// launched with the attribute calls both; without the attribute both do nothing.  A library that uses this defines
+// NN_LAUNCH_OVERLAP before it includes this file and exports nncpu_launch_overlap_<library>(on) (default: on).
+__device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_previous_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#ifdef NN_LAUNCH_OVERLAP
+static bool g_launch_overlap = true;
+extern "C" void NN_CAT(nncpu_launch_overlap_, NN_LIB)(int on) { g_launch_overlap = on != 0; }
+// Fills `attr` and returns how many attributes to pass on (0 when the overlap is switched off).
+inline unsigned overlap_attribute(cudaLaunchAttribute* attr) {
+    attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr->val.programmaticStreamSerializationAllowed = 1;
+    return g_launch_overlap ? 1u : 0u;
+}
+#endif
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

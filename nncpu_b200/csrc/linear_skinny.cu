@@ -30,10 +30,19 @@
 //     accumulators when it starts (72 bytes a row), turns them into the rows' scales after its weight stream, and
 //     multiplies its own result by them, which a product commutes with.
 // A producer also clears the accumulators of the norm before it, whose consumer has run by then.
+//
+// A step's products follow one another, and each would start with idle memory: launch, first addresses, the
+// first bytes' way from memory.  So the kernel is launched to overlap with the end of the kernel before it
+// (programmatic dependent launch): its blocks take the places that blocks of the earlier kernel leave, ask for
+// their first weights, which depend on nobody, and only then wait for the earlier kernel's results.  Only after
+// another product of this kind, though: a block that moves in beside blocks of a kernel with much shared memory
+// (decode attention) keeps the SM in that kernel's split of shared memory and L1 for as long as the chain of
+// overlapping products lasts, and with little L1 these products crawl (a decode layer took 135 us instead of 91).
 
 #include <math.h>
 
 #define NN_LIB linear_skinny
+#define NN_LAUNCH_OVERLAP
 #include "common.cuh"
 
 namespace {
@@ -121,6 +130,28 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
 
+    // this warp's share of K, in groups of 32
+    const int n_groups = (K + 31) / 32;
+    const int per_warp = (n_groups + kWarps - 1) / kWarps;
+    const int g_begin = warp * per_warp, g_end = min(n_groups, g_begin + per_warp);
+    // Full blocks of kUnroll groups: every load is issued before the first product, without predicates.
+    // Columns of tokens beyond M read a valid row and are never stored.
+    const int k_full = K / 32;                        // groups that lie wholly inside K
+    const int g_fast_end = min(g_end, k_full);
+
+    // The first weights are asked for before anything that an earlier kernel may still be writing is touched.
+    let_next_kernel_start();
+    uint4 a_lo[kU], a_hi[kU];
+    if (g_begin + kU <= g_fast_end) {
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int k = (g_begin + u) * 32 + c * 8;
+            a_lo[u] = ldg16_stream(w_lo + k);
+            a_hi[u] = ldg16_stream(w_hi + k);
+        }
+    }
+    wait_for_previous_kernels();
+
     // What the product is added to is fetched now, under the weight stream, not after it: thread i of the
     // epilogue owns output (token i / 16, row i % 16); with at most 16 tokens that is one element per thread.
     float before = 0.0f;
@@ -143,22 +174,20 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
     // Producer of a norm: the accumulators of the norm before it are cleared for their next use.
     if (nf.bins_clear != nullptr && blockIdx.x == 0) nf.bins_clear[threadIdx.x] = 0ull;   // 16 * kBinWords = 256 words
 
-    // this warp's share of K, in groups of 32
-    const int n_groups = (K + 31) / 32;
-    const int per_warp = (n_groups + kWarps - 1) / kWarps;
-    const int g_begin = warp * per_warp, g_end = min(n_groups, g_begin + per_warp);
-    // Full blocks of kUnroll groups: every load is issued before the first product, without predicates.
-    // Columns of tokens beyond M read a valid row and are never stored.
-    const int k_full = K / 32;                        // groups that lie wholly inside K
-    const int g_fast_end = min(g_end, k_full);
     int g0 = g_begin;
     for (; g0 + kU <= g_fast_end; g0 += kU) {
-        uint4 a_lo[kU], a_hi[kU], b0[kU], b1[kU];
+        uint4 b0[kU], b1[kU];
+        if (g0 != g_begin) {
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int k = (g0 + u) * 32 + c * 8;
+                a_lo[u] = ldg16_stream(w_lo + k);
+                a_hi[u] = ldg16_stream(w_hi + k);
+            }
+        }
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
             const int k = (g0 + u) * 32 + c * 8;
-            a_lo[u] = ldg16_stream(w_lo + k);
-            a_hi[u] = ldg16_stream(w_hi + k);
             b0[u] = *reinterpret_cast<const uint4*>(x0 + k);
             if (NT > 1) b1[u] = *reinterpret_cast<const uint4*>(x1 + k);
         }
@@ -246,11 +275,17 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
 
 template <int NT, int kEpi>
 int launch(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M, int N, int K, int lda,
-           int ldc, int accumulate, const NormFusion& nf, cudaStream_t stream) {
-    const int blocks = (N + kRows - 1) / kRows;
-    skinny_kernel<NT, kEpi><<<blocks, kWarps * 32, 0, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias,
-                                                                bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf);
-    NN_LAUNCH_OK("linear_skinny");
+           int ldc, int accumulate, const NormFusion& nf, bool overlap, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + kRows - 1) / kRows);
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.numAttrs = overlap ? overlap_attribute(attr) : 0;
+    cfg.attrs = attr;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_kernel<NT, kEpi>, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
+                                             bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf);
+    NN_CHECK(e == cudaSuccess, "linear (few tokens): launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
 
@@ -272,10 +307,12 @@ extern "C" int nncpu_linear_skinny_norm_words() { return 16 * kBinWords; }
 //     bins_out, which must be zero, the sums of squares of C's rows; bins_clear (may be null) is set to zero;
 //   consumer: X holds such C * gamma rows of width K and bins_in their accumulators: the result is multiplied by
 //     1 / sqrt(sum / K + eps) per row before bias and activation.
+// after_skinny: the kernel before this one in the stream is a product of this function too; then this one may start
+// while that one ends (switched off for the whole library by nncpu_launch_overlap_linear_skinny(0)).
 extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt,
                                    int M, int N, int K, int lda, int ldc, int accumulate, int epilogue, void* xg_out,
                                    const void* gamma, int gamma_dt, void* bins_out, void* bins_clear,
-                                   const void* bins_in, float eps, void* stream_) {
+                                   const void* bins_in, float eps, int after_skinny, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(nncpu_linear_skinny_supported(M, N, K, lda),
              "linear (few tokens): M %d, N %d, K %d, lda %d: at most 16 tokens, K and lda multiples of 8", M, N, K, lda);
@@ -304,9 +341,9 @@ extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bia
     if (epilogue == kSwiglu) {
         NN_CHECK(N % 16 == 0 && bias == nullptr && !accumulate,
                  "linear (few tokens): the gated epilogue needs N %% 16 == 0, no bias and no accumulation (N %d)", N);
-        return M <= 8 ? launch<1, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream)
-                      : launch<2, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream);
+        return M <= 8 ? launch<1, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, after_skinny != 0, stream)
+                      : launch<2, kSwiglu>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, after_skinny != 0, stream);
     }
-    return M <= 8 ? launch<1, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream)
-                  : launch<2, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, stream);
+    return M <= 8 ? launch<1, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, after_skinny != 0, stream)
+                  : launch<2, kPlain>(X, W, bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf, after_skinny != 0, stream);
 }

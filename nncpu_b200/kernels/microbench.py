@@ -161,6 +161,8 @@ def rmsnorm(args) -> None:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--once", action="store_true", help="three plain launches, no timing (for a profiler)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="every kernel waits for the end of the one before it (no programmatic dependent launch)")
     sub = ap.add_subparsers(dest="kernel", required=True)
     p = sub.add_parser("linear")
     p.add_argument("m", type=int); p.add_argument("n", type=int); p.add_argument("k", type=int)
@@ -185,6 +187,8 @@ def main(argv=None) -> int:
     p.add_argument("rows", type=int); p.add_argument("dim", type=int)
     p.set_defaults(fn=rmsnorm)
     args = ap.parse_args(argv)
+    if args.no_overlap:
+        ops.launch_overlap(False)
     args.fn(args)
     return 0
 

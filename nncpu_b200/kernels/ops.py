@@ -81,15 +81,27 @@ def add_launches(n: int) -> None:
     _launches += n
 
 
+_last_fn = ""      # the entry point that launched last (a hint for launches that can overlap with their like)
+
+
 def _call(libname: str, fn: str, *args) -> None:
-    global _launches
+    global _launches, _last_fn
     lib = library.load(libname)
     if _dry:
         return
     f = getattr(lib, fn)
+    _last_fn = ""
     if f(*args) != 0:
         raise ExtensionError(lib.last_error().decode())
     _launches += 1
+    _last_fn = fn
+
+
+def launch_overlap(on: bool) -> None:
+    """Whether a few-token product that follows another one is launched so that it may start (and fetch its
+    first weights) while that one ends.  On by default; off, every kernel waits for the one before it to be
+    over, and the results are the same bits."""
+    library.load("linear_skinny").nncpu_launch_overlap_linear_skinny(ctypes.c_int(1 if on else 0))
 
 
 def _i(v) -> ctypes.c_int:
@@ -233,10 +245,12 @@ def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "pl
         assert norm_out is None, "a product is a norm's producer or its consumer"
         bins_in, eps = norm_in
         assert bins_in.dtype == torch.int64 and bins_in.numel() == NORM_WORDS
+    # a product that follows another one may start while that one ends (see launch_overlap)
+    after_skinny = _last_fn == "nncpu_linear_skinny"
     _call("linear_skinny", "nncpu_linear_skinny", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
           _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
           _ptr(xg), _ptr(gamma), _i(_code(gamma)), _ptr(bins_out), _ptr(bins_clear), _ptr(bins_in), _f(eps),
-          _stream())
+          _i(after_skinny), _stream())
 
 
 NORM_WORDS = 256    # 64-bit words of the accumulators of one norm: 16 rows of 16 (8 bins, a flag, spare)

@@ -284,6 +284,56 @@ def test_rope_table(ops):
         assert (out[..., 1].cpu() - torch.sin(ang).float()).abs().max() < 2e-6
 
 
+@pytest.mark.parametrize("m", [3, 13])
+def test_products_that_start_under_their_predecessor_give_the_same_bits(ops, m):
+    """A chain of few-token products, each reading what the one before wrote (with a norm carried between two of
+    them): launched so that each may start while its predecessor ends, and launched one after the other, in a
+    plain stream and in a captured graph, it leaves the same bits.  The chain is long and its matrices differ in
+    size, so that blocks of three kernels are in flight at once."""
+    g = torch.Generator().manual_seed(m)
+    hidden, inter = 1024, 2816
+    w_up = [(torch.randn(2 * inter, hidden, generator=g) * 0.05).bfloat16().to(DEV) for _ in range(4)]
+    w_down = [(torch.randn(hidden, inter, generator=g) * 0.05).bfloat16().to(DEV) for _ in range(4)]
+    gamma = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16().to(DEV)
+    x0 = torch.randn(m, hidden, generator=g).to(DEV)
+
+    def chain():
+        residual = x0.clone()
+        xg = (x0 * gamma.float()).bfloat16()
+        bins = torch.zeros(2, ops.NORM_WORDS, dtype=torch.int64, device=DEV)
+        ss = (x0.double() ** 2).sum(-1)
+        act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+        first = torch.empty(m, 2 * inter, dtype=torch.bfloat16, device=DEV)
+        ops.linear_skinny(xg, w_up[0], None, first)                       # nothing of this kind before it
+        for layer in range(4):
+            if layer == 0:
+                ops.linear_skinny(xg, w_up[0], None, act, epilogue="swiglu")
+            else:
+                ops.linear_skinny(xg, w_up[layer], None, act, epilogue="swiglu", norm_in=(bins[layer % 2], 1e-6))
+            ops.linear_skinny(act, w_down[layer], None, residual, accumulate=True,
+                              norm_out=(xg, gamma, bins[(layer + 1) % 2], bins[layer % 2]))
+        return residual, xg.clone(), bins.clone()
+
+    try:
+        ops.launch_overlap(False)
+        want = chain()
+        ops.launch_overlap(True)
+        for _ in range(3):
+            got = chain()
+            assert all(torch.equal(a, b) for a, b in zip(got, want))
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = chain()
+        for _ in range(3):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert all(torch.equal(a, b) for a, b in zip(captured, want))
+    finally:
+        ops.launch_overlap(True)
+    assert bool(torch.isfinite(want[0]).all())
+
+
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (5, 1, 48, 48), (3, 3, 80, 32), (8, 2, 128, 128)])
 @pytest.mark.parametrize("dt", DT)
 def test_qk_norm_rope_append(ops, nh, nkv, hd, rot, dt):
