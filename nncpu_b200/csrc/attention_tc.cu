@@ -35,6 +35,7 @@
 #include <tuple>
 
 #define NN_LIB attention_tc
+#define NN_LAUNCH_OVERLAP
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -136,6 +137,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     uint32_t* tmem_slot = (uint32_t*)(o_done + kStreams);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Launched to start while the kernel before it ends (its set-up needs nothing of that kernel; the step's
+    // metadata was copied before the step's first kernel).  It waits before its first copy of q or of a page.
+    let_next_kernel_start();
 
     // the block's 128 query rows: tiles are numbered within each sequence from its end (long spans first)
     int tile = blockIdx.y;
@@ -192,6 +196,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    wait_for_previous_kernels();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -517,8 +522,16 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     // tiles: an upper bound, since the sequence boundaries live on the device; spare blocks leave at once
     const int group = p.n_heads / p.n_kv;
     const dim3 grid(p.n_kv * ((group + kStreams - 1) / kStreams), (n_tok + kQRows - 1) / kQRows + p.n_seqs);
-    prefill_tc_kernel<HD, kStreams><<<grid, 64 + 128 * kStreams, smem, stream>>>(mq, mk, mv, p);
-    NN_LAUNCH_OK("attention prefill (tensor cores)");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(64 + 128 * kStreams);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_attribute(attr);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, prefill_tc_kernel<HD, kStreams>, mq, mk, mv, p);
+    NN_CHECK(e == cudaSuccess, "attention prefill (tensor cores): launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
 

@@ -37,6 +37,7 @@
 #include <tuple>
 
 #define NN_LIB gemm_sm100
+#define NN_LAUNCH_OVERLAP
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -201,6 +202,10 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
     }
 }
 
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
+}
+
 template <int BN, int kStages, int kEpi>
 __global__ void __launch_bounds__(kThreads)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -222,8 +227,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = p.tiles_a * p.tiles_b;
     const unsigned long long limit = p.wait_ns ? p.wait_ns : kWaitLimitNs;
+    // This block's k-blocks in the order it works through them: run r is k-block r % kb_total of its tile r / kb_total.
+    const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_runs = my_tiles * p.kb_total;
+    const int n_first = min(kStages, my_runs);   // copies that need no free stage
 
+    let_next_kernel_start();
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
@@ -234,6 +246,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // The first weights are asked for before anything that the kernel before this one may still be writing is
+        // touched (with swapped operands the weights are A).
+        for (int r = 0; r < n_first; ++r) {
+            const int w = blockIdx.x + (r / p.kb_total) * gridDim.x, kb = r % p.kb_total;
+            mbar_expect_tx(&full[r], kBytesA + kBytesB + p.tx_extra);
+            if (p.swap) tma_load_2d(smem_a + r * kBytesA, &map_a, &full[r], kb * kBlockK, (w % p.tiles_a) * kBlockM);
+            else tma_load_2d(smem_b + r * kBytesB, &map_b, &full[r], kb * kBlockK, (w / p.tiles_a) * BN);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -245,26 +265,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    wait_for_previous_kernels();
 
     // Work item w: output tile (w % tiles_a, w / tiles_a), all of K.
     if (warp == 0) {
         if (lane == 0) {
-            int kb_run = 0, issued = 0;
+            int issued = n_first;
             bool ok = true;
-            for (int w = blockIdx.x; w < n_tiles && ok; w += gridDim.x) {
+            for (int r = 0; r < n_first; ++r) {   // the activations of the first copies
+                const int w = blockIdx.x + (r / p.kb_total) * gridDim.x, kb = r % p.kb_total;
+                if (p.swap) tma_load_2d(smem_b + r * kBytesB, &map_b, &full[r], kb * kBlockK, (w / p.tiles_a) * BN);
+                else tma_load_2d(smem_a + r * kBytesA, &map_a, &full[r], kb * kBlockK, (w % p.tiles_a) * kBlockM);
+            }
+            for (int r = n_first; r < my_runs; ++r) {
+                const int w = blockIdx.x + (r / p.kb_total) * gridDim.x, kb = r % p.kb_total;
                 const int m0 = (w % p.tiles_a) * kBlockM, n0 = (w / p.tiles_a) * BN;
-                for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
-                    const int s = kb_run % kStages;
-                    if (!mbar_wait(&empty[s], ((kb_run / kStages) & 1) ^ 1, limit)) {
-                        atomicExch(p.status, kTimeoutEmpty);
-                        ok = false;
-                        break;
-                    }
-                    mbar_expect_tx(&full[s], kBytesA + kBytesB + p.tx_extra);
-                    tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
-                    tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
-                    issued = kb_run + 1;
+                const int s = r % kStages;
+                if (!mbar_wait(&empty[s], ((r / kStages) & 1) ^ 1, limit)) {
+                    atomicExch(p.status, kTimeoutEmpty);
+                    ok = false;
+                    break;
                 }
+                mbar_expect_tx(&full[s], kBytesA + kBytesB + p.tx_extra);
+                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
+                issued = r + 1;
             }
             if (!ok) {
                 // let the copies already in flight land before the block gives up its shared memory
@@ -391,6 +416,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int n_tiles = p.tiles_a * p.tiles_b;
     const long units = (long)n_tiles * p.kb_total;
     const int blocks = (int)gridDim.x;
+    let_next_kernel_start();   // the set-up below runs while the kernel before this one ends
     const long u_begin = streamk_start((int)blockIdx.x, units, blocks);
     const long u_end = streamk_start((int)blockIdx.x + 1, units, blocks);
     // this block's next segment from unit u on
@@ -425,6 +451,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    wait_for_previous_kernels();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -610,10 +637,6 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
     return v;
 }
 
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
-}
-
 // Copies `bytes` of this block's shared memory into the shared memory of block `rank` of the cluster; the bytes
 // are counted by the mbarrier at `bar_local_addr` in that block.  The copy runs on its own: nothing waits here.
 __device__ __forceinline__ void bulk_copy_to_rank(uint32_t dst_local_addr, uint32_t src_addr, uint32_t bytes,
@@ -674,6 +697,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int cols = c_end - c_begin;
     const int n_first = min(kStages, kb1 - kb0);   // copies that need no free stage: issued before anything else
 
+    let_next_kernel_start();
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
@@ -687,11 +711,17 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // S senders bring this block's columns, 128 rows of floats each
         mbar_expect_tx(arrived, (uint32_t)(S * cols * kBlockM * 4));
-        // the first round of copies starts now, under the set-up of tensor memory
+        // the first round of copies starts now, under the set-up of tensor memory and, for the weights, under the end
+        // of the kernel before this one (with swapped operands the weights are A)
         for (int i = 0; i < n_first; ++i) {
             mbar_expect_tx(&full[i], kBytesA + kBytesB);
-            tma_load_2d(smem_a + i * kBytesA, &map_a, &full[i], (kb0 + i) * kBlockK, m0);
-            tma_load_2d(smem_b + i * kBytesB, &map_b, &full[i], (kb0 + i) * kBlockK, n0);
+            if (p.swap) tma_load_2d(smem_a + i * kBytesA, &map_a, &full[i], (kb0 + i) * kBlockK, m0);
+            else tma_load_2d(smem_b + i * kBytesB, &map_b, &full[i], (kb0 + i) * kBlockK, n0);
+        }
+        wait_for_previous_kernels();
+        for (int i = 0; i < n_first; ++i) {
+            if (p.swap) tma_load_2d(smem_b + i * kBytesB, &map_b, &full[i], (kb0 + i) * kBlockK, n0);
+            else tma_load_2d(smem_a + i * kBytesA, &map_a, &full[i], (kb0 + i) * kBlockK, m0);
         }
     }
     if (warp == 1) {
@@ -704,6 +734,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    wait_for_previous_kernels();   // thread 0 has waited already; the others read what the product is added to
     // Every block of the cluster has started (its shared memory and its barrier exist) before anyone copies into
     // it.  The wait for this arrival comes just before the copies.  The barriers' initialisation was published by
     // its own fence above, so the arrival orders nothing else and does not flush this thread's memory operations.
@@ -1001,6 +1032,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
     __shared__ float s_gamma[kEpi == kQkv ? 2 : 1][128];   // the q and k norm weights of the fused q/k/v epilogue
+    let_next_kernel_start();   // the set-up below runs while the kernel before this one ends
     if constexpr (kEpi == kQkv) {
         for (int i = threadIdx.x; i < 256; i += kThreads) {
             const void* gamma = i < 128 ? p.qkv.q_gamma : p.qkv.k_gamma;
@@ -1036,6 +1068,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     cluster_barrier();   // both blocks' barriers exist before anyone signals across the pair
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    wait_for_previous_kernels();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -1206,8 +1239,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int bloc
     }
     const int n_items = p.tiles_a * p.tiles_b;
     const int grid = n_items < blocks_per_sm * sm_count() ? n_items : blocks_per_sm * sm_count();
-    gemm_bf16_kernel<BN, kStages, kEpi><<<grid, kThreads, smem, stream>>>(ma, mb, p);
-    NN_LAUNCH_OK("gemm_bf16");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_attribute(attr);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, kStages, kEpi>, ma, mb, p);
+    NN_CHECK(e == cudaSuccess, "gemm: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
 
@@ -1225,8 +1266,16 @@ int launch_streamk(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, 
     long grid = sm_count();
     if (grid > units / 4) grid = units / 4;
     if (grid < 1) grid = 1;
-    gemm_streamk_kernel<BN, kStages, kEpi><<<(unsigned)grid, kThreads, smem, stream>>>(ma, mb, p);
-    NN_LAUNCH_OK("gemm_streamk");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_attribute(attr);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_streamk_kernel<BN, kStages, kEpi>, ma, mb, p);
+    NN_CHECK(e == cudaSuccess, "gemm (stream-K): launch failed: %s", cudaGetErrorString(e));
     if (units % grid != 0 || (units / grid) % p.kb_total != 0) {
         // some tile is shared between blocks
         gemm_streamk_fixup_kernel<BN, kEpi><<<dim3((unsigned)(p.tiles_a * p.tiles_b), BN / 16), kBlockM, 0, stream>>>(
@@ -1261,13 +1310,13 @@ int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, 
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 1 + overlap_attribute(attr + 1);
     const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_cluster_kernel<BN, kStages, kEpi>, ma, mb, p);
     NN_CHECK(e == cudaSuccess, "gemm (cluster of %d): launch failed: %s", p.splits, cudaGetErrorString(e));
     return 0;
@@ -1291,13 +1340,13 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cud
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 1 + overlap_attribute(attr + 1);
     const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<kStages, kEpi>, ma, mb, p);
     NN_CHECK(e == cudaSuccess, "gemm (pairs of SMs): launch failed: %s", cudaGetErrorString(e));
     return 0;

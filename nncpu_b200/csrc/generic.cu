@@ -15,6 +15,7 @@
 #include <math.h>
 
 #define NN_LIB generic
+#define NN_LAUNCH_OVERLAP
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
@@ -74,6 +75,9 @@ __global__ void __launch_bounds__(256)
 rmsnorm_f32_kernel(const float* __restrict__ x, const void* __restrict__ gamma, int g_dt, void* __restrict__ y,
                    int y_dt, const int* __restrict__ rows, int dim, float eps) {
     __shared__ float scratch[33];
+    // launched to start while the kernel before it ends: the product that follows may set itself up meanwhile
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     const int r_out = blockIdx.x;
     const int r_in = rows ? rows[r_out] : r_out;
     const int n4 = dim >> 2;
@@ -120,11 +124,16 @@ extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_d
     if (x_dt == DT_F32 && dim % 4 == 0 && dim >= 1024 && dim <= 256 * 4 * 8 && (uintptr_t)x % 16 == 0 &&
         (uintptr_t)y % 16 == 0) {
         const float* xf = (const float*)x;
-        cudaStream_t st = (cudaStream_t)stream;
-        if (dim <= 256 * 4 * 2) rmsnorm_f32_kernel<2><<<n_rows, 256, 0, st>>>(xf, gamma, g_dt, y, y_dt, rows, dim, eps);
-        else if (dim <= 256 * 4 * 4) rmsnorm_f32_kernel<4><<<n_rows, 256, 0, st>>>(xf, gamma, g_dt, y, y_dt, rows, dim, eps);
-        else rmsnorm_f32_kernel<8><<<n_rows, 256, 0, st>>>(xf, gamma, g_dt, y, y_dt, rows, dim, eps);
-        NN_LAUNCH_OK("rmsnorm");
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n_rows);
+        cfg.blockDim = dim3(256);
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[1];
+        cfg.attrs = attr;
+        cfg.numAttrs = overlap_attribute(attr);
+        const auto kernel = dim <= 256 * 4 * 2 ? rmsnorm_f32_kernel<2> : dim <= 256 * 4 * 4 ? rmsnorm_f32_kernel<4> : rmsnorm_f32_kernel<8>;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, xf, gamma, g_dt, y, y_dt, rows, dim, eps);
+        NN_CHECK(e == cudaSuccess, "rmsnorm: launch failed: %s", cudaGetErrorString(e));
         return 0;
     }
     int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));

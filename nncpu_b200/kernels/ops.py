@@ -98,10 +98,13 @@ def _call(libname: str, fn: str, *args) -> None:
 
 
 def launch_overlap(on: bool) -> None:
-    """Whether a few-token product that follows another one is launched so that it may start (and fetch its
-    first weights) while that one ends.  On by default; off, every kernel waits for the one before it to be
-    over, and the results are the same bits."""
-    library.load("linear_skinny").nncpu_launch_overlap_linear_skinny(ctypes.c_int(1 if on else 0))
+    """Whether kernels that can do so are launched to start while the kernel before them ends: a few-token
+    product after another one (it asks for its first weights before it waits for that one's results), the
+    tensor-core products (their set-up; up to 64 tokens also their first weight tiles), prefill attention (its
+    set-up) and the norms between them.
+    On by default; off, every kernel waits for the one before it to be over, and the results are the same bits."""
+    for name in ("linear_skinny", "gemm_sm100", "generic", "attention_tc"):
+        getattr(library.load(name), f"nncpu_launch_overlap_{name}")(ctypes.c_int(1 if on else 0))
 
 
 def _i(v) -> ctypes.c_int:
