@@ -90,6 +90,49 @@ inline unsigned overlap_attribute(cudaLaunchAttribute* attr) {
 }
 #endif
 
+// ---------------------------------------------------------------------------
+// Norms that ride on the products around them (linear_skinny.cu explains the scheme; the tensor-core products of
+// whole prompts do the same).  A row's sum of squares is kept in an exact accumulator of kBinWords 64-bit words:
+// eight integers, one per 32 binary orders of magnitude, a word that counts values that are not finite, and spare
+// words that keep a row at 128 bytes.
+// ---------------------------------------------------------------------------
+// What a product does for the norms around it (all null or zero: nothing).
+constexpr int kBinWords = 16;    // 64-bit words a row: 8 accumulator bins, a word that says "not finite", 7 spare
+struct NormFusion {
+    // producer: besides C, leave the input of the norm that reads C next
+    __nv_bfloat16* xg_out;        // [M, N]: C * gamma, not yet multiplied by the row's scale
+    const void* gamma;            // [N] weights of that norm
+    int gamma_dt;
+    unsigned long long* bins_out; // [rows, kBinWords], zero before the launch: the rows' sums of squares of C
+    unsigned long long* bins_clear;  // [rows, kBinWords] of an earlier norm whose consumer has run: set to zero (or null)
+    // consumer: X is such an input; the rows' scales are applied to this product's result
+    const unsigned long long* bins_in;   // [rows, kBinWords]
+    float eps;
+};
+
+// A non-negative float into its row's accumulator: value = mantissa * 2^(E - 150) with E = 32 * bin + shift.
+__device__ __forceinline__ void bins_add(unsigned long long* bins, float v) {
+    const uint32_t bits = __float_as_uint(v);
+    const uint32_t e = (bits >> 23) & 0xFF;
+    if (e == 0xFF) {                       // infinity or NaN: the row has no finite norm
+        atomicAdd(bins + 8, 1ull);
+        return;
+    }
+    const uint32_t ee = e ? e : 1;         // subnormals have the exponent of the smallest normal and no hidden bit
+    const unsigned long long mant = (bits & 0x7FFFFF) | (e ? 0x800000u : 0u);
+    if (mant) atomicAdd(bins + ee / 32, mant << (ee % 32));
+}
+
+// The sum that an accumulator holds, rounded once to float.
+__device__ __forceinline__ float bins_total(const unsigned long long* bins) {
+    if (bins[8] != 0) return __int_as_float(0x7FC00000);   // NaN
+    double s = 0.0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b)   // 2^(32 b - 150), spelled as the bits of the double
+        s += (double)bins[b] * __longlong_as_double((long long)(1023 + 32 * b - 150) << 52);
+    return (float)s;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

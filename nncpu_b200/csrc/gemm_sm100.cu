@@ -86,6 +86,7 @@ struct GemmParams {
     unsigned long long wait_ns;  // limit of every mbarrier wait of gemm_bf16_kernel; 0: the default (2 s)
     int tx_extra;      // bytes added to what a stage's barrier expects (the wait probe only: they never arrive)
     QkvParams qkv;     // epilogue kQkv only
+    NormFusion nf;     // pairs of SMs only: the norms that ride on this product (common.cuh)
 };
 
 // Stores up to 16 accumulator values of one thread: A row `a_row`, B rows b0 .. b0 + ncols - 1
@@ -928,9 +929,10 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 // heads get the per-head RMS norm (32-bit sum over the head) and the rotation of the pairs (i, i + 64); value
 // heads are only rounded.  Queries go to q_out, keys and values to the token's place in the cache pages.
 // The same arithmetic as the separate kernel (x * scale * gamma, then the rotation), so prefill and decode
-// agree to rounding (crates/nncpu/src/model/forward.rs:278-324).
+// agree to rounding (crates/nncpu/src/model/forward.rs:278-324).  `row_scale` multiplies the accumulators first: the
+// scale of the norm before the projection when that norm rides on this product, else 1 (which changes no bit).
 __device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float (*s_gamma)[128], uint32_t taddr,
-                                               int a_row, int n0) {
+                                               int a_row, int n0, float row_scale) {
     const QkvParams& e = p.qkv;
     const bool row_ok = a_row < p.rows_a;
     // where this token's keys and values go
@@ -958,7 +960,10 @@ __device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float 
                 uint32_t u[64];
                 tmem_ld64(t0 + (uint32_t)c0, u);
 #pragma unroll
-                for (int c = 0; c < 64; ++c) ss[c & 3] = fmaf(__uint_as_float(u[c]), __uint_as_float(u[c]), ss[c & 3]);
+                for (int c = 0; c < 64; ++c) {
+                    const float x = __uint_as_float(u[c]) * row_scale;
+                    ss[c & 3] = fmaf(x, x, ss[c & 3]);
+                }
             }
             scale = 1.0f / sqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) * (1.0f / 128.0f) + e.eps);
         }
@@ -980,7 +985,7 @@ __device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float 
             if (dst == nullptr) continue;
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-                float a = __uint_as_float(lo[c]), b = __uint_as_float(hi[c]);
+                float a = __uint_as_float(lo[c]) * row_scale, b = __uint_as_float(hi[c]) * row_scale;
                 if (gamma) {
                     a = (a * scale) * s_gamma[is_q ? 0 : 1][c0 + c];
                     b = (b * scale) * s_gamma[is_q ? 0 : 1][64 + c0 + c];
@@ -1147,13 +1152,89 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+            // the norm before this product rides on it: its rows' scales multiply the accumulators
+            const bool a_ok = a_row < p.rows_a;
+            float row_scale = 1.0f;
+            if (p.nf.bins_in != nullptr && a_ok)
+                row_scale = 1.0f / sqrtf(bins_total(p.nf.bins_in + (size_t)a_row * kBinWords) * (1.0f / (float)p.K) + p.nf.eps);
             if constexpr (kEpi == kQkv) {
-                store_qkv_tile(p, s_gamma, taddr, a_row, n0);
+                store_qkv_tile(p, s_gamma, taddr, a_row, n0, row_scale);
+            } else if (kEpi == kPlain && p.nf.xg_out != nullptr) {
+                // the norm after this product rides on it: besides out (float32, rows of whole 16-byte pieces: the
+                // launcher checked) it leaves out * gamma in bfloat16 and adds this tile's part of the row's sum of
+                // squares to the row's accumulator
+                float ss = 0.0f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    const int col = n0 + c0;
+                    if (col >= p.rows_b) break;        // the same for the whole warp
+                    float v[16];
+                    tmem_ld16(taddr + (uint32_t)c0, v);   // every lane takes part in the load, whatever its row
+                    if (!a_ok) continue;
+                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)a_row * p.ldc + col);
+                    float4 y[4];
+                    if (p.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) y[j] = dst[j];
+                    }
+                    float g[16];
+                    if (p.nf.gamma_dt == DT_BF16) {
+                        const uint4* gp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.nf.gamma) + col);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint4 w = gp[h];
+                            const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __bfloat1622float2(wh[j]);
+                                g[8 * h + 2 * j] = f.x;
+                                g[8 * h + 2 * j + 1] = f.y;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) g[j] = reinterpret_cast<const float*>(p.nf.gamma)[col + j];
+                    }
+                    if (p.bias) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] += ld_f(p.bias, col + j, p.bias_dt);
+                    }
+                    if (p.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            v[4 * j] += y[j].x; v[4 * j + 1] += y[j].y; v[4 * j + 2] += y[j].z; v[4 * j + 3] += y[j].w;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    __nv_bfloat16* xg = p.nf.xg_out + (size_t)a_row * p.rows_b + col;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        __nv_bfloat162 o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            o[j] = __floats2bfloat162_rn(v[8 * h + 2 * j] * g[8 * h + 2 * j], v[8 * h + 2 * j + 1] * g[8 * h + 2 * j + 1]);
+                        *reinterpret_cast<uint4*>(xg + 8 * h) = *reinterpret_cast<uint4*>(o);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) ss = fmaf(v[j], v[j], ss);
+                }
+                if (a_ok) {
+                    bins_add(p.nf.bins_out + (size_t)a_row * kBinWords, ss);
+                    if (p.nf.bins_clear != nullptr && n0 == 0) {
+                        // the accumulators of the norm before, whose consumer has run: zero for their next use
+                        uint4* z = reinterpret_cast<uint4*>(p.nf.bins_clear + (size_t)a_row * kBinWords);
+#pragma unroll
+                        for (int j = 0; j < kBinWords / 2; ++j) z[j] = make_uint4(0, 0, 0, 0);
+                    }
+                }
             } else {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     float v[16];
                     tmem_ld16(taddr + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] *= row_scale;
                     store16<kEpi>(p, a_row, n0 + c0, v);
                 }
             }
@@ -1395,7 +1476,8 @@ extern "C" int nncpu_linear_tc_qkv_supported(int M, int K, int lda, int n_heads,
 extern "C" int nncpu_linear_tc_qkv(const void* X, const void* W, int M, int K, int lda, void* q_out, void* k_pages,
                                    void* v_pages, const void* q_gamma, const void* k_gamma, int g_dt, float eps,
                                    const float* cos_sin, const int* tok_seq, const int* tok_pos, const int* block_table,
-                                   int bt_stride, int n_heads, int n_kv, int head_dim, int* status, void* stream_) {
+                                   int bt_stride, int n_heads, int n_kv, int head_dim, const void* bins_in,
+                                   float norm_eps, int* status, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(nncpu_linear_tc_qkv_supported(M, K, lda, n_heads, n_kv, head_dim),
              "gemm (q/k/v epilogue): M %d, K %d, lda %d, %d heads over %d of size %d: it takes 512 or more tokens, "
@@ -1422,6 +1504,13 @@ extern "C" int nncpu_linear_tc_qkv(const void* X, const void* W, int M, int K, i
     p.qkv.cos_sin = (const float2*)cos_sin;
     p.qkv.tok_seq = tok_seq; p.qkv.tok_pos = tok_pos; p.qkv.block_table = block_table; p.qkv.bt_stride = bt_stride;
     p.qkv.n_heads = n_heads; p.qkv.n_kv = n_kv;
+    if (bins_in != nullptr) {
+        // X holds a norm's rows times gamma; the rows' scales multiply the accumulators (see nncpu_linear_tc)
+        NN_CHECK(((uintptr_t)bins_in % 8) == 0 && norm_eps >= 0.0f, "gemm (q/k/v epilogue): a norm's accumulators (8-byte aligned), eps %g",
+                 norm_eps);
+        p.nf.bins_in = (const unsigned long long*)bins_in;
+        p.nf.eps = norm_eps;
+    }
     CUtensorMap ma, mb;
     if (int e = g_maps.get(&ma, X, M, K, lda, kBlockM)) return e;
     if (int e = g_maps.get(&mb, W, N, K, K, 128)) return e;
@@ -1463,9 +1552,19 @@ extern "C" int nncpu_linear_tc_wait_probe(const void* X, const void* W, float* o
 // evenly from 17 tokens on; kPlanNeverEven: never dealt out evenly; kPlanNoPairs: one SM per 128 x 256 tile.
 enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4 };
 
+//
+// The norms around a product of whole prompts can ride on it as they do on the few-token products (linear_skinny.cu),
+// where nncpu_linear_tc_fuses_norms(M, N) says so (the kernel for pairs of SMs).  Producer (plain epilogue, float32
+// C with 16-byte rows, N a multiple of 16): xg_out bfloat16 [M, N] receives C * gamma and bins_out [M, 16] (64-bit
+// words, zero before the call) the exact sums of squares of C's rows; bins_clear [M, 16] (or null) is set to zero.
+// Consumer: X holds such rows of width K and bins_in [M, 16] their accumulators: the result is multiplied by
+// 1 / sqrt(sum / K + eps) per row before bias and activation.
+extern "C" int nncpu_linear_tc_fuses_norms(int M, int N) { return M >= 512 && N >= 512; }
+
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
-                               int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, float* scratch,
-                               int* status, void* stream_) {
+                               int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, void* xg_out,
+                               const void* gamma, int gamma_dt, void* bins_out, void* bins_clear, const void* bins_in,
+                               float eps, float* scratch, int* status, void* stream_) {
     const int streamk_mode = (plan & kPlanNeverEven) ? 0 : (plan & kPlanEvenFrom17) ? 2 : 1;
     const int pair_mode = (plan & kPlanNoPairs) ? 0 : 1;
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -1485,6 +1584,28 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
     p.scratch = scratch; p.status = status;
     const int esize = c_dt == DT_F32 ? 4 : 2;
     p.vec = ((uintptr_t)C % 16 == 0) && ((size_t)ldc * esize % 16 == 0);
+    if (xg_out != nullptr || bins_in != nullptr) {
+        NN_CHECK(nncpu_linear_tc_fuses_norms(M, N) && !(plan & kPlanNoPairs),
+                 "gemm: norms ride only on products of 512 or more tokens and output features (M %d, N %d)", M, N);
+        NN_CHECK(xg_out == nullptr || bins_in == nullptr, "gemm: a product is a norm's producer or its consumer");
+    }
+    if (xg_out != nullptr) {
+        NN_CHECK(epilogue == kPlain && c_dt == DT_F32 && p.vec && N % 16 == 0 && gamma != nullptr && bins_out != nullptr &&
+                     ((uintptr_t)xg_out % 16) == 0 && ((uintptr_t)gamma % 16) == 0 && ((uintptr_t)bins_out % 16) == 0 &&
+                     ((uintptr_t)bins_clear % 16) == 0,
+                 "gemm: leaving a norm's input needs the plain epilogue, float32 output in 16-byte rows, N %% 16 == 0, "
+                 "the norm's weights and its accumulators (all 16-byte aligned)");
+        p.nf.xg_out = (__nv_bfloat16*)xg_out;
+        p.nf.gamma = gamma;
+        p.nf.gamma_dt = gamma_dt;
+        p.nf.bins_out = (unsigned long long*)bins_out;
+        p.nf.bins_clear = (unsigned long long*)bins_clear;
+    }
+    if (bins_in != nullptr) {
+        NN_CHECK(((uintptr_t)bins_in % 8) == 0 && eps >= 0.0f, "gemm: a norm's accumulators (8-byte aligned), eps %g", eps);
+        p.nf.bins_in = (const unsigned long long*)bins_in;
+        p.nf.eps = eps;
+    }
     CUtensorMap ma, mb;
     int bn;
     if (M <= 256) {

@@ -171,14 +171,17 @@ class Model:
         with rt.phase("embed"):
             ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale)
         ctx.next_norm = ctx.after_block = None
-        if ctx.n_tokens <= ops.SKINNY_MAX_TOKENS and rt.dtype == torch.bfloat16:
-            rt.begin_norm_fusion()      # a step of few tokens: norms may ride on the products around them
+        fusing = rt.dtype == torch.bfloat16 and rt.fuses_norms(ctx.n_tokens, spec.hidden_size)
+        if fusing:
+            rt.begin_norm_fusion(ctx.n_tokens)      # norms may ride on the products around them
         for i, (e, (first, count)) in enumerate(zip(self.schedule, self._users)):
             if i + 1 < len(self.schedule):
                 # the block that follows may ask this one to leave its first norm's input (a few tokens only)
                 ctx.after_block = self.blocks[self.schedule[i + 1].layer].entry_norm_request(ctx, residual)
             self.blocks[e.layer].forward(ctx, residual, [ctx.entry_cache(cache, u) for u in range(first, first + count)])
         ctx.next_norm = ctx.after_block = None
+        if fusing:
+            rt.end_norm_fusion()
         if ctx.n_wanted == 0:
             return None
         x = self.final_norm.forward(ctx, residual, rows=ctx.logit_rows)

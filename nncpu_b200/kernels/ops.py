@@ -166,20 +166,41 @@ PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4}
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 
+def linear_tc_fuses_norms(m: int, n: int) -> bool:
+    """Whether the tensor-core product of ``m`` tokens with ``n`` output features can carry the norms around it
+    (``linear_tc``'s ``norm_out`` and ``norm_in``): the products of whole prompts."""
+    return bool(library.load("gemm_sm100").nncpu_linear_tc_fuses_norms(m, n))
+
+
 def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = False, epilogue: str = "plain",
-              plan: str = "auto") -> None:
+              plan: str = "auto", norm_out=None, norm_in=None) -> None:
     """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16.  With
     ``epilogue="swiglu"`` the rows of w hold gate and up rows interleaved in
     blocks of 8 and out [m, n/2] receives silu(gate) * up.  ``plan``: "auto",
     or for measurements and tests "even_from_17" (17 to 64 tokens deal their
-    k-blocks out evenly like 65 to 256), "never_even", "no_pairs"."""
+    k-blocks out evenly like 65 to 256), "never_even", "no_pairs".
+
+    Where ``linear_tc_fuses_norms(m, n)``, the product can carry the RMS norms around it as ``linear_skinny``
+    does: ``norm_out = (xg, gamma, bins, bins_clear)`` and ``norm_in = (bins, eps)`` with accumulators of
+    ``NORM_ROW_WORDS`` 64-bit words per row (int64 [m, NORM_ROW_WORDS])."""
     m, k = x.shape
     n = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert w.shape[1] == k and out.shape == (m, n // 2 if epilogue == "swiglu" else n)
+    xg = gamma = bins_out = bins_clear = bins_in = None
+    eps = 0.0
+    if norm_out is not None:
+        xg, gamma, bins_out, bins_clear = norm_out
+        assert xg.dtype == torch.bfloat16 and xg.shape == (m, n) and xg.is_contiguous() and gamma.numel() == n
+        assert bins_out.dtype == torch.int64 and bins_out.shape == (m, NORM_ROW_WORDS) and bins_out.is_contiguous()
+        assert bins_clear is None or (bins_clear.dtype == torch.int64 and bins_clear.shape == (m, NORM_ROW_WORDS))
+    if norm_in is not None:
+        bins_in, eps = norm_in
+        assert bins_in.dtype == torch.int64 and bins_in.shape == (m, NORM_ROW_WORDS) and bins_in.is_contiguous()
     _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
-          _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
-          _i(PLANS[plan]), _ptr(workspace.scratch), _ptr(workspace.status), _stream())
+          _i(_code(out)), _i(m), _i(n), _i(k), _i(x.stride(0)), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
+          _i(PLANS[plan]), _ptr(xg), _ptr(gamma), _i(_code(gamma)), _ptr(bins_out), _ptr(bins_clear), _ptr(bins_in),
+          _f(eps), _ptr(workspace.scratch), _ptr(workspace.status), _stream())
 
 
 def linear_tc_wait_probe(x, w, out, workspace: GemmWorkspace, limit_ms: int = 5) -> None:
@@ -200,12 +221,15 @@ def linear_tc_qkv_supported(x, n_heads: int, n_kv: int, head_dim: int) -> bool:
 
 
 def linear_tc_qkv(x, w_qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, block_table, k_pages, v_pages, q_out,
-                  workspace: GemmWorkspace, n_heads: int, n_kv: int, head_dim: int) -> None:
+                  workspace: GemmWorkspace, n_heads: int, n_kv: int, head_dim: int, norm_in=None) -> None:
     """x . w_qkv^T with the per-head norm, the rotation and the stores fused into the product's epilogue:
     queries to ``q_out``, keys and values to the tokens' rows of the cache pages.  bfloat16 throughout,
     32-bit accumulators, norm and rotation.  ``cos_sin`` is the rotation table laid out by pair:
-    float32 [head_dim / 2, tokens, 2]."""
+    float32 [head_dim / 2, tokens, 2].  ``norm_in = (bins, eps)``: ``x`` holds the rows of the norm before the
+    projection times gamma, and the rows' scales are applied to the accumulators (as in ``linear_tc``)."""
     m, k = x.shape
+    bins_in, norm_eps = norm_in if norm_in is not None else (None, 0.0)
+    assert bins_in is None or (bins_in.dtype == torch.int64 and bins_in.shape == (m, NORM_ROW_WORDS))
     assert w_qkv.shape == ((n_heads + 2 * n_kv) * head_dim, k) and q_out.shape == (m, n_heads * head_dim)
     assert x.dtype == w_qkv.dtype == q_out.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16
     assert q_out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -216,7 +240,7 @@ def linear_tc_qkv(x, w_qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, bl
     _call("gemm_sm100", "nncpu_linear_tc_qkv", _ptr(x), _ptr(w_qkv), _i(m), _i(k), _i(x.stride(0)), _ptr(q_out),
           _ptr(k_pages), _ptr(v_pages), _ptr(q_gamma), _ptr(k_gamma), _i(_code(g)), _f(eps), _ptr(cos_sin),
           _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table), _i(block_table.shape[1]), _i(n_heads), _i(n_kv),
-          _i(head_dim), _ptr(workspace.status), _stream())
+          _i(head_dim), _ptr(bins_in), _f(norm_eps), _ptr(workspace.status), _stream())
 
 
 SKINNY_MAX_TOKENS = 16
@@ -256,7 +280,8 @@ def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "pl
           _i(after_skinny), _stream())
 
 
-NORM_WORDS = 256    # 64-bit words of the accumulators of one norm: 16 rows of 16 (8 bins, a flag, spare)
+NORM_ROW_WORDS = 16  # 64-bit words of one row's accumulator: 8 bins, a word that says "not finite", spare
+NORM_WORDS = 256    # the accumulators of one norm of a few-token step: 16 rows
 
 
 def rope_table(positions, inv_freq, out, position_scale: float = 1.0, by_pair: bool = False) -> None:

@@ -92,10 +92,13 @@ class Attention(Mixer):
             q = rt.empty(n, self.q_size)
             with rt.phase("attn_rope"):
                 cos_sin = None if self.position is None else self.position.tables(ctx, by_pair=True)
+            norm_in = None
+            if isinstance(x, base.DeferredNorm):      # the norm before rides on this product
+                x, norm_in = x.x_gamma, (x.bins, x.request.eps)
             with rt.phase("attn_qkv", self.w_qkv, n):
                 ops.linear_tc_qkv(x, self.w_qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
                                   cache.block_table, cache.k_pages, cache.v_pages, q, rt.workspace, s.n_heads,
-                                  s.n_kv_heads, s.head_dim)
+                                  s.n_kv_heads, s.head_dim, norm_in=norm_in)
             with self._core_phase(ctx, cache):
                 self._attend(ctx, q, cache, attn)
         else:
@@ -156,7 +159,9 @@ class Attention(Mixer):
 
     def _fused_qkv(self, x, cache) -> bool:
         s = self.spec
-        return (not isinstance(x, base.DeferredNorm) and not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
+        if isinstance(x, base.DeferredNorm):
+            x = x.x_gamma
+        return (not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
                 and self.w_qkv.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and (self.position is None or (self.position.tables_by_pair and self.position.half * 2 == s.head_dim))
                 and ops.linear_tc_qkv_supported(x, s.n_heads, s.n_kv_heads, s.head_dim))

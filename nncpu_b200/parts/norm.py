@@ -30,8 +30,10 @@ class RMSNorm(Norm):
         return out
 
     def request(self, ctx, residual):
-        """At up to 16 tokens in a bfloat16 run the few-token products around this norm can carry it."""
-        if (ctx.n_tokens > ops.SKINNY_MAX_TOKENS or self.rt.dtype != torch.bfloat16 or self.size % 8
-                or residual.dtype != torch.float32):
+        """In a bfloat16 run the products around this norm can carry it: the few-token products at up to 16
+        tokens, the tensor-core products of whole prompts (a launch, and at many tokens a pass over the residual
+        stream, less)."""
+        if (self.rt.dtype != torch.bfloat16 or self.size % 16 or residual.dtype != torch.float32
+                or not self.rt.fuses_norms(ctx.n_tokens, self.size)):
             return None
         return NormRequest(self, residual, self.gamma, self.eps, self.size)

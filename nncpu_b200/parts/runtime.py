@@ -104,7 +104,8 @@ class Runtime:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._workspace = None
         self.arena: Optional[Arena] = None      # set by the engine around a step; without one, the allocator serves
-        self._norm_bins = None          # accumulators of the norms that ride on the few-token products
+        self._norm_bins = None          # accumulators of the norms that ride on products, during such a step
+        self._norm_rows = [None, None]
         self._norm_turn = 0
         self._status_host = None
         self._status_posted = []
@@ -152,47 +153,64 @@ class Runtime:
         alignment rule go to the tensor cores; everything else, and every
         float32 product, runs in true 32-bit on CUDA cores.
 
-        ``x`` may be a ``DeferredNorm`` (a norm's unfinished output): the few-token product finishes it, any
-        other path makes the ordinary tensor first.  ``then_norm`` (a ``NormRequest``): this product is the last
-        write into ``out`` before that norm reads it; where the few-token product runs it fulfils the request."""
+        ``x`` may be a ``DeferredNorm`` (a norm's unfinished output): the few-token product and the product of
+        whole prompts finish it, any other path makes the ordinary tensor first.  ``then_norm`` (a ``NormRequest``):
+        this product is the last write into ``out`` before that norm reads it; the same two products fulfil it."""
         deferred = x if isinstance(x, DeferredNorm) else None
-        few = (x.shape[0] <= ops.SKINNY_MAX_TOKENS and self.tensor_cores_take(x.dtype, w, x.shape[1]))
+        takes = self.tensor_cores_take(x.dtype, w, x.shape[1])
+        few = takes and x.shape[0] <= ops.SKINNY_MAX_TOKENS
+        fuses = few or (takes and self.fuses_norms(x.shape[0], w.shape[0]))   # this product can carry norms
         if deferred is not None:
-            if few:
+            if fuses:
                 x, norm_in = deferred.x_gamma, (deferred.bins, deferred.request.eps)
             else:
                 x, norm_in = deferred.finish(), None
         else:
             norm_in = None
-        if self.tensor_cores_take(x.dtype, w, x.shape[1]):
+        if takes:
+            norm_out = None
+            if (fuses and then_norm is not None and self._norm_bins is not None and epilogue == "plain"
+                    and out.dtype == torch.float32 and out.shape[1] == then_norm.size == w.shape[0] and out.is_contiguous()
+                    and self._norm_bins.shape[1] == (ops.SKINNY_MAX_TOKENS if few else out.shape[0])):
+                # two sets of accumulators (and of rows times gamma) take turns: this product adds into one (zero
+                # since it was last cleared) and clears the other, whose consumer has run by now
+                turn = self._norm_turn
+                self._norm_turn = 1 - turn
+                if self._norm_rows[turn] is None:
+                    self._norm_rows[turn] = self.empty(*out.shape, keep=True)
+                made = DeferredNorm(self._norm_rows[turn], self._norm_bins[turn], then_norm)
+                norm_out = (made.x_gamma, then_norm.gamma, made.bins, self._norm_bins[1 - turn])
             if few:
-                norm_out = None
-                if (then_norm is not None and self._norm_bins is not None and epilogue == "plain" and out.dtype == torch.float32
-                        and out.shape[1] == then_norm.size == w.shape[0] and out.is_contiguous()):
-                    m, n = out.shape
-                    # two blocks of accumulators take turns: this product adds into one (zero since it was last
-                    # cleared) and clears the other, whose consumer has run by now
-                    mine, other = self._norm_bins[self._norm_turn], self._norm_bins[1 - self._norm_turn]
-                    self._norm_turn = 1 - self._norm_turn
-                    made = DeferredNorm(self.empty(m, n, keep=True), mine, then_norm)
-                    norm_out = (made.x_gamma, then_norm.gamma, mine, other)
-                ops.linear_skinny(x, w, bias, out, accumulate, epilogue, norm_out, norm_in)
-                if norm_out is not None:
-                    then_norm.result = made
+                ops.linear_skinny(x, w, bias, out, accumulate, epilogue,
+                                  norm_out and (norm_out[0], norm_out[1], norm_out[2].view(-1), norm_out[3].view(-1)),
+                                  norm_in and (norm_in[0].view(-1), norm_in[1]))
             else:
-                ops.linear_tc(x, w, bias, out, self.workspace, accumulate, epilogue)
+                ops.linear_tc(x, w, bias, out, self.workspace, accumulate, epilogue, norm_out=norm_out, norm_in=norm_in)
+            if norm_out is not None:
+                then_norm.result = made
         else:
             assert epilogue == "plain", "the fused epilogue exists on the tensor-core path only"
             ops.linear_simt(x, w, bias, out, accumulate)
 
-    def begin_norm_fusion(self) -> None:
-        """Once per step that may fuse norms into the few-token products: both blocks of accumulators start at
-        zero (one small fill), whatever an earlier step or another captured graph left in them."""
-        if self._norm_bins is None:
-            self._norm_bins = torch.zeros(2, ops.NORM_WORDS, dtype=torch.int64, device=self.device)
-        else:
-            self._norm_bins.zero_()
+    def fuses_norms(self, n_tokens: int, n_out: int) -> bool:
+        """Whether a bfloat16 product of ``n_tokens`` rows with ``n_out`` output features can carry the norms around
+        it: the few-token product always, the tensor-core product where it runs on pairs of SMs."""
+        return n_tokens <= ops.SKINNY_MAX_TOKENS or ops.linear_tc_fuses_norms(n_tokens, n_out)
+
+    def begin_norm_fusion(self, n_tokens: int) -> None:
+        """Once per step whose products may carry norms: two sets of exact accumulators, one row each per token (16
+        rows for a step of few tokens), start at zero (one fill), whatever an earlier step or another captured graph
+        left in them; the rows times gamma that go with them are taken when the first product needs them."""
+        rows = ops.SKINNY_MAX_TOKENS if n_tokens <= ops.SKINNY_MAX_TOKENS else n_tokens
+        self._norm_bins = self.empty(2, rows, ops.NORM_ROW_WORDS, dtype=torch.int64, keep=True)
+        self._norm_bins.zero_()
+        self._norm_rows = [None, None]
         self._norm_turn = 0
+
+    def end_norm_fusion(self) -> None:
+        """The step is over: its accumulators belong to the step's arena."""
+        self._norm_bins = None
+        self._norm_rows = [None, None]
 
     def phase(self, slot: str, weight=None, n_tokens: int = 0, nbytes: float = 0, flops: float = 0):
         """A profiler scope for the launches of one phase (free when the profiler is off).  With ``weight`` the

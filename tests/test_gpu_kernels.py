@@ -284,6 +284,54 @@ def test_rope_table(ops):
         assert (out[..., 1].cpu() - torch.sin(ang).float()).abs().max() < 2e-6
 
 
+@pytest.mark.parametrize("m,hidden,inter", [(512, 512, 1024), (700, 1040, 528)])
+def test_products_of_prompts_carry_the_norm_between_them(ops, m, hidden, inter):
+    """The same on the tensor cores for 512 tokens and more: the product that adds into the residual stream leaves
+    residual * gamma and one exact accumulator of the sum of squares per row; the product that follows (plain or
+    gated epilogue) multiplies its accumulators by the rows' scales.  A token count and widths that are no multiples
+    of the 256 x 256 tiles."""
+    g = torch.Generator().manual_seed(m + hidden)
+    act = torch.randn(m, inter, generator=g).bfloat16().to(DEV)
+    w_down = (torch.randn(hidden, inter, generator=g) * 0.1).bfloat16().to(DEV)
+    residual0 = torch.randn(m, hidden, generator=g).to(DEV)
+    gamma = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16().to(DEV)
+    eps = 1e-5
+    ws = ops.GemmWorkspace(DEV)
+    assert ops.linear_tc_fuses_norms(m, hidden) and not ops.linear_tc_fuses_norms(511, hidden)
+    residual = residual0.clone()
+    xg = torch.full((m, hidden), 9.0, dtype=torch.bfloat16, device=DEV)
+    bins = torch.zeros(m, ops.NORM_ROW_WORDS, dtype=torch.int64, device=DEV)
+    stale = torch.full((m, ops.NORM_ROW_WORDS), 77, dtype=torch.int64, device=DEV)
+    ops.linear_tc(act, w_down, None, residual, ws, accumulate=True, norm_out=(xg, gamma, bins, stale))
+    plain = residual0.clone()
+    ops.linear_tc(act, w_down, None, plain, ws, accumulate=True)
+    assert torch.equal(residual, plain)                                   # the product itself is untouched
+    assert int(stale.abs().max()) == 0                                    # the other norm's accumulators are cleared
+    check(xg, residual * gamma.float(), 8e-3, "residual * gamma")
+    words = bins.cpu().numpy().astype(object)
+    total = np.array([float(sum(int(words[t][b]) * 2.0 ** (32 * b - 150) for b in range(8))) for t in range(m)])
+    want_ss = (residual.double() ** 2).sum(-1).cpu().numpy()
+    assert np.abs(total - want_ss).max() <= 1e-6 * want_ss.max() and int(bins[:, 8].sum()) == 0
+    again = torch.zeros_like(bins)                                        # the same bits whatever the blocks' order
+    ops.linear_tc(act, w_down, None, residual0.clone(), ws, accumulate=True, norm_out=(torch.empty_like(xg), gamma, again, None))
+    assert torch.equal(again, bins)
+    normed = P.rmsnorm(residual.cpu().numpy(), gamma.float().cpu().numpy(), eps)
+    n_out = 16 * ((inter + 15) // 16)
+    w_next = (torch.randn(n_out, hidden, generator=g) * 0.1).bfloat16().to(DEV)
+    bias = torch.randn(n_out, generator=g).to(DEV)
+    out = torch.full((m, n_out), 9.0, device=DEV)
+    ops.linear_tc(xg, w_next, bias, out, ws, norm_in=(bins, eps))
+    want = P.linear(normed, w_next.float().cpu().numpy(), bias.cpu().numpy())
+    check(out, want, 8e-3, "consumer, plain epilogue")
+    gated = torch.full((m, n_out // 2), 9.0, device=DEV)
+    ops.linear_tc(xg, w_next, None, gated, ws, epilogue="swiglu", norm_in=(bins, eps))
+    y = P.linear(normed, w_next.float().cpu().numpy()).reshape(m, -1, 2, 8)
+    check(gated, P.swiglu(y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)), 8e-3, "consumer, gated epilogue")
+    with pytest.raises(ExtensionError):                                   # sizes whose kernel cannot carry a norm say so
+        ops.linear_tc(xg[:100].contiguous(), w_next, None, torch.empty(100, n_out, device=DEV), ws, norm_in=(bins[:100].contiguous(), eps))
+    assert int(ws.status.item()) == 0
+
+
 @pytest.mark.parametrize("m", [3, 13])
 def test_products_that_start_under_their_predecessor_give_the_same_bits(ops, m):
     """A chain of few-token products, each reading what the one before wrote (with a norm carried between two of
