@@ -47,6 +47,9 @@ constexpr int kBlockM = 128;  // rows of the A tile = tensor-core M
 constexpr int kBlockK = 64;   // 64 bfloat16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;    // K of one tcgen05.mma for 16-bit inputs
 constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA and tensor memory, warps 2-5: epilogue
+// The kernel for pairs of SMs has eight epilogue warps: two per quarter of the tensor-memory lanes, each with one
+// half of a tile's 256 columns, so that an epilogue that no product hides (the last tile's) takes half as long.
+constexpr int kPairThreads = 64 + 256;
 
 enum GemmStatus : int { kOk = 0, kTimeoutEmpty = 101, kTimeoutFull = 102, kTimeoutAccumFull = 103,
                         kTimeoutAccumEmpty = 104 };
@@ -925,14 +928,15 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
         : "memory");
 }
 
-// The q/k/v epilogue of one thread: its token's 256 accumulator columns are two whole heads.  Query and key
+// The q/k/v epilogue of one thread: its token's 256 accumulator columns are two whole heads, of which this thread's
+// warp takes head `hh`.  Query and key
 // heads get the per-head RMS norm (32-bit sum over the head) and the rotation of the pairs (i, i + 64); value
 // heads are only rounded.  Queries go to q_out, keys and values to the token's place in the cache pages.
 // The same arithmetic as the separate kernel (x * scale * gamma, then the rotation), so prefill and decode
 // agree to rounding (crates/nncpu/src/model/forward.rs:278-324).  `row_scale` multiplies the accumulators first: the
 // scale of the norm before the projection when that norm rides on this product, else 1 (which changes no bit).
 __device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float (*s_gamma)[128], uint32_t taddr,
-                                               int a_row, int n0, float row_scale) {
+                                               int a_row, int n0, float row_scale, int hh) {
     const QkvParams& e = p.qkv;
     const bool row_ok = a_row < p.rows_a;
     // where this token's keys and values go
@@ -945,10 +949,9 @@ __device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float 
             if (page >= 0) kv_row = (long)page * e.n_kv * kPage + pos % kPage;
         }
     }
-#pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {
+    {
         const int head = n0 / 128 + hh;
-        if (head >= e.n_heads + 2 * e.n_kv) break;
+        if (head >= e.n_heads + 2 * e.n_kv) return;
         const bool is_q = head < e.n_heads, is_k = !is_q && head < e.n_heads + e.n_kv;
         const uint32_t t0 = taddr + (uint32_t)(128 * hh);
         const void* gamma = is_q ? e.q_gamma : (is_k ? e.k_gamma : nullptr);
@@ -1019,7 +1022,7 @@ __device__ __forceinline__ void store_qkv_tile(const GemmParams& p, const float 
 }
 
 template <int kStages, int kEpi>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kPairThreads)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const GemmParams p) {
     constexpr int BN = 256;                       // columns of the pair's tile; each block stages 128 of its B rows
@@ -1039,7 +1042,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __shared__ float s_gamma[kEpi == kQkv ? 2 : 1][128];   // the q and k norm weights of the fused q/k/v epilogue
     let_next_kernel_start();   // the set-up below runs while the kernel before this one ends
     if constexpr (kEpi == kQkv) {
-        for (int i = threadIdx.x; i < 256; i += kThreads) {
+        for (int i = threadIdx.x; i < 256; i += kPairThreads) {
             const void* gamma = i < 128 ? p.qkv.q_gamma : p.qkv.k_gamma;
             s_gamma[i >> 7][i & 127] = gamma ? ld_f(gamma, i & 127, p.qkv.g_dt) : 1.0f;
         }
@@ -1057,7 +1060,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 8);  // four epilogue warps in each block
+            mbar_init(&acc_empty[b], 16); // eight epilogue warps in each block
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1137,7 +1140,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
         }
     } else {
-        const int quarter = warp & 3;
+        const int quarter = warp & 3;         // the quarter of the tensor-memory lanes this warp may read
+        const int half = (warp - 2) >> 2;     // the half of the tile's columns it takes
         const int row_in_tile = quarter * 32 + lane;
         int it = 0;
         for (int w = pair; w < n_items; w += n_pairs, ++it) {
@@ -1158,14 +1162,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (p.nf.bins_in != nullptr && a_ok)
                 row_scale = 1.0f / sqrtf(bins_total(p.nf.bins_in + (size_t)a_row * kBinWords) * (1.0f / (float)p.K) + p.nf.eps);
             if constexpr (kEpi == kQkv) {
-                store_qkv_tile(p, s_gamma, taddr, a_row, n0, row_scale);
+                store_qkv_tile(p, s_gamma, taddr, a_row, n0, row_scale, half);
             } else if (kEpi == kPlain && p.nf.xg_out != nullptr) {
                 // the norm after this product rides on it: besides out (float32, rows of whole 16-byte pieces: the
                 // launcher checked) it leaves out * gamma in bfloat16 and adds this tile's part of the row's sum of
                 // squares to the row's accumulator
                 float ss = 0.0f;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
                     const int col = n0 + c0;
                     if (col >= p.rows_b) break;        // the same for the whole warp
                     float v[16];
@@ -1221,7 +1225,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
                 if (a_ok) {
                     bins_add(p.nf.bins_out + (size_t)a_row * kBinWords, ss);
-                    if (p.nf.bins_clear != nullptr && n0 == 0) {
+                    if (p.nf.bins_clear != nullptr && n0 == 0 && half == 0) {
                         // the accumulators of the norm before, whose consumer has run: zero for their next use
                         uint4* z = reinterpret_cast<uint4*>(p.nf.bins_clear + (size_t)a_row * kBinWords);
 #pragma unroll
@@ -1230,7 +1234,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
             } else {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
                     float v[16];
                     tmem_ld16(taddr + (uint32_t)c0, v);
 #pragma unroll
@@ -1418,7 +1422,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cud
     const int pairs = n_items < max_pairs ? n_items : max_pairs;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kPairThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
