@@ -3,9 +3,9 @@ counterpart of the reference's ignored micro-benchmarks
 (crates/nncpu/src/kernels/tests.rs:1295-1482), which print streaming GB/s and
 GFLOP/s for its row kernels and one attention block.
 
-    python -m nncpu_b200.kernels.microbench linear M N K [--epilogue swiglu] [--accumulate]
+    python -m nncpu_b200.kernels.microbench linear M N K [--epilogue swiglu] [--accumulate] [--norm producer|consumer]
     python -m nncpu_b200.kernels.microbench linear-qkv TOKENS [--hidden K]
-    python -m nncpu_b200.kernels.microbench attention-decode BATCH CONTEXT [--splits S]
+    python -m nncpu_b200.kernels.microbench attention-decode BATCH CONTEXT [--splits S] [--cluster] [--from-projections]
     python -m nncpu_b200.kernels.microbench attention-prefill BATCH TOKENS
     python -m nncpu_b200.kernels.microbench rmsnorm ROWS DIM
 
@@ -67,13 +67,28 @@ def linear(args) -> None:
     out = torch.zeros(m, n_out, device=DEV, dtype=torch.float32 if args.accumulate else torch.bfloat16)
     work = ops.GemmWorkspace(DEV)
 
+    # the norms around the product riding on it: as the norm's producer it also leaves out * gamma and the rows' sums
+    # of squares, as its consumer it applies the rows' scales (few tokens, or 512 and more)
+    few = m <= ops.SKINNY_MAX_TOKENS
+    rows = ops.SKINNY_MAX_TOKENS if few else m
+    norm_out = norm_in = None
+    if args.norm == "producer":
+        gamma = torch.ones(n, device=DEV).bfloat16()
+        bins = torch.zeros(2, rows, ops.NORM_ROW_WORDS, dtype=torch.int64, device=DEV)
+        xg = torch.empty(m, n, device=DEV).bfloat16()
+        norm_out = (xg, gamma, bins[0].view(-1) if few else bins[0], bins[1].view(-1) if few else bins[1])
+    elif args.norm == "consumer":
+        bins = torch.zeros(rows, ops.NORM_ROW_WORDS, dtype=torch.int64, device=DEV)
+        bins[:, 4] = 1 << 20            # some sum of squares in every row
+        norm_in = (bins.view(-1) if few else bins, 1e-6)
+
     def call(w):
-        if m <= ops.SKINNY_MAX_TOKENS:
-            ops.linear_skinny(x, w, None, out, args.accumulate, args.epilogue)
+        if few:
+            ops.linear_skinny(x, w, None, out, args.accumulate, args.epilogue, norm_out, norm_in)
         else:
-            ops.linear_tc(x, w, None, out, work, args.accumulate, args.epilogue)
+            ops.linear_tc(x, w, None, out, work, args.accumulate, args.epilogue, norm_out=norm_out, norm_in=norm_in)
     ms = _time([lambda w=w: call(w) for w in ws], args.once)
-    print(f"linear M={m} N={n} K={k} epilogue={args.epilogue}: {ms * 1e3:.1f} us, "
+    print(f"linear M={m} N={n} K={k} epilogue={args.epilogue}{' norm ' + args.norm if args.norm else ''}: {ms * 1e3:.1f} us, "
           f"{n * k * 2 / ms / 1e6:.0f} GB/s of weights, {2 * m * n * k / ms / 1e9:.1f} TFLOP/s")
 
 
@@ -122,9 +137,21 @@ def attention_decode(args) -> None:
     splits = args.splits or max(1, min(296 // (b * nkv), ctx // 256))
     floats = 0 if args.cluster else ops.attention_decode_scratch_floats(b, nh, nkv, hd, splits)
     scratch = torch.empty(floats, device=DEV) if floats else None
-    ms = _time([lambda kp=kp, vp=vp: ops.attention_decode_mma(q, kp, vp, table, seq, pos, out, scratch, nh, nkv, hd,
-                                                              1 / math.sqrt(hd), 0, splits) for kp, vp in sets], args.once)
-    print(f"attention-decode batch={b} context={ctx} splits={splits}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of cache")
+    if args.from_projections:
+        # as a decode step runs it: from the float32 q/k/v projections, with per-head norm, rotation and cache append
+        qkv = torch.randn(b, (nh + 2 * nkv) * hd, device=DEV)
+        gamma = torch.ones(hd, device=DEV).bfloat16()
+        inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+        cs = torch.empty(b, hd // 2, 2, device=DEV)
+        ops.rope_table(pos, inv.float().to(DEV), cs)
+        run = lambda kp, vp: ops.attention_decode_mma_from_qkv(qkv, gamma, gamma, 1e-6, cs, kp, vp, True, table, seq, pos, out,
+                                                               scratch, nh, nkv, hd, 1 / math.sqrt(hd), 0, splits)
+    else:
+        run = lambda kp, vp: ops.attention_decode_mma(q, kp, vp, table, seq, pos, out, scratch, nh, nkv, hd,
+                                                      1 / math.sqrt(hd), 0, splits)
+    ms = _time([lambda kp=kp, vp=vp: run(kp, vp) for kp, vp in sets], args.once)
+    print(f"attention-decode batch={b} context={ctx} splits={splits}{' from projections' if args.from_projections else ''}: "
+          f"{ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of cache")
 
 
 def attention_prefill(args) -> None:
@@ -168,6 +195,8 @@ def main(argv=None) -> int:
     p.add_argument("m", type=int); p.add_argument("n", type=int); p.add_argument("k", type=int)
     p.add_argument("--epilogue", default="plain", choices=["plain", "swiglu"])
     p.add_argument("--accumulate", action="store_true")
+    p.add_argument("--norm", choices=["producer", "consumer"],
+                   help="the product also carries the norm after it (with --accumulate) or the norm before it")
     p.set_defaults(fn=linear)
     for name, fn, a, b in (("attention-decode", attention_decode, "batch", "context"),
                            ("attention-prefill", attention_prefill, "batch", "tokens")):
@@ -177,6 +206,8 @@ def main(argv=None) -> int:
         p.add_argument("--head-dim", type=int, default=128); p.add_argument("--splits", type=int, default=0)
         p.add_argument("--cluster", action="store_true", help="merge the splits inside a cluster (at most 8)")
         p.add_argument("--legacy", action="store_true", help="prefill: the mma.sync kernel instead of tcgen05")
+        p.add_argument("--from-projections", action="store_true",
+                       help="decode: start from the float32 q/k/v projections (norm, rotation, append inside), as a step does")
         p.set_defaults(fn=fn)
     p = sub.add_parser("linear-qkv")
     p.add_argument("tokens", type=int); p.add_argument("--hidden", type=int, default=4096)
