@@ -31,6 +31,10 @@
 //     multiplies its own result by them, which a product commutes with.
 // A producer also clears the accumulators of the norm before it, whose consumer has run by then.
 //
+// Two blocks of 8 warps run per SM.  A grid of N / 16 blocks that is a little more than that (N 5120: 320 blocks for
+// 296 places) would leave its last blocks to stream alone, each at what one block can keep in flight; such a grid
+// runs as blocks of 4 warps, four per SM, all at once with the same bytes in flight per SM.
+//
 // A step's products follow one another, and each would start with idle memory: launch, first addresses, the
 // first bytes' way from memory.  So the kernel is launched to overlap with the end of the kernel before it
 // (programmatic dependent launch): its blocks take the places that blocks of the earlier kernel leave, ask for
@@ -47,11 +51,9 @@
 
 namespace {
 
-constexpr int kWarps = 8;
 constexpr int kRows = 16;     // weight rows per block
 constexpr int kUnroll = 8;    // 32-wide k groups in flight per warp with up to 8 tokens; 6 with up to 16 (registers)
 
-static_assert(kRows * 16 <= kWarps * 32, "one output element per thread with 16 tokens");
 
 enum Epilogue : int { kPlain = 0, kSwiglu = 1 };
 
@@ -70,14 +72,16 @@ __device__ __forceinline__ uint4 ldg16_stream(const __nv_bfloat16* p) {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
 
-// NT = number of 8-token tiles (1: up to 8 tokens, 2: up to 16).
-template <int NT, int kEpi>
-__global__ void __launch_bounds__(kWarps * 32, 2)
+// NT = number of 8-token tiles (1: up to 8 tokens, 2: up to 16); kW = warps of the block (8 or 4).
+template <int NT, int kEpi, int kW>
+__global__ void __launch_bounds__(kW * 32, 16 / kW)
 skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, const void* __restrict__ bias,
               int bias_dt, void* __restrict__ out, int out_dt, int M, int N, int K, int lda, int ldc, int accumulate,
               const NormFusion nf) {
     constexpr int kU = NT == 1 ? kUnroll : 6;
-    __shared__ float part[kWarps][kRows][NT * 8 + 1];
+    constexpr int kThreadsHere = kW * 32;
+    constexpr int kPasses = kRows * 16 / kThreadsHere;   // output elements per thread: (token, row) pairs of 16 x 16
+    __shared__ float part[kW][kRows][NT * 8 + 1];
     __shared__ float row_scale[16];
     __shared__ unsigned long long bins_s[16][9];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -95,7 +99,7 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
 
     // this warp's share of K, in groups of 32
     const int n_groups = (K + 31) / 32;
-    const int per_warp = (n_groups + kWarps - 1) / kWarps;
+    const int per_warp = (n_groups + kW - 1) / kW;
     const int g_begin = warp * per_warp, g_end = min(n_groups, g_begin + per_warp);
     // Full blocks of kUnroll groups: every load is issued before the first product, without predicates.
     // Columns of tokens beyond M read a valid row and are never stored.
@@ -117,10 +121,15 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
 
     // What the product is added to is fetched now, under the weight stream, not after it: thread i of the
     // epilogue owns output (token i / 16, row i % 16); with at most 16 tokens that is one element per thread.
-    float before = 0.0f;
-    if (kEpi == kPlain && accumulate) {
-        const int tok = threadIdx.x / kRows, row = row0 + threadIdx.x % kRows;
-        if (tok < M && row < N) before = ld_f(out, (size_t)tok * ldc + row, out_dt);
+    float before[kPasses];
+#pragma unroll
+    for (int e = 0; e < kPasses; ++e) {
+        before[e] = 0.0f;
+        if (kEpi == kPlain && accumulate) {
+            const int i = threadIdx.x + e * kThreadsHere;
+            const int tok = i / kRows, row = row0 + i % kRows;
+            if (tok < M && row < N) before[e] = ld_f(out, (size_t)tok * ldc + row, out_dt);
+        }
     }
 
     // Consumer of a norm: the rows' accumulators are asked for now (asynchronous 8-byte copies into shared memory
@@ -135,7 +144,8 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     // Producer of a norm: the accumulators of the norm before it are cleared for their next use.
-    if (nf.bins_clear != nullptr && blockIdx.x == 0) nf.bins_clear[threadIdx.x] = 0ull;   // 16 * kBinWords = 256 words
+    if (nf.bins_clear != nullptr && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < 16 * kBinWords; i += kThreadsHere) nf.bins_clear[i] = 0ull;
 
     int g0 = g_begin;
     for (; g0 + kU <= g_fast_end; g0 += kU) {
@@ -194,12 +204,12 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
     __syncthreads();
     if (kEpi == kSwiglu) {
         // rows 0..7 of the block are gate rows, rows 8..15 the up rows of the same outputs
-        for (int i = threadIdx.x; i < 8 * M; i += kWarps * 32) {
+        for (int i = threadIdx.x; i < 8 * M; i += kThreadsHere) {
             const int tok = i / 8, j = i % 8;
             if (row0 + j + 8 >= N) continue;
             float g = 0.0f, u = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
+            for (int w = 0; w < kW; ++w) {
                 g += part[w][j][tok];
                 u += part[w][j + 8][tok];
             }
@@ -210,49 +220,74 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
             st_f(out, (size_t)tok * ldc + (row0 >> 1) + j, out_dt, silu_mul(g, u));
         }
     } else {
-        // thread i owns output (token i / 16, row i % 16): one element per thread, and every thread of the block
-        // walks through (the producer's sums of squares are taken with shuffles)
-        const int tok = threadIdx.x / kRows, j = threadIdx.x % kRows;
-        const int row = row0 + j;
-        const bool valid = tok < M && row < N;
-        float v = 0.0f;
-        if (valid) {
+        // output element i is (token i / 16, row i % 16): one per thread of 8 warps, two per thread of 4; every thread
+        // of the block walks through (the producer's sums of squares are taken with shuffles)
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) v += part[w][j][tok];
-            if (nf.bins_in != nullptr) v *= row_scale[tok];
-            if (bias) v += ld_f(bias, row, bias_dt);
-            if (accumulate) v += before;
-            st_f(out, (size_t)tok * ldc + row, out_dt, v);
-        }
-        if (nf.xg_out != nullptr) {
-            // producer of a norm: x * gamma for the consumer, and this block's part of every row's sum of squares
-            // (the 16 lanes that hold a row's 16 columns add up through the shuffle tree)
-            if (valid) nf.xg_out[(size_t)tok * N + row] = __float2bfloat16(v * ld_f(nf.gamma, row, nf.gamma_dt));
-            float sq = valid ? v * v : 0.0f;
+        for (int e = 0; e < kPasses; ++e) {
+            const int i = threadIdx.x + e * kThreadsHere;
+            const int tok = i / kRows, j = i % kRows;
+            const int row = row0 + j;
+            const bool valid = tok < M && row < N;
+            float v = 0.0f;
+            if (valid) {
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            if (j == 0 && tok < M) bins_add(nf.bins_out + tok * kBinWords, sq);
+                for (int w = 0; w < kW; ++w) v += part[w][j][tok];
+                if (nf.bins_in != nullptr) v *= row_scale[tok];
+                if (bias) v += ld_f(bias, row, bias_dt);
+                if (accumulate) v += before[e];
+                st_f(out, (size_t)tok * ldc + row, out_dt, v);
+            }
+            if (nf.xg_out != nullptr) {
+                // producer of a norm: x * gamma for the consumer, and this block's part of every row's sum of squares
+                // (the 16 lanes that hold a row's 16 columns add up through the shuffle tree)
+                if (valid) nf.xg_out[(size_t)tok * N + row] = __float2bfloat16(v * ld_f(nf.gamma, row, nf.gamma_dt));
+                float sq = valid ? v * v : 0.0f;
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (j == 0 && tok < M) bins_add(nf.bins_out + tok * kBinWords, sq);
+            }
         }
     }
 }
 
+int sm_count() {
+    static int counts[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (counts[dev] == 0 && cudaDeviceGetAttribute(&counts[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        counts[dev] = 148;
+    return counts[dev];
+}
+
+int g_forced_warps = 0;   // measurements and tests: blocks of 8 or of 4 warps whatever the sizes (0: by the sizes)
+
 template <int NT, int kEpi>
 int launch(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M, int N, int K, int lda,
            int ldc, int accumulate, const NormFusion& nf, bool overlap, cudaStream_t stream) {
+    const int blocks = (N + kRows - 1) / kRows;
+    // more blocks than two per SM but no more than four: blocks of 4 warps all run at once
+    const int sms = sm_count();
+    const bool small = g_forced_warps ? g_forced_warps == 4 : (blocks > 2 * sms && blocks <= 4 * sms);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + kRows - 1) / kRows);
-    cfg.blockDim = dim3(kWarps * 32);
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(small ? 128 : 256);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = overlap ? overlap_attribute(attr) : 0;
     cfg.attrs = attr;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_kernel<NT, kEpi>, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
-                                             bias, bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf);
+    const cudaError_t e =
+        small ? cudaLaunchKernelEx(&cfg, skinny_kernel<NT, kEpi, 4>, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias,
+                                   bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf)
+              : cudaLaunchKernelEx(&cfg, skinny_kernel<NT, kEpi, 8>, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias,
+                                   bias_dt, C, c_dt, M, N, K, lda, ldc, accumulate, nf);
     NN_CHECK(e == cudaSuccess, "linear (few tokens): launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
 
 }  // namespace
+
+// For measurements and tests: blocks of 8 or of 4 warps whatever the sizes; 0: chosen by the sizes.
+extern "C" void nncpu_linear_skinny_force_warps(int warps) { g_forced_warps = warps; }
 
 extern "C" int nncpu_linear_skinny_supported(int M, int N, int K, int lda) {
     return M > 0 && M <= 16 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0;

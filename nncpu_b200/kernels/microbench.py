@@ -69,7 +69,8 @@ def linear(args) -> None:
 
     # the norms around the product riding on it: as the norm's producer it also leaves out * gamma and the rows' sums
     # of squares, as its consumer it applies the rows' scales (few tokens, or 512 and more)
-    few = m <= ops.SKINNY_MAX_TOKENS
+    few = m <= ops.SKINNY_MAX_TOKENS and not args.tensor_cores
+    ops.linear_skinny_force_warps(args.warps)
     rows = ops.SKINNY_MAX_TOKENS if few else m
     norm_out = norm_in = None
     if args.norm == "producer":
@@ -195,6 +196,9 @@ def main(argv=None) -> int:
     p.add_argument("m", type=int); p.add_argument("n", type=int); p.add_argument("k", type=int)
     p.add_argument("--epilogue", default="plain", choices=["plain", "swiglu"])
     p.add_argument("--accumulate", action="store_true")
+    p.add_argument("--tensor-cores", action="store_true", help="up to 16 tokens too on the tcgen05 kernels")
+    p.add_argument("--warps", type=int, default=0, choices=[0, 4, 8],
+                   help="few tokens: blocks of 8 or of 4 warps (0: chosen by the sizes)")
     p.add_argument("--norm", choices=["producer", "consumer"],
                    help="the product also carries the norm after it (with --accumulate) or the norm before it")
     p.set_defaults(fn=linear)

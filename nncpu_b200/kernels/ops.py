@@ -280,6 +280,12 @@ def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "pl
           _i(after_skinny), _stream())
 
 
+def linear_skinny_force_warps(warps: int) -> None:
+    """For measurements and tests: the few-token product runs as blocks of 8 or of 4 warps whatever the sizes;
+    0: chosen by the sizes (4 warps where 16-row blocks number more than two per SM and at most four)."""
+    library.load("linear_skinny").nncpu_linear_skinny_force_warps(ctypes.c_int(int(warps)))
+
+
 NORM_ROW_WORDS = 16  # 64-bit words of one row's accumulator: 8 bins, a word that says "not finite", spare
 NORM_WORDS = 256    # the accumulators of one norm of a few-token step: 16 rows
 

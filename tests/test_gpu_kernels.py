@@ -284,6 +284,57 @@ def test_rope_table(ops):
         assert (out[..., 1].cpu() - torch.sin(ang).float()).abs().max() < 2e-6
 
 
+@pytest.mark.parametrize("m,n,k", [(3, 307, 4104), (8, 64, 8192), (13, 5120, 2560), (16, 1000, 136)])
+def test_few_token_product_in_blocks_of_four_warps(ops, m, n, k):
+    """Grids of a little more than two 16-row blocks per SM run as blocks of 4 warps (every thread finishes two
+    output elements): forced here at other sizes too, every epilogue, with and without the norms riding on it, and
+    bit for bit what blocks of 8 warps give wherever a warp's share of K is the same."""
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    want = (x.double() @ w.double().T).float()
+    try:
+        ops.linear_skinny_force_warps(4)
+        out = torch.full((m, n), 9.0, device=DEV)
+        ops.linear_skinny(x, w, b, out)
+        check(out, want + b, 1e-5, "float32 out with bias")
+        again = torch.full((m, n), 9.0, device=DEV)
+        ops.linear_skinny(x, w, b, again)
+        assert torch.equal(out, again)
+        acc = torch.full((m, n), 0.5, dtype=torch.bfloat16, device=DEV)
+        ops.linear_skinny(x, w, None, acc, accumulate=True)
+        check(acc, want + 0.5, 8e-3, "accumulate in bfloat16")
+        if n % 16 == 0:
+            gated = torch.full((m, n // 2), 9.0, device=DEV)
+            ops.linear_skinny(x, w, None, gated, epilogue="swiglu")
+            y = want.cpu().numpy().reshape(m, -1, 2, 8)
+            check(gated, P.swiglu(y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)), 1e-5, "gated")
+            gamma = (1 + 0.1 * torch.randn(n, generator=g)).bfloat16().to(DEV)
+            residual = torch.full((m, n), 0.25, device=DEV)
+            xg = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+            bins = torch.zeros(ops.NORM_WORDS, dtype=torch.int64, device=DEV)
+            stale = torch.full((ops.NORM_WORDS,), 5, dtype=torch.int64, device=DEV)
+            ops.linear_skinny(x, w, None, residual, accumulate=True, norm_out=(xg, gamma, bins, stale))
+            check(residual, want + 0.25, 1e-5, "producer")
+            assert int(stale.abs().max()) == 0
+            check(xg, residual * gamma.float(), 8e-3, "residual * gamma")
+            w2 = (torch.randn(64, n, generator=g) * 0.05).bfloat16().to(DEV)
+            out2 = torch.empty(m, 64, device=DEV)
+            ops.linear_skinny(xg, w2, None, out2, norm_in=(bins, 1e-6))
+            normed = P.rmsnorm(residual.cpu().numpy(), gamma.float().cpu().numpy(), 1e-6)
+            check(out2, P.linear(normed, w2.float().cpu().numpy()), 8e-3, "consumer")
+            ops.linear_skinny_force_warps(8)
+            wide = torch.zeros_like(bins)
+            ops.linear_skinny(x, w, None, torch.full((m, n), 0.25, device=DEV), accumulate=True,
+                              norm_out=(torch.empty_like(xg), gamma, wide, None))
+            ss = lambda t: np.array([sum(int(v) * 2.0 ** (32 * i - 150) for i, v in enumerate(row[:8]))
+                                     for row in t.view(16, 16).cpu().numpy().astype(object)])
+            assert np.abs(ss(bins) - ss(wide)).max() <= 1e-4 * max(ss(wide).max(), 1e-30)
+    finally:
+        ops.linear_skinny_force_warps(0)
+
+
 @pytest.mark.parametrize("m,hidden,inter", [(512, 512, 1024), (700, 1040, 528)])
 def test_products_of_prompts_carry_the_norm_between_them(ops, m, hidden, inter):
     """The same on the tensor cores for 512 tokens and more: the product that adds into the residual stream leaves
