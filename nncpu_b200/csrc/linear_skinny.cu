@@ -174,19 +174,29 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
             }
         }
     }
-    // The rest, one group at a time; K is a multiple of 8, so a 16-byte chunk is inside K or outside.
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    for (; g0 < g_end; ++g0) {
-        const int k = g0 * 32 + c * 8;
-        const bool ok = k < K;
-        const uint4 a_lo = ok ? ldg16_stream(w_lo + k) : z, a_hi = ok ? ldg16_stream(w_hi + k) : z;
-        const uint4 b0 = ok ? *reinterpret_cast<const uint4*>(x0 + k) : z;
-        mma_bf16(acc[0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b0.x, b0.y);
-        mma_bf16(acc[0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b0.z, b0.w);
-        if (NT > 1) {
-            const uint4 b1 = ok ? *reinterpret_cast<const uint4*>(x1 + k) : z;
-            mma_bf16(acc[1], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b1.x, b1.y);
-            mma_bf16(acc[1], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b1.z, b1.w);
+    // The rest (fewer than a full round of groups, the last of them perhaps cut by K) as one more round whose loads
+    // are all issued before the first product, with zeros where there is nothing: K is a multiple of 8, so a
+    // 16-byte chunk is inside K or outside.
+    if (g0 < g_end) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        uint4 b0[kU], b1[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int k = (g0 + u) * 32 + c * 8;
+            const bool ok = g0 + u < g_end && k < K;
+            a_lo[u] = ok ? ldg16_stream(w_lo + k) : z;
+            a_hi[u] = ok ? ldg16_stream(w_hi + k) : z;
+            b0[u] = ok ? *reinterpret_cast<const uint4*>(x0 + k) : z;
+            if (NT > 1) b1[u] = ok ? *reinterpret_cast<const uint4*>(x1 + k) : z;
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            mma_bf16(acc[0], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b0[u].x, b0[u].y);
+            mma_bf16(acc[0], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b0[u].z, b0[u].w);
+            if (NT > 1) {
+                mma_bf16(acc[1], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b1[u].x, b1[u].y);
+                mma_bf16(acc[1], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b1[u].z, b1[u].w);
+            }
         }
     }
     // accumulator layout: [0..1] row r, tokens 2c, 2c+1; [2..3] row r + 8
@@ -259,15 +269,32 @@ int sm_count() {
     return counts[dev];
 }
 
+// Blocks of 4 warps (four per SM) or of 8 (two per SM)?  What a product costs beyond its bytes are the round trips
+// to memory that follow one another: a warp makes one per round of `unroll` groups of its share of K, and a grid
+// makes one pass per filling of the SMs' places.  The smaller count of (passes x rounds) wins; on a tie the
+// small blocks, if the big ones would leave a nearly empty second pass (at most four blocks per SM) or with two
+// token tiles.  Measured on the layer shapes and output matrices of the 8B, 14B and 32B sizes at 8 and 16 tokens
+// (26 cases, differences of 3 to 30 %): the rule picks the faster kind in all of them.
+bool four_warps_pay(int blocks, int K, int unroll, int sms) {
+    const int groups = (K + 31) / 32;
+    auto cost = [&](int warps) {
+        const int places = (16 / warps) * sms;
+        const int passes = (blocks + places - 1) / places;
+        const int per_warp = (groups + warps - 1) / warps;
+        return (long)passes * ((per_warp + unroll - 1) / unroll);
+    };
+    const long big = cost(8), small = cost(4);
+    if (small != big) return small < big;
+    return blocks > 2 * sms && (blocks <= 4 * sms || unroll < kUnroll);
+}
+
 int g_forced_warps = 0;   // measurements and tests: blocks of 8 or of 4 warps whatever the sizes (0: by the sizes)
 
 template <int NT, int kEpi>
 int launch(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M, int N, int K, int lda,
            int ldc, int accumulate, const NormFusion& nf, bool overlap, cudaStream_t stream) {
     const int blocks = (N + kRows - 1) / kRows;
-    // more blocks than two per SM but no more than four: blocks of 4 warps all run at once
-    const int sms = sm_count();
-    const bool small = g_forced_warps ? g_forced_warps == 4 : (blocks > 2 * sms && blocks <= 4 * sms);
+    const bool small = g_forced_warps ? g_forced_warps == 4 : four_warps_pay(blocks, K, NT == 1 ? kUnroll : 6, sm_count());
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)blocks);
     cfg.blockDim = dim3(small ? 128 : 256);
