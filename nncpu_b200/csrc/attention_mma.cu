@@ -316,6 +316,7 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 // warp).  grid = (n_splits, n_kv, n_tok), 128 threads; splits are whole pages.
 // ---------------------------------------------------------------------------
 constexpr int kDecodeStages = 3;
+constexpr int kMaxClusterSplits = 8;   // splits that merge inside a thread-block cluster (the portable cluster size)
 
 // The decode kernel can start from the float32 q/k/v projections of its tokens instead of finished queries: every
 // block then makes its own queries (per-head RMS norm, rotation: crates/nncpu/src/model/forward.rs:278-324), and the
@@ -619,14 +620,29 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
         const int rank = (int)cluster_rank_();
         for (int i = rank * share + threadIdx.x; i < min(total, (rank + 1) * share); i += 128) {
             const int head = i / HD, d = i % HD;
+            // all the loads from the other blocks' shared memory are issued before the first is used: one trip
+            // through the cluster, not one per split
+            float ms[kMaxClusterSplits], os[kMaxClusterSplits], ls[kMaxClusterSplits];
+#pragma unroll
+            for (int sp = 0; sp < kMaxClusterSplits; ++sp) {
+                if (sp < n_splits) {
+                    ms[sp] = ld_cluster_(merged + head * W + HD, sp);
+                    os[sp] = ld_cluster_(merged + head * W + d, sp);
+                    ls[sp] = ld_cluster_(merged + head * W + HD + 1, sp);
+                }
+            }
             float mm = -INFINITY;
-            for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, ld_cluster_(merged + head * W + HD, sp));
+#pragma unroll
+            for (int sp = 0; sp < kMaxClusterSplits; ++sp)
+                if (sp < n_splits) mm = fmaxf(mm, ms[sp]);
             float oo = 0.0f, ll = 0.0f;
-            for (int sp = 0; sp < n_splits; ++sp) {
-                const float ms = ld_cluster_(merged + head * W + HD, sp);
-                const float cs = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
-                oo = fmaf(ld_cluster_(merged + head * W + d, sp), cs, oo);
-                ll = fmaf(ld_cluster_(merged + head * W + HD + 1, sp), cs, ll);
+#pragma unroll
+            for (int sp = 0; sp < kMaxClusterSplits; ++sp) {
+                if (sp < n_splits) {
+                    const float cs = ms[sp] == -INFINITY ? 0.0f : exp2f(ms[sp] - mm);
+                    oo = fmaf(os[sp], cs, oo);
+                    ll = fmaf(ls[sp], cs, ll);
+                }
             }
             out[out_row + i] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
         }
