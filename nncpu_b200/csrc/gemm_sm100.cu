@@ -338,6 +338,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // Epilogue: warp w may read the tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
+        // The norm before this product rides on it (swapped operands: tokens are the columns, and all of them are
+        // in every tile): the tokens' scales, worked out once by the four epilogue warps while the first tile's
+        // products run.
+        __shared__ float s_scale[BN];
+        const bool scaled = p.nf.bins_in != nullptr;
+        if (scaled) {
+            for (int j = threadIdx.x - 64; j < BN; j += 128)
+                s_scale[j] = j < p.rows_b ? 1.0f / sqrtf(bins_total(p.nf.bins_in + (size_t)j * kBinWords) * (1.0f / (float)p.K) + p.nf.eps)
+                                          : 0.0f;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         int it = 0;
         for (int w = blockIdx.x; w < n_tiles; w += gridDim.x, ++it) {
             const int m0 = (w % p.tiles_a) * kBlockM, n0 = (w / p.tiles_a) * BN;
@@ -354,6 +365,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
                 tmem_ld16(taddr + (uint32_t)c0, v);
+                if (scaled) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] *= s_scale[c0 + j];
+                }
                 store16<kEpi>(p, a_row, n0 + c0, v);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -792,6 +807,16 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int row_in_tile = quarter * 32 + lane;
     const int a_row = m0 + row_in_tile;
     const bool early_old = kEpi == kPlain && p.swap && cols <= 16;
+    // The norm before this product rides on it (tokens are columns here): the scales of the tile's tokens, worked
+    // out by the epilogue warps while the weights stream; they meet at the named barrier below before anyone reads.
+    __shared__ float s_scale[BN];
+    if (warp >= 2 && p.nf.bins_in != nullptr) {
+        for (int j = threadIdx.x - 64; j < BN; j += 128) {
+            const int tok = n0 + j;
+            s_scale[j] = tok < p.rows_b ? 1.0f / sqrtf(bins_total(p.nf.bins_in + (size_t)tok * kBinWords) * (1.0f / (float)p.K) + p.nf.eps)
+                                        : 0.0f;
+        }
+    }
     float old[16];
     if (warp >= 2 && early_old) {
 #pragma unroll
@@ -801,6 +826,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                          ? ld_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt) : 0.0f;
         }
     }
+    if (warp >= 2 && p.nf.bins_clear != nullptr && blockIdx.x == 0)   // the norm before: its consumer has run
+        for (int i = threadIdx.x - 64; i < p.rows_b * kBinWords; i += 128) p.nf.bins_clear[i] = 0ull;
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // all blocks of the cluster are running
     bool received = true;
     if (warp >= 2) {
@@ -853,14 +880,29 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int j = 0; j < 16; ++j)
                     if (j < n) v[j] += recv[(r * cols + c0 + j) * kBlockM + row_in_tile];
             }
+            if (p.nf.bins_in != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j < n) v[j] *= s_scale[c_begin + c0 + j];
+            }
             if (early_old) {
                 // C[token, a_row] = (product + bias) + what was there, as store16 does for this layout
+                const bool a_ok = a_row < p.rows_a;
                 const float b = p.bias ? ld_f(p.bias, min(a_row, p.rows_a - 1), p.bias_dt) : 0.0f;
+                const float g = p.nf.xg_out != nullptr ? ld_f(p.nf.gamma, min(a_row, p.rows_a - 1), p.nf.gamma_dt) : 0.0f;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = n0 + c_begin + j;
-                    if (j < n && tok < p.rows_b && a_row < p.rows_a)
-                        st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, (v[j] + b) + old[j]);
+                    const bool ok = j < n && tok < p.rows_b;        // the same for the whole warp
+                    const float y = (v[j] + b) + old[j];
+                    if (ok && a_ok) st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, y);
+                    if (p.nf.xg_out != nullptr && ok) {
+                        // the norm after this product rides on it: out * gamma for its consumer, and the token's sum
+                        // of squares over this warp's 32 features into the token's exact accumulator
+                        if (a_ok) p.nf.xg_out[(size_t)tok * p.rows_a + a_row] = __float2bfloat16(y * g);
+                        const float sq = warp_sum(a_ok ? y * y : 0.0f);
+                        if (lane == 0) bins_add(p.nf.bins_out + (size_t)tok * kBinWords, sq);
+                    }
                 }
             } else {
                 store16<kEpi>(p, a_row, n0 + c_begin + c0, v, n);
@@ -1563,7 +1605,30 @@ enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4 };
 // words, zero before the call) the exact sums of squares of C's rows; bins_clear [M, 16] (or null) is set to zero.
 // Consumer: X holds such rows of width K and bins_in [M, 16] their accumulators: the result is multiplied by
 // 1 / sqrt(sum / K + eps) per row before bias and activation.
+// From 17 to 64 tokens the same holds where nncpu_linear_tc_norm_roles says so (bit 0: may be a consumer, bit 1: may
+// be a producer): the cluster kernel does both (a producer with at most 16 tokens a block), the kernel of whole
+// 128-row tiles per block consumes.
 extern "C" int nncpu_linear_tc_fuses_norms(int M, int N) { return M >= 512 && N >= 512; }
+
+namespace {
+// The cluster size that nncpu_linear_tc picks for a product of 17 to 64 tokens (1: whole tiles per block).
+int cluster_blocks(int bn, int n_tiles, int kb_total) {
+    if (!(bn >= 32 && bn <= 128 && n_tiles < sm_count())) return 1;
+    const int places = (bn <= 64 ? 2 : 1) * sm_count() * 87 / 100;
+    int best = 1;
+    for (int s = 2; s <= 8 && s <= bn && kb_total / s >= 4; ++s)
+        if (n_tiles * s <= places) best = s;
+    return best;
+}
+}  // namespace
+
+extern "C" int nncpu_linear_tc_norm_roles(int M, int N, int K) {
+    if (nncpu_linear_tc_fuses_norms(M, N)) return 3;
+    if (M < 17 || M > 64) return 0;
+    const int bn = M <= 32 ? 32 : 64;
+    const int s = cluster_blocks(bn, (N + kBlockM - 1) / kBlockM, (K + kBlockK - 1) / kBlockK);
+    return 1 | ((s > 1 && (bn + s - 1) / s <= 16) ? 2 : 0);
+}
 
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
                                int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, void* xg_out,
@@ -1589,12 +1654,13 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
     const int esize = c_dt == DT_F32 ? 4 : 2;
     p.vec = ((uintptr_t)C % 16 == 0) && ((size_t)ldc * esize % 16 == 0);
     if (xg_out != nullptr || bins_in != nullptr) {
-        NN_CHECK(nncpu_linear_tc_fuses_norms(M, N) && !(plan & kPlanNoPairs),
-                 "gemm: norms ride only on products of 512 or more tokens and output features (M %d, N %d)", M, N);
+        const int roles = plan == 0 ? nncpu_linear_tc_norm_roles(M, N, K) : (nncpu_linear_tc_fuses_norms(M, N) && !(plan & kPlanNoPairs) ? 3 : 0);
+        NN_CHECK((bins_in == nullptr || (roles & 1)) && (xg_out == nullptr || (roles & 2)),
+                 "gemm: this product cannot carry that norm (M %d, N %d, K %d: see nncpu_linear_tc_norm_roles)", M, N, K);
         NN_CHECK(xg_out == nullptr || bins_in == nullptr, "gemm: a product is a norm's producer or its consumer");
     }
     if (xg_out != nullptr) {
-        NN_CHECK(epilogue == kPlain && c_dt == DT_F32 && p.vec && N % 16 == 0 && gamma != nullptr && bins_out != nullptr &&
+        NN_CHECK(epilogue == kPlain && c_dt == DT_F32 && (p.vec || M <= 64) && N % 16 == 0 && gamma != nullptr && bins_out != nullptr &&
                      ((uintptr_t)xg_out % 16) == 0 && ((uintptr_t)gamma % 16) == 0 && ((uintptr_t)bins_out % 16) == 0 &&
                      ((uintptr_t)bins_clear % 16) == 0,
                  "gemm: leaving a norm's input needs the plain epilogue, float32 output in 16-byte rows, N %% 16 == 0, "
@@ -1658,10 +1724,7 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         // whole clusters waiting (measured at 64 tokens on the Qwen3-8B layer sizes: 48 tiles take 5 blocks each,
         // 17.3 us, where 6 take 25 us; 32 tiles take 8).  With as many tiles as SMs or more, whole tiles per block
         // stream as fast and need no exchange.
-        const int places = (bn <= 64 ? 2 : 1) * sm_count() * 87 / 100;
-        int best = 1;
-        for (int s = 2; s <= 8 && s <= bn && p.kb_total / s >= 4; ++s)
-            if (n_tiles * s <= places) best = s;
+        const int best = cluster_blocks(bn, n_tiles, p.kb_total);
         p.splits = best;
         if (best > 1)
             return epilogue == kSwiglu ? dispatch_cluster<kSwiglu>(bn, ma, mb, p, stream)

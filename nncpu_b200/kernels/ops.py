@@ -172,6 +172,13 @@ def linear_tc_fuses_norms(m: int, n: int) -> bool:
     return bool(library.load("gemm_sm100").nncpu_linear_tc_fuses_norms(m, n))
 
 
+def linear_tc_norm_roles(m: int, n: int, k: int) -> int:
+    """Which norms the tensor-core product of ``m`` tokens, ``n`` output features and width ``k`` can carry: bit 0 the
+    norm before it (``norm_in``), bit 1 the norm after it (``norm_out``).  Whole prompts both; 17 to 64 tokens the
+    norm before, and the norm after where a cluster shares every output tile."""
+    return int(library.load("gemm_sm100").nncpu_linear_tc_norm_roles(m, n, k))
+
+
 def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = False, epilogue: str = "plain",
               plan: str = "auto", norm_out=None, norm_in=None) -> None:
     """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16.  With
@@ -180,8 +187,8 @@ def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = Fals
     or for measurements and tests "even_from_17" (17 to 64 tokens deal their
     k-blocks out evenly like 65 to 256), "never_even", "no_pairs".
 
-    Where ``linear_tc_fuses_norms(m, n)``, the product can carry the RMS norms around it as ``linear_skinny``
-    does: ``norm_out = (xg, gamma, bins, bins_clear)`` and ``norm_in = (bins, eps)`` with accumulators of
+    Where ``linear_tc_norm_roles(m, n, k)`` says so, the product can carry the RMS norms around it as
+    ``linear_skinny`` does: ``norm_out = (xg, gamma, bins, bins_clear)`` and ``norm_in = (bins, eps)`` with accumulators of
     ``NORM_ROW_WORDS`` 64-bit words per row (int64 [m, NORM_ROW_WORDS])."""
     m, k = x.shape
     n = w.shape[0]
@@ -244,6 +251,7 @@ def linear_tc_qkv(x, w_qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, bl
 
 
 SKINNY_MAX_TOKENS = 16
+CLUSTER_MAX_TOKENS = 64    # up to here a tensor-core product's weights are the 128-row operand of one tile row
 
 
 def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "plain", norm_out=None,

@@ -159,9 +159,11 @@ class Runtime:
         deferred = x if isinstance(x, DeferredNorm) else None
         takes = self.tensor_cores_take(x.dtype, w, x.shape[1])
         few = takes and x.shape[0] <= ops.SKINNY_MAX_TOKENS
-        fuses = few or (takes and self.fuses_norms(x.shape[0], w.shape[0]))   # this product can carry norms
+        # which norms this product can carry: the one before it (bit 0), the one after it (bit 1)
+        roles = 3 if few else (ops.linear_tc_norm_roles(x.shape[0], w.shape[0], x.shape[1]) if takes else 0)
+        fuses = bool(roles & 2)
         if deferred is not None:
-            if fuses:
+            if roles & 1:
                 x, norm_in = deferred.x_gamma, (deferred.bins, deferred.request.eps)
             else:
                 x, norm_in = deferred.finish(), None
@@ -193,9 +195,12 @@ class Runtime:
             ops.linear_simt(x, w, bias, out, accumulate)
 
     def fuses_norms(self, n_tokens: int, n_out: int) -> bool:
-        """Whether a bfloat16 product of ``n_tokens`` rows with ``n_out`` output features can carry the norms around
-        it: the few-token product always, the tensor-core product where it runs on pairs of SMs."""
-        return n_tokens <= ops.SKINNY_MAX_TOKENS or ops.linear_tc_fuses_norms(n_tokens, n_out)
+        """Whether the bfloat16 products of a step of ``n_tokens`` rows (``n_out`` output features) may carry the norms
+        around them: the few-token product always, the tensor-core product on pairs of SMs, and from 17 to 64
+        tokens the kernels that ``ops.linear_tc_norm_roles`` names (each product is asked when its turn comes; one
+        that cannot leaves the norm to its own kernel)."""
+        return (n_tokens <= ops.SKINNY_MAX_TOKENS or ops.linear_tc_fuses_norms(n_tokens, n_out)
+                or n_tokens <= ops.CLUSTER_MAX_TOKENS)
 
     def begin_norm_fusion(self, n_tokens: int) -> None:
         """Once per step whose products may carry norms: two sets of exact accumulators, one row each per token (16

@@ -383,6 +383,53 @@ def test_products_of_prompts_carry_the_norm_between_them(ops, m, hidden, inter):
     assert int(ws.status.item()) == 0
 
 
+@pytest.mark.parametrize("m", [17, 40, 64])
+def test_products_of_17_to_64_tokens_carry_the_norm_between_them(ops, m):
+    """With the weights as the 128-row operand a token is a column: the cluster kernel that adds into the residual
+    stream leaves residual * gamma and adds each warp's part of a token's sum of squares into the token's
+    accumulator; the cluster kernel and the kernel of whole tiles per block multiply their columns by the tokens'
+    scales (plain and gated epilogue)."""
+    g = torch.Generator().manual_seed(m)
+    hidden, inter, wide = 1024, 2816, 19200
+    act = torch.randn(m, inter, generator=g).bfloat16().to(DEV)
+    w_down = (torch.randn(hidden, inter, generator=g) * 0.1).bfloat16().to(DEV)
+    residual0 = torch.randn(m, hidden, generator=g).to(DEV)
+    gamma = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16().to(DEV)
+    eps = 1e-5
+    ws = ops.GemmWorkspace(DEV)
+    assert ops.linear_tc_norm_roles(m, hidden, inter) == 3 and ops.linear_tc_norm_roles(m, wide, hidden) == 1
+    assert ops.linear_tc_norm_roles(100, hidden, inter) == 0
+    residual = residual0.clone()
+    xg = torch.full((m, hidden), 9.0, dtype=torch.bfloat16, device=DEV)
+    bins = torch.zeros(m, ops.NORM_ROW_WORDS, dtype=torch.int64, device=DEV)
+    stale = torch.full((m, ops.NORM_ROW_WORDS), 77, dtype=torch.int64, device=DEV)
+    ops.linear_tc(act, w_down, None, residual, ws, accumulate=True, norm_out=(xg, gamma, bins, stale))
+    plain = residual0.clone()
+    ops.linear_tc(act, w_down, None, plain, ws, accumulate=True)
+    assert torch.equal(residual, plain) and int(stale.abs().max()) == 0
+    check(xg, residual * gamma.float(), 8e-3, "residual * gamma")
+    words = bins.cpu().numpy().astype(object)
+    total = np.array([float(sum(int(words[t][b]) * 2.0 ** (32 * b - 150) for b in range(8))) for t in range(m)])
+    want_ss = (residual.double() ** 2).sum(-1).cpu().numpy()
+    assert np.abs(total - want_ss).max() <= 1e-6 * want_ss.max() and int(bins[:, 8].sum()) == 0
+    again = torch.zeros_like(bins)
+    ops.linear_tc(act, w_down, None, residual0.clone(), ws, accumulate=True, norm_out=(torch.empty_like(xg), gamma, again, None))
+    assert torch.equal(again, bins)
+    normed = P.rmsnorm(residual.cpu().numpy(), gamma.float().cpu().numpy(), eps)
+    for n_out in (inter, wide):     # a cluster per tile; whole tiles per block
+        w_next = (torch.randn(n_out, hidden, generator=g) * 0.1).bfloat16().to(DEV)
+        bias = torch.randn(n_out, generator=g).to(DEV)
+        out = torch.full((m, n_out), 9.0, device=DEV)
+        ops.linear_tc(xg, w_next, bias, out, ws, norm_in=(bins, eps))
+        want = P.linear(normed, w_next.float().cpu().numpy(), bias.cpu().numpy())
+        check(out, want, 8e-3, f"consumer, plain epilogue, {n_out} features")
+        gated = torch.full((m, n_out // 2), 9.0, device=DEV)
+        ops.linear_tc(xg, w_next, None, gated, ws, epilogue="swiglu", norm_in=(bins, eps))
+        y = P.linear(normed, w_next.float().cpu().numpy()).reshape(m, -1, 2, 8)
+        check(gated, P.swiglu(y[:, :, 0].reshape(m, -1), y[:, :, 1].reshape(m, -1)), 8e-3, f"consumer, gated, {n_out}")
+    assert int(ws.status.item()) == 0
+
+
 @pytest.mark.parametrize("m", [3, 13])
 def test_products_that_start_under_their_predecessor_give_the_same_bits(ops, m):
     """A chain of few-token products, each reading what the one before wrote (with a norm carried between two of
