@@ -123,14 +123,21 @@ __device__ __forceinline__ void bins_add(unsigned long long* bins, float v) {
     if (mant) atomicAdd(bins + ee / 32, mant << (ee % 32));
 }
 
-// The sum that an accumulator holds, rounded once to float.
+// The sum that an accumulator holds, as a float: every bin is rounded to float and weighted with its power of two
+// (2^(32 b - 150), applied as two factors of 2^(16 b - 75) so that neither leaves the float range), and the eight
+// terms are added in bin order.  Eight roundings of 2^-24: the accumulators are exact so that the sum does not depend
+// on the order in which blocks add to it, not because its last bits matter (the norm's own kernel adds 4 096 squares
+// in float).  The terms do not depend on one another, which keeps this short where it stands at the end of a block:
+// an exact conversion in 64-bit floating point or in 128-bit integers cost a decode step's consumers twice as much.
 __device__ __forceinline__ float bins_total(const unsigned long long* bins) {
     if (bins[8] != 0) return __int_as_float(0x7FC00000);   // NaN
-    double s = 0.0;
+    float s = 0.0f;
 #pragma unroll
-    for (int b = 0; b < 8; ++b)   // 2^(32 b - 150), spelled as the bits of the double
-        s += (double)bins[b] * __longlong_as_double((long long)(1023 + 32 * b - 150) << 52);
-    return (float)s;
+    for (int b = 0; b < 8; ++b) {
+        const float c = __int_as_float((127 + 16 * b - 75) << 23);   // 2^(16 b - 75)
+        s += (__ull2float_rn(bins[b]) * c) * c;
+    }
+    return s;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -80,7 +80,8 @@ def linear(args) -> None:
         norm_out = (xg, gamma, bins[0].view(-1) if few else bins[0], bins[1].view(-1) if few else bins[1])
     elif args.norm == "consumer":
         bins = torch.zeros(rows, ops.NORM_ROW_WORDS, dtype=torch.int64, device=DEV)
-        bins[:, 4] = 1 << 20            # some sum of squares in every row
+        bins[:, 5] = max(1, k // 1024)  # a sum of squares of k in every row (bin 5 counts units of 2^10): scales near 1,
+        #                                 as a model's are (large ones push the gated epilogue off its fast paths)
         norm_in = (bins.view(-1) if few else bins, 1e-6)
 
     def call(w):
