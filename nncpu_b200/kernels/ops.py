@@ -8,6 +8,7 @@ checks sizes and either launches or refuses with a message.
 from __future__ import annotations
 
 import ctypes
+import functools
 from typing import Optional
 
 import torch
@@ -29,15 +30,16 @@ def _code(t: Optional[torch.Tensor]) -> int:
 
 
 def _ptr(t: Optional[torch.Tensor]):
+    # asked several times per launch (a prompt step of a few tokens is bound by the host): the usual case first
     if t is None:
-        return _vp(0)
+        return None             # a null pointer
+    if t.is_cuda and t.is_contiguous():
+        return _vp(t.data_ptr())
     if t.is_meta and _dry:
-        return _vp(0)           # a pass over shapes alone: nothing is launched, so nothing is pointed at
+        return None             # a pass over shapes alone: nothing is launched, so nothing is pointed at
     if not t.is_cuda:
         raise ExtensionError("the kernels run on the GPU: a tensor on the CPU was passed, and there is no CPU path")
-    if not t.is_contiguous():
-        raise InvalidArgument("kernels take contiguous tensors")
-    return _vp(t.data_ptr())
+    raise InvalidArgument("kernels take contiguous tensors")
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -84,15 +86,20 @@ def add_launches(n: int) -> None:
 _last_fn = ""      # the entry point that launched last (a hint for launches that can overlap with their like)
 
 
+_entry_points = {}     # (library, function) -> (the function, its library): found once
+
+
 def _call(libname: str, fn: str, *args) -> None:
     global _launches, _last_fn
-    lib = library.load(libname)
+    found = _entry_points.get((libname, fn))
+    if found is None:
+        lib = library.load(libname)
+        found = _entry_points[libname, fn] = (getattr(lib, fn), lib)
     if _dry:
         return
-    f = getattr(lib, fn)
     _last_fn = ""
-    if f(*args) != 0:
-        raise ExtensionError(lib.last_error().decode())
+    if found[0](*args) != 0:
+        raise ExtensionError(found[1].last_error().decode())
     _launches += 1
     _last_fn = fn
 
@@ -107,8 +114,7 @@ def launch_overlap(on: bool) -> None:
         getattr(library.load(name), f"nncpu_launch_overlap_{name}")(ctypes.c_int(1 if on else 0))
 
 
-def _i(v) -> ctypes.c_int:
-    return ctypes.c_int(int(v))
+_i = int      # a C int: ctypes passes a Python int as one (sizes, counts, flags, type codes; booleans become 0 or 1)
 
 
 def _f(v) -> ctypes.c_float:
@@ -166,12 +172,14 @@ PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4}
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 
+@functools.lru_cache(maxsize=4096)
 def linear_tc_fuses_norms(m: int, n: int) -> bool:
     """Whether the tensor-core product of ``m`` tokens with ``n`` output features can carry the norms around it
     (``linear_tc``'s ``norm_out`` and ``norm_in``): the products of whole prompts."""
     return bool(library.load("gemm_sm100").nncpu_linear_tc_fuses_norms(m, n))
 
 
+@functools.lru_cache(maxsize=4096)
 def linear_tc_norm_roles(m: int, n: int, k: int) -> int:
     """Which norms the tensor-core product of ``m`` tokens, ``n`` output features and width ``k`` can carry: bit 0 the
     norm before it (``norm_in``), bit 1 the norm after it (``norm_out``).  Whole prompts both; 17 to 64 tokens the
