@@ -154,6 +154,11 @@ class Cache:
                 None if st is None else torch.zeros((self.n_slots + 1, *st.shape), dtype=st.dtype, device=self.device)
                 for _, st in requests]
 
+    @property
+    def has_state(self) -> bool:
+        """Whether some part keeps per-sequence state of fixed size beside the keys and values."""
+        return any(s is not None for s in self.states)
+
     # -- slots ---------------------------------------------------------------
 
     def alloc_slot(self) -> int:

@@ -1,4 +1,4 @@
-"""Decode steps as CUDA graphs.
+"""Decode steps, and the short prompt steps of one sequence, as CUDA graphs.
 
 A decode step is launch-bound when run kernel by kernel: a few hundred small
 launches per token.  For every batch size (rounded up to a power of two) the
@@ -190,14 +190,140 @@ class DecodeGraph:
         return self.logits[:len(slots)]
 
 
+PROMPT_GRAPH_MIN = 16     # the smallest padded size of a captured prompt step
+PROMPT_GRAPH_MAX = 256    # longer prompts keep the device busy about as long as the host needs to launch them (measured at
+#                           the 8B sizes, a layer: 17 tokens 223 -> 142 us, 64: 197 -> 153, 128: 217 -> 179, 256: 255 -> 233;
+#                           300 tokens padded to 512 would take 311 us against 301 launched kernel by kernel)
+
+
+class PromptGraph:
+    """Static buffers and the captured step of ONE sequence that brings up to ``size`` new tokens and wants the
+    logits of its last one: the step that a chat turn, or a single short prompt, begins with.  Launched kernel by
+    kernel from Python such a step of a few dozen tokens is bound by the host (some 17 us a launch); captured for
+    its padded size (a power of two from 16 to 256) it is one launch.  The tokens beyond the prompt's own are padding: they belong to
+    no sequence (index -1), so nothing is written to the cache for them, attention leaves them out, and what the
+    products compute in their rows is never read."""
+
+    def __init__(self, engine, size: int):
+        self._engine, self.size = weakref.ref(engine), size
+        cache = engine.cache
+        dev = cache.device
+        self.width = pages_for(cache.max_seq_len)
+        n_groups = len(cache.groups)
+        T = size
+        # layout of the metadata block (int32): tok_seq, tok_pos, the slot, cu_seqlens, the wanted row, page tables
+        self.o_seq, self.o_pos, self.o_slot, self.o_cu, self.o_row = 0, T, 2 * T, 2 * T + 1, 2 * T + 3
+        self.o_tables = [2 * T + 4 + g * self.width for g in range(n_groups)]
+        self.n_meta = 2 * T + 4 + n_groups * self.width
+        self.meta = torch.zeros(self.n_meta, dtype=torch.int32, device=dev)
+        self.tok_ids = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.host = [torch.zeros(self.n_meta, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.host_np = [h.numpy() for h in self.host]
+        self.tok_host = [torch.zeros(T, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * _RING
+        self.turn = 0
+        m = self.meta
+        self.ctx = StepContext(
+            n_tokens=T, n_seqs=1, n_wanted=1, tok_ids=self.tok_ids, tok_seq=m[self.o_seq:self.o_seq + T],
+            tok_pos=m[self.o_pos:self.o_pos + T], seq_slots=m[self.o_slot:self.o_slot + 1],
+            cu_seqlens=m[self.o_cu:self.o_cu + 2], logit_rows=m[self.o_row:self.o_row + 1],
+            block_tables=[m[o:o + self.width].view(1, self.width) for o in self.o_tables],
+            q_lens=[T], kv_lens=[T], is_decode=False, max_kv_len=cache.max_seq_len)
+        self.logits: Optional[torch.Tensor] = None
+        self.arena = Arena(dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.n_kernels = 0
+        self.h2d_bytes = 0
+
+    @property
+    def engine(self):
+        return self._engine()
+
+    def _fill(self, slot: int, tokens: Sequence[int]) -> None:
+        cache, T, n = self.engine.cache, self.size, len(tokens)
+        i = self.turn = (self.turn + 1) % _RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        a = self.host_np[i]
+        start = cache.lengths[slot]
+        a[:] = -1
+        a[self.o_seq:self.o_seq + n] = 0
+        a[self.o_pos:self.o_pos + T] = 0
+        a[self.o_pos:self.o_pos + n] = np.arange(start, start + n)
+        a[self.o_slot] = slot
+        a[self.o_cu:self.o_cu + 2] = (0, n)
+        a[self.o_row] = n - 1
+        for g, group in enumerate(cache.groups):
+            table = group.tables[slot]
+            a[self.o_tables[g]:self.o_tables[g] + len(table)] = table
+        self.meta.copy_(self.host[i], non_blocking=True)
+        th = self.tok_host[i]
+        th[:n] = torch.as_tensor(tokens, dtype=torch.int32)
+        th[n:] = 0
+        self.tok_ids.copy_(th, non_blocking=True)
+        self.h2d_bytes = (self.n_meta + T) * 4
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+    def _forward(self) -> None:
+        with self.engine.model.rt.using(self.arena):
+            self.arena.begin()
+            self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
+
+    def run(self, slot: int, tokens: Sequence[int]) -> torch.Tensor:
+        """The step: ``tokens`` appended to the sequence in ``slot``.  Returns float32 logits [1, vocab] of the last
+        token, valid until the next step."""
+        with perf.paused():
+            self.ctx.memo.clear()
+            self._fill(slot, tokens)
+            if self.graph is None:
+                # as for decode steps: the first step of this size runs kernel by kernel and is the step's result;
+                # the same work is then captured, not run
+                self._forward()
+                eager = self.logits
+                self.arena.begin()
+                self.arena.frozen = True
+                before = ops.launch_count()
+                g = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize()
+                self.ctx.memo.clear()
+                gc.collect()
+                gc_was_on = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                        self._forward()
+                finally:
+                    if gc_was_on:
+                        gc.enable()
+                self.n_kernels = ops.launch_count() - before
+                ops.add_launches(-self.n_kernels)
+                self.graph = g
+                self.logits.copy_(eager)
+            else:
+                self.graph.replay()
+                ops.add_launches(self.n_kernels)
+            return self.logits
+
+
 class DecodeGraphs:
     def __init__(self, engine):
         self._engine = weakref.ref(engine)
         self.by_size: Dict[int, DecodeGraph] = {}
+        self.prompts: Dict[int, PromptGraph] = {}
 
     def get(self, n: int) -> DecodeGraph:
         size = bucket(n)
         g = self.by_size.get(size)
         if g is None:
             g = self.by_size[size] = DecodeGraph(self._engine(), size)
+        return g
+
+    def prompt(self, n: int) -> PromptGraph:
+        """The captured step of one sequence with ``n`` new tokens (2 <= n <= PROMPT_GRAPH_MAX)."""
+        size = max(PROMPT_GRAPH_MIN, bucket(n))
+        g = self.prompts.get(size)
+        if g is None:
+            g = self.prompts[size] = PromptGraph(self._engine(), size)
         return g

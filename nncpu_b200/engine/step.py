@@ -172,7 +172,8 @@ class Engine:
     def __init__(self, model, max_tokens: int, n_slots: Optional[int] = None, max_seq_len: Optional[int] = None,
                  kv_dtype: Optional[torch.dtype] = None, use_graphs: bool = True,
                  max_step_tokens: Optional[int] = None):
-        from .decode_graph import DecodeGraphs
+        from .decode_graph import PROMPT_GRAPH_MAX, DecodeGraphs
+        self._prompt_graph_max = PROMPT_GRAPH_MAX
         self.model = model
         self.graphs = DecodeGraphs(self) if use_graphs else None
         self._last_graph = None   # the graph of the last step, if that step ran through one
@@ -275,6 +276,20 @@ class Engine:
             self._last_graph = g
             return logits
         self._last_graph = None
+        if (self.graphs is not None and not perf.enabled() and len(slots) == 1
+                and 1 < len(tokens[0]) <= self._prompt_graph_max and list(want[0]) == [len(tokens[0]) - 1]
+                and not self.cache.has_state):
+            # one sequence's short prompt (a chat turn): one captured launch instead of a host-bound string of them
+            try:
+                with translating_oom(f"a prompt step of {len(tokens[0])} tokens"):
+                    g = self.graphs.prompt(len(tokens[0]))
+                    logits = g.run(slots[0], tokens[0])
+            except BaseException:
+                self.cache.rollback(slots)
+                raise
+            self.h2d_bytes_last_step = g.h2d_bytes
+            self.cache.commit(slots, [len(tokens[0])])
+            return logits
         try:
             with translating_oom(f"a step of {sum(len(t) for t in tokens)} tokens in {len(slots)} sequences"), \
                     self.model.rt.using(self.arena):

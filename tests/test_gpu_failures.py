@@ -79,7 +79,11 @@ def test_no_room_on_the_device_is_out_of_memory_with_the_sizes(tmp_path):
         raise torch.OutOfMemoryError("CUDA out of memory. Tried to allocate 20.00 GiB. GPU 0 has ...")
     model.forward = no_room
     try:
-        with pytest.raises(OutOfMemory, match="a step of 200 tokens in 1 sequences.*Tried to allocate 20.00 GiB"):
+        with pytest.raises(OutOfMemory, match="a step of 300 tokens in 1 sequences.*Tried to allocate 20.00 GiB"):
+            engine.step([s], [[i % 200 for i in range(300)]])
+        assert engine.cache.length(s) == 3 and engine.cache.groups[0].pool.n_free == pages
+        # the same through the captured form of one sequence's short prompt step
+        with pytest.raises(OutOfMemory, match="a prompt step of 200 tokens.*Tried to allocate 20.00 GiB"):
             engine.step([s], [list(range(200))])
     finally:
         model.forward = real

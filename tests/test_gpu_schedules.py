@@ -68,6 +68,42 @@ def test_decoders_and_a_newcomers_prompt_in_one_step(folders, name, dtype):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", "BEG")
+def test_one_sequences_short_prompt_steps_run_as_captured_graphs(folders, name, dtype):
+    """A step in which one sequence brings 2 to 256 tokens and wants its last logits is captured for its padded
+    size and replayed: the first step of a size (run kernel by kernel, then captured), a replay for another
+    sequence of another length in the same size, and a second turn on a sequence that is under way (positions
+    that do not start at 0, keys from earlier turns) all give the plain model's logits; the cache's books stay
+    right; and a step that wants other places, or runs with graphs off, takes the ordinary way to the same logits."""
+    plain = PlainQwen3(folders[name, dtype])
+    model = Model.load(folders[name, dtype], dtype=dtype)
+    engine = Engine(model, max_tokens=64 * 40)
+    plain_engine = Engine(model, max_tokens=64 * 12, use_graphs=False)
+    sizes_seen = set()
+    for k, (first, second) in enumerate([(2, 30), (5, 3), (17, 100), (33, 31), (100, 17), (300, 212), (512, 40), (20, 9)]):
+        seq = toks(plain, first + second, 11 * k + first)
+        want = plain.logits(seq, rows=[first - 1, first + second - 1])
+        s = engine.alloc_slot()
+        got = [engine.step([s], [seq[:first]]).clone()]              # a fresh sequence
+        got.append(engine.step([s], [seq[first:]]).clone())            # its second turn, on top of the first
+        check(torch.cat(got), want, TOL[dtype], f"{first} tokens, then {second} more")
+        engine.free_slot(s)
+        engine.cache.check()
+        sizes_seen.update(g for g in engine.graphs.prompts)
+        if first == 100:                                               # the ordinary way: other places wanted, or no graphs
+            s = engine.alloc_slot()
+            some = engine.step([s], [seq[:first]], want=[[0, first - 1]]).clone()
+            check(some[1:], want[:1], TOL[dtype], "two places wanted")
+            engine.free_slot(s)
+            p = plain_engine.alloc_slot()
+            check(plain_engine.step([p], [seq[:first]]).clone(), want[:1], TOL[dtype], "graphs off")
+            plain_engine.free_slot(p)
+    assert sizes_seen == {16, 32, 64, 128, 256}         # 300 and 512 tokens took the ordinary way
+    assert all(g.graph is not None for g in engine.graphs.prompts.values())
+    model.rt.check_status()
+
+
 @pytest.mark.parametrize("dtype,n_prompt", [("bfloat16", 3000), ("float32", 700)])
 def test_long_context_decode_inside_a_graph(folders, dtype, n_prompt):
     """An engine sized for 8 192 tokens: one sequence's decode step cuts its keys into more splits than merge
@@ -152,7 +188,8 @@ def test_evaluated_logits_outlive_a_generate_call(folders, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_a_step_asks_the_allocator_for_nothing(folders, dtype):
     """The engine's arena is sized when the engine is made; 50 steps of every kind (prompts of unequal lengths,
-    mixed steps, decode steps through graphs after their first) then leave the allocator's counters alone."""
+    mixed steps, decode steps and one sequence's short prompts through graphs after their first) then leave the
+    allocator's counters alone."""
     plain = PlainQwen3(folders["G", dtype])
     model = Model.load(folders["G", dtype], dtype=dtype)
     engine = Engine(model, max_tokens=64 * 40, max_step_tokens=2000)
@@ -194,6 +231,10 @@ def test_a_step_asks_the_allocator_for_nothing(folders, dtype):
         engine.step(slots, [[4]] * b)
         for s in slots:
             engine.free_slot(s)
+    for n in (3, 40, 200):                                 # ... and every size of one sequence's short prompt step
+        s = engine.alloc_slot()
+        engine.step([s], [toks(plain, n, n)])
+        engine.free_slot(s)
     torch.cuda.synchronize()
     before = torch.cuda.memory_stats()["allocation.all.allocated"]
     capacity = engine.arena.capacity
