@@ -407,10 +407,13 @@ def main() -> int:
         tok_s, ms_step, bytes_step, key_range, phases = run_decode_point(model, cfg, BATCH, args.steps, args.warmup,
                                                                           with_phases=True)
     launches = ops.launch_count() - launches0
-    points = {}
+    points, points_frac = {}, {}
     if not args.skip_points:
-        points["decode_b1"] = run_decode_point(model, cfg, 1, args.steps, args.warmup)[0]
-        points["decode_b64"] = run_decode_point(model, cfg, 64, args.steps, args.warmup)[0]
+        for name, batch in (("decode_b1", 1), ("decode_b64", 64)):
+            point = run_decode_point(model, cfg, batch, args.steps, args.warmup)
+            points[name] = point[0]
+            # the same roofline as the headline's: used weights once and the live requests' cache, over the step's time
+            points_frac[name] = round(point[2] / (point[1] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
     e2e = run_e2e(model, cfg, args.steps, args.warmup)
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     line = {
@@ -434,6 +437,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,
+        "points_roofline_frac": points_frac,
         "phases": {"unit": "ms per decode step, kernel by kernel under the phase profiler (not the graph)",
                    **(phases or {})},
         "prefill_batched": {"tokens": BATCH * PROMPT, "ms": e2e["prefill_s"] * 1e3,
