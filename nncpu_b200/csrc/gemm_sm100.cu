@@ -413,14 +413,21 @@ __device__ __forceinline__ int streamk_owner(long u, long units, int blocks) {
     return c;
 }
 
-template <int BN, int kStages, int kEpi>
+// kTM: tiles of 128 A rows that a unit holds.  With two, a k-block of B is copied to shared memory once for 256 rows
+// of A: where B (the tokens, with swapped operands) is as large as a tile of A, the copies into shared memory are
+// what a block waits for, and a quarter of them goes away.
+template <int BN, int kStages, int kEpi, int kTM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
-    constexpr int kBytesA = kBlockM * kBlockK * 2;
+    constexpr int kBytesA1 = kBlockM * kBlockK * 2;
+    constexpr int kBytesA = kTM * kBytesA1;
     constexpr int kBytesB = BN * kBlockK * 2;
-    constexpr int kAccCols = BN < 32 ? 32 : BN;
-    constexpr int kTmemCols = 2 * kAccCols;
+    constexpr int kTileCols = BN < 32 ? 32 : BN;
+    constexpr int kAccCols = kTM * kTileCols;
+    constexpr int kAccBufs = 2 * kAccCols <= 512 ? 2 : 1;   // two accumulators where tensor memory has room for them
+    constexpr int kTmemCols = kAccBufs * kAccCols;
+    static_assert(kTmemCols <= 512, "the accumulators fit tensor memory");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
@@ -478,7 +485,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (long u = u_begin; u < u_end && ok;) {
                 const Segment sg = segment_at(u);
-                const int m0 = (sg.tile % p.tiles_a) * kBlockM, n0 = (sg.tile / p.tiles_a) * BN;
+                const int m0 = (sg.tile % p.tiles_a) * (kTM * kBlockM), n0 = (sg.tile / p.tiles_a) * BN;
                 for (int kb = sg.kb0; kb < sg.kb0 + sg.len; ++kb, ++kb_run) {
                     const int s = kb_run % kStages;
                     if (!mbar_wait(&empty[s], ((kb_run / kStages) & 1) ^ 1)) {
@@ -487,7 +494,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         break;
                     }
                     mbar_expect_tx(&full[s], kBytesA + kBytesB);
-                    tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                    // (rows past the end of A are filled with zeros and counted like the others)
+#pragma unroll
+                    for (int sub = 0; sub < kTM; ++sub)
+                        tma_load_2d(smem_a + s * kBytesA + sub * kBytesA1, &map_a, &full[s], kb * kBlockK,
+                                    m0 + sub * kBlockM);
                     tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                     issued = kb_run + 1;
                 }
@@ -505,8 +516,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (long u = u_begin; u < u_end && ok; ++it) {
                 const Segment sg = segment_at(u);
-                const int buf = it & 1;
-                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1)) {
+                const int buf = it % kAccBufs;
+                if (!mbar_wait(&acc_empty[buf], ((it / kAccBufs) & 1) ^ 1)) {
                     atomicExch(p.status, kTimeoutAccumEmpty);
                     break;
                 }
@@ -524,8 +535,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t b_addr = smem_u32(smem_b + s * kBytesB);
 #pragma unroll
                     for (int k = 0; k < kBlockK / kUmmaK; ++k)
-                        umma_bf16(tmem_d, smem_desc_sw128(a_addr + k * kUmmaK * 2), smem_desc_sw128(b_addr + k * kUmmaK * 2),
-                                  idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int sub = 0; sub < kTM; ++sub)
+                            umma_bf16(tmem_d + (uint32_t)(sub * kTileCols),
+                                      smem_desc_sw128(a_addr + sub * kBytesA1 + k * kUmmaK * 2),
+                                      smem_desc_sw128(b_addr + k * kUmmaK * 2), idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
                     umma_commit(&empty[s]);
                 }
                 if (ok) umma_commit(&acc_full[buf]);
@@ -540,10 +554,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (long u = u_begin; u < u_end; ++it) {
             const Segment sg = segment_at(u);
             u += sg.len;
-            const int m0 = (sg.tile % p.tiles_a) * kBlockM, n0 = (sg.tile / p.tiles_a) * BN;
-            const int a_row = m0 + row_in_tile;
-            const int buf = it & 1;
-            const bool ok = mbar_wait(&acc_full[buf], (it >> 1) & 1);
+            const int m0 = (sg.tile % p.tiles_a) * (kTM * kBlockM), n0 = (sg.tile / p.tiles_a) * BN;
+            const int buf = it % kAccBufs;
+            const bool ok = mbar_wait(&acc_full[buf], (it / kAccBufs) & 1);
             if (!ok && lane == 0) atomicExch(p.status, kTimeoutAccumFull);
             __syncwarp();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -552,10 +565,13 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // the whole tile is this block's
                 if (!ok) break;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + (uint32_t)c0, v);
-                    store16<kEpi>(p, a_row, n0 + c0, v);
+                for (int sub = 0; sub < kTM; ++sub) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        tmem_ld16(taddr + (uint32_t)(sub * kTileCols + c0), v);
+                        store16<kEpi>(p, m0 + sub * kBlockM + row_in_tile, n0 + c0, v);
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -566,13 +582,16 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // block's first segment does; 1: it starts with the tile), column by column so that a warp writes
             // 128 contiguous bytes.  The kernel that follows puts the tile together.
             if (!ok) break;
-            float* mine = p.scratch + ((size_t)blockIdx.x * 2 + (sg.kb0 > 0 ? 0 : 1)) * ((size_t)BN * kBlockM);
+            float* mine = p.scratch + ((size_t)blockIdx.x * 2 + (sg.kb0 > 0 ? 0 : 1)) * ((size_t)kTM * BN * kBlockM);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                tmem_ld16(taddr + (uint32_t)c0, v);
+            for (int sub = 0; sub < kTM; ++sub) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + (uint32_t)(sub * kTileCols + c0), v);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) mine[(c0 + j) * kBlockM + row_in_tile] = v[j];
+                    for (int j = 0; j < 16; ++j) mine[(sub * BN + c0 + j) * kBlockM + row_in_tile] = v[j];
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -591,18 +610,18 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // Puts together the tiles that gemm_streamk_kernel left in parts: block (tile, 16 columns), thread = row of the
 // tile.  The parts of a tile are added in block order, which is the order of k, with all loads in flight at
 // once; then the same epilogue as everywhere.  `blocks` is the grid the product ran with.
-template <int BN, int kEpi>
+template <int BN, int kEpi, int kTM>
 __global__ void __launch_bounds__(kBlockM)
 gemm_streamk_fixup_kernel(const GemmParams p, int blocks) {
-    const int tile = blockIdx.x, c0 = blockIdx.y * 16;
+    const int tile = blockIdx.x, sub = blockIdx.z, c0 = sub * BN + blockIdx.y * 16;   // c0: the column within a slot
     const long units = (long)p.tiles_a * p.tiles_b * p.kb_total;
     const long t_begin = (long)tile * p.kb_total;
     const int c_first = streamk_owner(t_begin, units, blocks);
     const int c_last = streamk_owner(t_begin + p.kb_total - 1, units, blocks);
     if (c_first == c_last) return;   // one block had the whole tile and stored it
     const int row_in_tile = threadIdx.x;
-    const int m0 = (tile % p.tiles_a) * kBlockM, n0 = (tile / p.tiles_a) * BN;
-    const size_t slot_floats = (size_t)BN * kBlockM;
+    const int m0 = (tile % p.tiles_a) * (kTM * kBlockM) + sub * kBlockM, n0 = (tile / p.tiles_a) * BN;
+    const size_t slot_floats = (size_t)kTM * BN * kBlockM;
     float v[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
@@ -626,7 +645,7 @@ gemm_streamk_fixup_kernel(const GemmParams p, int blocks) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] += __ldcg(a + j * kBlockM);
     }
-    store16<kEpi>(p, m0 + row_in_tile, n0 + c0, v);
+    store16<kEpi>(p, m0 + row_in_tile, n0 + (int)blockIdx.y * 16, v);
 }
 
 // ---------------------------------------------------------------------------
@@ -1379,12 +1398,13 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int bloc
     return 0;
 }
 
-template <int BN, int kStages, int kEpi>
+template <int BN, int kStages, int kEpi, int kTM = 1>
 int launch_streamk(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
-    constexpr size_t smem = smem_bytes<BN, kStages>();
+    constexpr size_t smem = smem_bytes<BN, kStages>() + (size_t)kStages * (kTM - 1) * (kBlockM * kBlockK * 2);
+    static_assert(smem <= 227 * 1024, "the stages fit shared memory");
     static bool configured[64] = {};
     if (first_use_on_this_device(configured)) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_streamk_kernel<BN, kStages, kEpi>,
+        const cudaError_t e = cudaFuncSetAttribute(gemm_streamk_kernel<BN, kStages, kEpi, kTM>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         NN_CHECK(e == cudaSuccess, "gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
@@ -1401,12 +1421,12 @@ int launch_streamk(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, 
     cudaLaunchAttribute attr[1];
     cfg.attrs = attr;
     cfg.numAttrs = overlap_attribute(attr);
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_streamk_kernel<BN, kStages, kEpi>, ma, mb, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_streamk_kernel<BN, kStages, kEpi, kTM>, ma, mb, p);
     NN_CHECK(e == cudaSuccess, "gemm (stream-K): launch failed: %s", cudaGetErrorString(e));
     if (units % grid != 0 || (units / grid) % p.kb_total != 0) {
         // some tile is shared between blocks
-        gemm_streamk_fixup_kernel<BN, kEpi><<<dim3((unsigned)(p.tiles_a * p.tiles_b), BN / 16), kBlockM, 0, stream>>>(
-            p, (int)grid);
+        gemm_streamk_fixup_kernel<BN, kEpi, kTM>
+            <<<dim3((unsigned)(p.tiles_a * p.tiles_b), BN / 16, kTM), kBlockM, 0, stream>>>(p, (int)grid);
         NN_LAUNCH_OK("gemm_streamk_fixup");
     }
     return 0;
@@ -1421,6 +1441,13 @@ int dispatch_streamk(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmP
         case 128: return launch_streamk<128, 6, kEpi>(ma, mb, p, stream);
         default: return launch_streamk<256, 4, kEpi>(ma, mb, p, stream);
     }
+}
+
+// The same with 256 rows of A per unit (p.tiles_a counts those).
+template <int kEpi>
+int dispatch_streamk_wide(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
+    if (bn == 128) return launch_streamk<128, 4, kEpi, 2>(ma, mb, p, stream);
+    return launch_streamk<256, 3, kEpi, 2>(ma, mb, p, stream);
 }
 
 template <int BN, int kStages, int kEpi>
@@ -1509,7 +1536,7 @@ extern "C" int nncpu_linear_tc_supported(int M, int N, int K, int lda) {
 }
 
 // Floats of scratch a workspace must hold for any product this library launches.
-extern "C" long nncpu_linear_tc_scratch_floats() { return 10l << 20; }  // 40 MiB: two partial tiles of 256 x 128 per SM
+extern "C" long nncpu_linear_tc_scratch_floats() { return 20l << 20; }  // 80 MiB: two partial units of 2 x 256 x 128 per SM
 
 // The q/k/v projection of a prompt with its epilogue fused: X[M, K] . W[(n_heads + 2 n_kv) * 128, K]^T, then per
 // head the RMS norm (q and k, if their weights are given), the rotation (if cos_sin is given) and the stores:
@@ -1595,8 +1622,9 @@ extern "C" int nncpu_linear_tc_wait_probe(const void* X, const void* W, float* o
 // `plan` chooses among the kernels where a measurement or a test wants another one than the sizes would get:
 // 0 the default (products of 512 or more tokens on pairs of SMs with 256 x 256 tiles; 65 to 256 tokens with their
 // k-blocks dealt out evenly over the SMs; 17 to 64 tokens a cluster per output tile); kPlanEvenFrom17: dealt out
-// evenly from 17 tokens on; kPlanNeverEven: never dealt out evenly; kPlanNoPairs: one SM per 128 x 256 tile.
-enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4 };
+// evenly from 17 tokens on; kPlanNeverEven: never dealt out evenly; kPlanNoPairs: one SM per 128 x 256 tile;
+// kPlanNarrowUnits: units of 128 weight rows where 256 would be taken.
+enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4, kPlanNarrowUnits = 8 };
 
 //
 // The norms around a product of whole prompts can ride on it as they do on the few-token products (linear_skinny.cu),
@@ -1714,6 +1742,16 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
     if ((even_swap || even_plain) && streamk_mode && scratch != nullptr &&
         2l * sm_count() * bn * kBlockM <= nncpu_linear_tc_scratch_floats()) {
         p.splits = 1;
+        // 65 to 256 tokens: a k-block of the tokens is as large as a tile of the weights or twice that, so units of
+        // 256 weight rows, which copy it once for two tiles.  Only with tiles for every SM: below that every unit is
+        // left in parts, and parts of twice the size cost more than the copies save (measured at 128 tokens on the
+        // Qwen3-8B layer sizes: 24 576 rows 57.6 -> 55.5 us, at 256 tokens 78.0 -> 71.5; 4 096 rows 18.3 -> 23.2 us)
+        if (p.swap && bn >= 128 && n_tiles >= sm_count() && !(plan & kPlanNarrowUnits) &&
+            4l * sm_count() * bn * kBlockM <= nncpu_linear_tc_scratch_floats()) {
+            p.tiles_a = (p.rows_a + 2 * kBlockM - 1) / (2 * kBlockM);
+            return epilogue == kSwiglu ? dispatch_streamk_wide<kSwiglu>(bn, ma, mb, p, stream)
+                                       : dispatch_streamk_wide<kPlain>(bn, ma, mb, p, stream);
+        }
         return epilogue == kSwiglu ? dispatch_streamk<kSwiglu>(bn, ma, mb, p, stream)
                                    : dispatch_streamk<kPlain>(bn, ma, mb, p, stream);
     }

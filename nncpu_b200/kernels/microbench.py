@@ -88,7 +88,8 @@ def linear(args) -> None:
         if few:
             ops.linear_skinny(x, w, None, out, args.accumulate, args.epilogue, norm_out, norm_in)
         else:
-            ops.linear_tc(x, w, None, out, work, args.accumulate, args.epilogue, norm_out=norm_out, norm_in=norm_in)
+            ops.linear_tc(x, w, None, out, work, args.accumulate, args.epilogue, plan=args.plan, norm_out=norm_out,
+                          norm_in=norm_in)
     ms = _time([lambda w=w: call(w) for w in ws], args.once)
     print(f"linear M={m} N={n} K={k} epilogue={args.epilogue}{' norm ' + args.norm if args.norm else ''}: {ms * 1e3:.1f} us, "
           f"{n * k * 2 / ms / 1e6:.0f} GB/s of weights, {2 * m * n * k / ms / 1e9:.1f} TFLOP/s")
@@ -198,6 +199,7 @@ def main(argv=None) -> int:
     p.add_argument("--epilogue", default="plain", choices=["plain", "swiglu"])
     p.add_argument("--accumulate", action="store_true")
     p.add_argument("--tensor-cores", action="store_true", help="up to 16 tokens too on the tcgen05 kernels")
+    p.add_argument("--plan", default="auto", choices=sorted(ops.PLANS), help="another tcgen05 kernel than the sizes' own")
     p.add_argument("--warps", type=int, default=0, choices=[0, 4, 8],
                    help="few tokens: blocks of 8 or of 4 warps (0: chosen by the sizes)")
     p.add_argument("--norm", choices=["producer", "consumer"],

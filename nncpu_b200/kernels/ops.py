@@ -167,7 +167,7 @@ class GemmWorkspace:
 
 
 # Which kernel a tensor-core product runs with, where a measurement or a test wants another than its sizes would get.
-PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4}
+PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4, "narrow_units": 8}
 
 EPILOGUES = {"plain": 0, "swiglu": 1}
 

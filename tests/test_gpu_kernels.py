@@ -120,19 +120,21 @@ def test_linear_tensor_core_with_gated_epilogue(ops, m, inter, k):
     assert int(ws.status.item()) == 0
 
 
+@pytest.mark.parametrize("plan", ["even_from_17", "narrow_units"])
 @pytest.mark.parametrize("m,n,k", [(20, 1000, 1096), (40, 25600, 512), (70, 640, 4096), (100, 25000, 264),
-                                   (130, 4096, 1024), (256, 19000, 520), (200, 128, 8192)])
-def test_linear_tensor_core_with_work_cut_evenly(ops, m, n, k):
+                                   (130, 4096, 1024), (256, 19000, 520), (200, 128, 8192), (128, 300, 2048),
+                                   (65, 12288, 4096)])
+def test_linear_tensor_core_with_work_cut_evenly(ops, m, n, k, plan):
     """17 to 256 tokens with the k-blocks of all tiles dealt out evenly to the blocks: fewer tiles than SMs
     (every tile in parts), more tiles than SMs (whole tiles and parts), one tile, every epilogue; twice, and
-    the runs agree bit for bit."""
+    the runs agree bit for bit.  From 65 tokens on a unit holds 256 weight rows (two tiles that share the tokens'
+    k-block; the last may be short of rows or lack its second tile), with "narrow_units" 128 as below that."""
     g = torch.Generator().manual_seed(m + n + k)
     x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
     w = (torch.randn(n, k, generator=g) * 0.1).bfloat16().to(DEV)
     b = torch.randn(n, generator=g).to(DEV)
     ws = ops.GemmWorkspace(DEV)
     want = (x.double() @ w.double().T).float()
-    plan = "even_from_17"
     out = torch.full((m, n), 9.0, device=DEV)
     ops.linear_tc(x, w, b, out, ws, plan=plan)
     check(out, want + b, 1e-5, "float32 out with bias")
