@@ -123,7 +123,7 @@ def test_linear_tensor_core_with_gated_epilogue(ops, m, inter, k):
 @pytest.mark.parametrize("plan", ["even_from_17", "narrow_units"])
 @pytest.mark.parametrize("m,n,k", [(20, 1000, 1096), (40, 25600, 512), (70, 640, 4096), (100, 25000, 264),
                                    (130, 4096, 1024), (256, 19000, 520), (200, 128, 8192), (128, 300, 2048),
-                                   (65, 12288, 4096)])
+                                   (65, 12288, 4096), (100, 25600, 264), (200, 19008, 520)])
 def test_linear_tensor_core_with_work_cut_evenly(ops, m, n, k, plan):
     """17 to 256 tokens with the k-blocks of all tiles dealt out evenly to the blocks: fewer tiles than SMs
     (every tile in parts), more tiles than SMs (whole tiles and parts), one tile, every epilogue; twice, and
