@@ -614,6 +614,8 @@ template <int BN, int kEpi, int kTM>
 __global__ void __launch_bounds__(kBlockM)
 gemm_streamk_fixup_kernel(const GemmParams p, int blocks) {
     const int tile = blockIdx.x, sub = blockIdx.z, c0 = sub * BN + blockIdx.y * 16;   // c0: the column within a slot
+    // launched to start under the end of the product, whose parts it may read only once that kernel is complete
+    let_next_kernel_start();
     const long units = (long)p.tiles_a * p.tiles_b * p.kb_total;
     const long t_begin = (long)tile * p.kb_total;
     const int c_first = streamk_owner(t_begin, units, blocks);
@@ -625,6 +627,7 @@ gemm_streamk_fixup_kernel(const GemmParams p, int blocks) {
     float v[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+    wait_for_previous_kernels();
     int c = c_first;
     for (; c + 1 <= c_last; c += 2) {
         const int s0 = streamk_start(c, units, blocks) > t_begin ? 0 : 1;
@@ -1425,9 +1428,15 @@ int launch_streamk(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, 
     NN_CHECK(e == cudaSuccess, "gemm (stream-K): launch failed: %s", cudaGetErrorString(e));
     if (units % grid != 0 || (units / grid) % p.kb_total != 0) {
         // some tile is shared between blocks
-        gemm_streamk_fixup_kernel<BN, kEpi, kTM>
-            <<<dim3((unsigned)(p.tiles_a * p.tiles_b), BN / 16, kTM), kBlockM, 0, stream>>>(p, (int)grid);
-        NN_LAUNCH_OK("gemm_streamk_fixup");
+        cudaLaunchConfig_t fix = {};
+        fix.gridDim = dim3((unsigned)(p.tiles_a * p.tiles_b), BN / 16, kTM);
+        fix.blockDim = dim3(kBlockM);
+        fix.stream = stream;
+        cudaLaunchAttribute fix_attr[1];
+        fix.attrs = fix_attr;
+        fix.numAttrs = overlap_attribute(fix_attr);
+        const cudaError_t e2 = cudaLaunchKernelEx(&fix, gemm_streamk_fixup_kernel<BN, kEpi, kTM>, p, (int)grid);
+        NN_CHECK(e2 == cudaSuccess, "gemm (stream-K, adding the parts): launch failed: %s", cudaGetErrorString(e2));
     }
     return 0;
 }
