@@ -9,7 +9,6 @@ are wanted, the final norm and the vocabulary projection
 """
 from __future__ import annotations
 
-from pathlib import Path
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -18,7 +17,7 @@ from ..cache import KVRequest, StateRequest
 from ..config import ModelSpec, load_config
 from ..errors import BadFormat, InvalidArgument, translating_oom
 from ..kernels import ops
-from ..parts import EntryCache, Runtime, build
+from ..parts import Runtime, build
 from ..weights import ParamSpec, load_tensors, random_tensors_on_device
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,

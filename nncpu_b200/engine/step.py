@@ -18,7 +18,7 @@ import torch
 
 from .. import perf
 from ..cache import Cache, pages_for
-from ..errors import ContextFull, InvalidArgument, translating_oom
+from ..errors import InvalidArgument, translating_oom
 from ..kernels import ops
 from ..parts import EntryCache
 from ..parts.runtime import Arena

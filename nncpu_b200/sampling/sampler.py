@@ -25,7 +25,6 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
-import numpy as np
 import torch
 
 from .. import perf

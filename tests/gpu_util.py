@@ -4,7 +4,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from nncpu_b200.cache import PAGE, Cache
+from nncpu_b200.cache import PAGE
 
 DEV = "cuda:0"
 # Largest difference allowed, as a fraction of the largest reference value.

@@ -3,7 +3,7 @@ import json
 
 import pytest
 
-from nncpu_b200.config import (AttentionSpec, GatedMlpSpec, Qwen3Config, architectures, config_from_dict,
+from nncpu_b200.config import (AttentionSpec, GatedMlpSpec, architectures, config_from_dict,
                                load_config, register_architecture)
 from nncpu_b200.errors import BadFormat, UnsupportedModel
 from tiny import TINY, tiny_config

@@ -1,12 +1,10 @@
 """Chat on the device: turns on the session's own sequence keep their cache, the reply is the plain model's
 greedy continuation of the whole conversation, text comes in whole characters, and the command line's chat
 loop runs two turns and a /reset through a pipe."""
-import json
 import subprocess
 import sys
 
 import pytest
-import torch
 
 from conftest import ROOT
 from nncpu_b200 import GenerateParams, Model, SamplerParams, Session, SessionParams

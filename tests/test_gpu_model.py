@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import DEV, TOL, check, rel_err
+from gpu_util import TOL, check
 from nncpu_b200 import Engine, Model
 from nncpu_b200.errors import ContextFull, InvalidArgument
 from nncpu_b200.weights import SafetensorsFile, write_safetensors

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import nncpu_b200
-from gpu_util import DEV, check
+from gpu_util import check
 from nncpu_b200 import Engine, Model, perf_enable, perf_report, perf_reset, perf_span_ms, perf_totals
 from tiny import make_folder
 

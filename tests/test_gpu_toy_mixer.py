@@ -4,7 +4,6 @@ another position encoding, and a schedule that runs a layer twice and lets a
 layer read another layer's cache, is registered, built, loaded and stepped
 without a change to the library's files, and matches a plain version of itself."""
 import json
-import math
 from dataclasses import dataclass
 
 import numpy as np
@@ -12,7 +11,7 @@ import pytest
 import torch
 
 import plain_qwen3 as P
-from gpu_util import DEV, check
+from gpu_util import check
 from nncpu_b200 import Engine, Model
 from nncpu_b200.cache import StateRequest
 from nncpu_b200.config import (AttentionSpec, BlockSpec, EmbeddingSpec, FeedForwardSpec, MixerSpec, ModelSpec,
