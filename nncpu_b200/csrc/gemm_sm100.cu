@@ -394,8 +394,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // their partial tiles: each block writes its own to scratch memory, and a
 // second, wide kernel adds a tile's parts in block order (the order of k) and
 // runs the epilogue.  No block waits for another, and the sum does
-// not depend on timing.  Used for 17 to 256 tokens (weights are the 128-row
-// operand), where tiles are few and K is long.
+// not depend on timing.  Used for 65 to 256 tokens (from 17 on where the plan
+// asks for it; weights are the 128-row operand), where tiles are few and K is
+// long.
 // ---------------------------------------------------------------------------
 struct Segment {
     int tile, kb0, len;
